@@ -1,0 +1,91 @@
+"""ctypes binding of libc0ven_moe.so (include/moe_layer.h). The library is required: nothing here falls back to
+another implementation, and a missing library is an ImportError-like failure at first use."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libc0ven_moe.so")
+
+MOE_OK, MOE_ERROR, MOE_BAD_ARGUMENT, MOE_BUSY, MOE_TIMEOUT = range(5)
+FLAG_PROFILE, FLAG_NO_TENSOR = 1, 2
+STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", "copies")
+
+SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_layer_forward_device", "moe_layer_sync",
+           "moe_layer_read_route", "moe_layer_read_stats", "moe_layer_stage_ms", "moe_layer_stream", "moe_last_error",
+           "moe_abi_layout", "moe_to_runs", "moe_from_runs")
+
+
+class Config(C.Structure):
+    _fields_ = [("n_embd", C.c_uint32), ("n_ff", C.c_uint32), ("n_experts", C.c_uint32), ("n_used", C.c_uint32),
+                ("gate_type", C.c_uint32), ("down_type", C.c_uint32), ("shexp_gate_type", C.c_uint32),
+                ("shexp_down_type", C.c_uint32), ("expert_first", C.c_uint32), ("expert_count", C.c_uint32),
+                ("max_tokens", C.c_uint32), ("device", C.c_int32), ("swiglu_limit", C.c_float), ("flags", C.c_uint32)]
+
+
+class Weights(C.Structure):
+    _fields_ = [("router", C.c_void_p), ("shexp_gate_inp", C.c_void_p), ("router_bias", C.c_void_p),
+                ("gate_exps", C.c_void_p), ("up_exps", C.c_void_p), ("down_exps", C.c_void_p),
+                ("gate_shexp", C.c_void_p), ("up_shexp", C.c_void_p), ("down_shexp", C.c_void_p)]
+
+
+class Tile(C.Structure):
+    _fields_ = [("expert", C.c_uint32), ("slot", C.c_uint32), ("start", C.c_uint32), ("count", C.c_uint32)]
+
+
+class Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("calls", "rows", "assignments", "kernels", "h2d_bytes", "d2h_bytes",
+                                          "last_tiles", "last_experts_hit", "last_tensor_rows")]
+
+
+class AbiRow(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("offset", C.c_uint32), ("size", C.c_uint32)]
+
+
+STRUCTS = {"moe_layer_config": Config, "moe_layer_weights": Weights, "moe_tile": Tile, "moe_layer_stats": Stats,
+           "moe_abi_row": AbiRow}
+
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded library. Raises LibraryMissing when it has not been built (python -m c0ven_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LibraryMissing(f"{LIB_PATH} is not built: run `python -m c0ven_b200.build` (there is no other path)")
+        L = C.CDLL(LIB_PATH)
+        vp, u32 = C.c_void_p, C.c_uint32
+        L.moe_layer_create.argtypes = [C.POINTER(Config), C.POINTER(Weights), C.POINTER(vp)]
+        L.moe_layer_destroy.argtypes = [vp]
+        L.moe_layer_destroy.restype = None
+        L.moe_layer_forward.argtypes = [vp, vp, u32, vp]
+        L.moe_layer_forward_device.argtypes = [vp, vp, u32, vp, vp]
+        L.moe_layer_sync.argtypes = [vp, u32]
+        L.moe_layer_read_route.argtypes = [vp, vp, vp, vp, vp, u32, C.POINTER(u32)]
+        L.moe_layer_read_stats.argtypes = [vp, C.POINTER(Stats)]
+        L.moe_layer_stage_ms.argtypes = [vp, vp]
+        L.moe_layer_stream.argtypes = [vp]
+        L.moe_layer_stream.restype = vp
+        L.moe_last_error.argtypes = [vp]
+        L.moe_last_error.restype = C.c_char_p
+        L.moe_to_runs.argtypes = [u32, vp, C.c_uint64, vp]
+        L.moe_from_runs.argtypes = [u32, vp, C.c_uint64, vp]
+        L.moe_abi_layout.argtypes = [C.POINTER(AbiRow), u32]
+        L.moe_abi_layout.restype = u32
+        _lib = L
+    return _lib
+
+
+def abi_layout():
+    """The library's own table of struct fields: [(name, offset, size)]."""
+    L = lib()
+    n = L.moe_abi_layout(None, 0)
+    rows = (AbiRow * n)()
+    L.moe_abi_layout(rows, n)
+    return [(r.name.decode(), r.offset, r.size) for r in rows]

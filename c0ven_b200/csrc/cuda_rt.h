@@ -1,0 +1,128 @@
+// The thin device layer under the MoE layer: one device's buffers, stream, events and pinned host memory, with every
+// CUDA error turned into an exception the C ABI catches. It stands where the reference has core/ze (Runtime, List,
+// EventPool: core/ze/ze.h:50-217) and offers only what this path uses. Waits are polls against a deadline, never an
+// unbounded synchronise (the reference's list timeout, core/ze/ze.cpp:549-560).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <thread>
+
+namespace moe {
+
+struct CudaFailure : std::runtime_error {
+  cudaError_t code;
+  CudaFailure(cudaError_t c, const std::string &what) : std::runtime_error(what), code(c) {}
+};
+struct Timeout : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+struct BadArgument : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+inline void cuda_check(cudaError_t e, const char *what, const char *file, int line) {
+  if (e != cudaSuccess)
+    throw CudaFailure(e, std::string(what) + ": " + cudaGetErrorString(e) + " (" + file + ":" + std::to_string(line) + ")");
+}
+#define CUDA_OK(call) ::moe::cuda_check((call), #call, __FILE__, __LINE__)
+
+// Device memory of n elements of T, freed with its owner.
+template <class T>
+class DeviceBuffer {
+ public:
+  DeviceBuffer() = default;
+  DeviceBuffer(const DeviceBuffer &) = delete;
+  DeviceBuffer &operator=(const DeviceBuffer &) = delete;
+  ~DeviceBuffer() { release(); }
+  void alloc(size_t n) {
+    release();
+    if (n == 0) return;
+    CUDA_OK(cudaMalloc((void **)&p_, n * sizeof(T)));
+    n_ = n;
+  }
+  void release() {
+    if (p_) cudaFree(p_);
+    p_ = nullptr, n_ = 0;
+  }
+  T *get() const { return p_; }
+  size_t size() const { return n_; }
+  size_t bytes() const { return n_ * sizeof(T); }
+
+ private:
+  T *p_ = nullptr;
+  size_t n_ = 0;
+};
+
+// Pinned host memory.
+template <class T>
+class PinnedBuffer {
+ public:
+  PinnedBuffer() = default;
+  PinnedBuffer(const PinnedBuffer &) = delete;
+  PinnedBuffer &operator=(const PinnedBuffer &) = delete;
+  ~PinnedBuffer() {
+    if (p_) cudaFreeHost(p_);
+  }
+  void alloc(size_t n) {
+    if (p_) cudaFreeHost(p_), p_ = nullptr;
+    if (n) CUDA_OK(cudaMallocHost((void **)&p_, n * sizeof(T)));
+    n_ = n;
+  }
+  T *get() const { return p_; }
+  size_t size() const { return n_; }
+
+ private:
+  T *p_ = nullptr;
+  size_t n_ = 0;
+};
+
+class Stream {
+ public:
+  Stream() { CUDA_OK(cudaStreamCreateWithFlags(&s_, cudaStreamNonBlocking)); }
+  Stream(const Stream &) = delete;
+  ~Stream() {
+    if (s_) cudaStreamDestroy(s_);
+  }
+  cudaStream_t get() const { return s_; }
+  // Waits until the stream's work is done, polling; throws Timeout after timeout_ms.
+  void wait(uint32_t timeout_ms) const { wait_on(s_, timeout_ms); }
+  static void wait_on(cudaStream_t s, uint32_t timeout_ms) {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms ? timeout_ms : 60000);
+    for (unsigned spins = 0;; spins++) {
+      const cudaError_t e = cudaStreamQuery(s);
+      if (e == cudaSuccess) return;
+      if (e != cudaErrorNotReady) cuda_check(e, "cudaStreamQuery", __FILE__, __LINE__);
+      if (std::chrono::steady_clock::now() > deadline) throw Timeout("the stream's work did not finish in time");
+      if (spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+  }
+
+ private:
+  cudaStream_t s_ = nullptr;
+};
+
+class Event {
+ public:
+  Event() { CUDA_OK(cudaEventCreate(&e_)); }
+  Event(const Event &) = delete;
+  ~Event() {
+    if (e_) cudaEventDestroy(e_);
+  }
+  void record(cudaStream_t s) { CUDA_OK(cudaEventRecord(e_, s)); }
+  cudaEvent_t get() const { return e_; }
+  static float ms(const Event &a, const Event &b) {
+    float v = 0;
+    CUDA_OK(cudaEventElapsedTime(&v, a.e_, b.e_));
+    return v;
+  }
+
+ private:
+  cudaEvent_t e_ = nullptr;
+};
+
+}  // namespace moe

@@ -1,0 +1,377 @@
+// The experts' products for few rows per expert: integer dots of quantised weights against int8 activations, a group
+// of lanes per weight row, 128-bit loads of the quants in the runs layout, the weights decoded once in registers for
+// every row of the group, shuffle reductions. This is the bandwidth-bound path (decode and draft-verify steps); it
+// replaces the reference's grouped GEMVs (kernels/quant/moe.cl:230-302,416-471; kernels/quant/matvec.cl:101-159) and
+// follows the arithmetic of its CPU path (core/cpu/experts.cpp:152-284): activations as q8_0 or q8_K, integer block
+// sums, f32 scales.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "formats.h"
+
+namespace moe {
+
+// Rows start .. start + n of the expert order, all of one expert (its slot among this GPU's experts), n <= 8: the
+// reference's MoeGroup (shared/moe_tile.h:20-33) with the rows named by their place in expert order.
+struct MoeGroup {
+  uint32_t slot, start, n;
+};
+constexpr int kGroupMax = 8;
+
+// Quantised activation rows: codes [rows][K]; q8_0: d [rows][K/32] (the f16 scale, widened); q8_K: d [rows][K/256]
+// and bs [rows][K/16], the sums of each 16 codes.
+struct ActView {
+  const int8_t *q;
+  const float *d;
+  const int16_t *bs;
+};
+
+struct ExpertRowsArgs {
+  const uint8_t *w0, *w1;  // slot 0's slice of the matrix (gate, up) or (down, unused), runs layout
+  uint64_t slice_bytes;    // from one slot's slice to the next
+  uint32_t K, R;           // values per weight row; weight rows
+  uint32_t rows_per_cta;
+  ActView act;
+  const uint32_t *act_row;  // expert-order row -> activation row; null: the same row
+  const MoeGroup *groups;   // null: dense_rows rows of slot 0, taken M at a time
+  const uint32_t *ngroups;
+  uint32_t dense_rows;
+  float *out;  // out[expert-order row][r]
+  uint32_t out_stride;
+  float limit;  // SwiGLU limit, 0: off
+};
+
+__device__ __forceinline__ uint4 ldg_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int dot4x4(const uint4 &w, const int4 &a) {
+  int s = __dp4a((int)w.x, a.x, 0);
+  s = __dp4a((int)w.y, a.y, s);
+  s = __dp4a((int)w.z, a.z, s);
+  return __dp4a((int)w.w, a.w, s);
+}
+
+// Bytes of one activation row in shared memory: codes, then the scales (padded to 16), then q8_K's sums.
+__host__ __device__ constexpr uint32_t act_d_bytes(bool q8k, uint32_t K) { return q8k ? ((K / 64 + 15) & ~15u) : K / 8; }
+__host__ __device__ constexpr uint32_t act_row_stride(bool q8k, uint32_t K) { return K + act_d_bytes(q8k, K) + (q8k ? K / 8 : 0) + 16; }
+
+// SwiGLU as the CPU path states it (core/cpu/experts.cpp:21-27).
+__device__ __forceinline__ float swiglu(float g, float u, float limit) {
+  if (limit > 0.0f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
+// One lane's unit of a weight row: what it loads (Raw, 16 bytes of quants and the scales beside them) and its dot with
+// the matching codes of M activation rows. nblk: blocks in the slice; r: row; u: unit within the row.
+template <int QT>
+struct Unit;
+
+// Q8_0: y = d * q (docs/spec/QUANT_FORMATS.md:461). A unit is 16 codes, half a block.
+template <>
+struct Unit<QT_Q8_0> {
+  static constexpr int kValues = 16;
+  struct Raw {
+    uint4 q;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.q = ldg_stream16(s + (uint64_t)r * K + 16u * u);
+    x.d = __half2float(__ldg((const __half *)(s + 32 * nblk) + (uint64_t)r * (K / 32) + u / 2));
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc) {
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      const uint8_t *a = acts + t * stride;
+      const int s = dot4x4(x.q, *(const int4 *)(a + 16u * u));
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[u / 2], (float)s, acc[t]);
+    }
+  }
+};
+
+// Q4_K: y = d * sc * q - dmin * m, eight sub-blocks of 32 with 6-bit sc and m (QUANT_FORMATS.md:373-394). A unit is
+// 16 bytes of qs: 16 values of sub-block 2p in the low nibbles, 16 of sub-block 2p + 1 in the high ones.
+template <>
+struct Unit<QT_Q4_K> {
+  static constexpr int kValues = 32;
+  struct Raw {
+    uint4 q;
+    uint32_t s0, s1, s2;
+    __half2 dm;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.q = ldg_stream16(s + (uint64_t)r * (K / 2) + 16u * u);
+    const uint64_t blk = (uint64_t)r * (K / 256) + u / 8;
+    const uint32_t *sc = (const uint32_t *)(s + 128 * nblk + 12 * blk);
+    x.s0 = __ldg(sc), x.s1 = __ldg(sc + 1), x.s2 = __ldg(sc + 2);
+    x.dm = __ldg((const __half2 *)(s + 140 * nblk + 4 * blk));
+    return x;
+  }
+  __device__ static __forceinline__ uint32_t byte_of(const Raw &x, int i) {
+    const uint32_t w = i < 4 ? x.s0 : i < 8 ? x.s1 : x.s2;
+    return (w >> (8 * (i & 3))) & 0xFF;
+  }
+  // The packed scale and minimum of sub-block j (QUANT_FORMATS.md:386-392).
+  __device__ static __forceinline__ void scale_min(const Raw &x, int j, int &sc, int &m) {
+    if (j < 4) {
+      sc = byte_of(x, j) & 63;
+      m = byte_of(x, j + 4) & 63;
+    } else {
+      sc = (byte_of(x, j + 4) & 0xF) | ((byte_of(x, j - 4) >> 6) << 4);
+      m = (byte_of(x, j + 4) >> 4) | ((byte_of(x, j) >> 6) << 4);
+    }
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc) {
+    const uint32_t b = u / 8, j = u % 8, p = j / 2, hf = j & 1;
+    int sc_lo, m_lo, sc_hi, m_hi;
+    scale_min(x, 2 * p, sc_lo, m_lo);
+    scale_min(x, 2 * p + 1, sc_hi, m_hi);
+    const uint4 lo = make_uint4(x.q.x & 0x0F0F0F0Fu, x.q.y & 0x0F0F0F0Fu, x.q.z & 0x0F0F0F0Fu, x.q.w & 0x0F0F0F0Fu);
+    const uint4 hi = make_uint4((x.q.x >> 4) & 0x0F0F0F0Fu, (x.q.y >> 4) & 0x0F0F0F0Fu, (x.q.z >> 4) & 0x0F0F0F0Fu,
+                                (x.q.w >> 4) & 0x0F0F0F0Fu);
+    const float d = __low2float(x.dm), dmin = __high2float(x.dm);
+    const uint32_t dsz = act_d_bytes(true, K);
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      const uint8_t *a = acts + t * stride;
+      const uint8_t *av = a + 256 * b + 64 * p + 16 * hf;
+      const int s_lo = dot4x4(lo, *(const int4 *)av), s_hi = dot4x4(hi, *(const int4 *)(av + 32));
+      const int16_t *bs = (const int16_t *)(a + K + dsz) + 16 * b + 4 * p + hf;
+      const float da = ((const float *)(a + K))[b];
+      acc[t] += da * (d * (float)(sc_lo * s_lo + sc_hi * s_hi) - dmin * (float)(m_lo * bs[0] + m_hi * bs[2]));
+    }
+  }
+};
+
+// Q6_K: y = d * scales[v / 16] * (q - 32), 6-bit codes split into ql (low 4) and qh (high 2) (QUANT_FORMATS.md:419-441).
+// A unit is 16 bytes of ql with the 16 bytes of qh that complete them: 16 values in the low nibbles and 16 in the high
+// ones, each a whole group of 16 with its own int8 scale.
+template <>
+struct Unit<QT_Q6_K> {
+  static constexpr int kValues = 32;
+  struct Raw {
+    uint4 ql, qh;
+    int sc_lo, sc_hi;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.ql = ldg_stream16(s + (uint64_t)r * (K / 2) + 16u * u);
+    const uint32_t j = u % 8, h = j / 4, jj = j % 4;
+    const uint64_t blk = (uint64_t)r * (K / 256) + u / 8;
+    x.qh = ldg_stream16(s + 128 * nblk + 64 * blk + 32 * h + 16 * (jj & 1));
+    const int8_t *sc = (const int8_t *)(s + 192 * nblk + 16 * blk) + 8 * h + 2 * (jj >> 1) + (jj & 1);
+    x.sc_lo = __ldg(sc), x.sc_hi = __ldg(sc + 4);
+    x.d = __half2float(__ldg((const __half *)(s + 208 * nblk) + blk));
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc) {
+    const uint32_t b = u / 8, j = u % 8, h = j / 4, jj = j % 4, sh = jj < 2 ? 0 : 2;
+    const uint32_t g16 = 8 * h + 2 * (jj >> 1) + (jj & 1);  // the low nibbles' group of 16; the high ones' is 4 on
+    uint4 lo, hi;
+    lo.x = (x.ql.x & 0x0F0F0F0Fu) | (((x.qh.x >> sh) & 0x03030303u) << 4);
+    lo.y = (x.ql.y & 0x0F0F0F0Fu) | (((x.qh.y >> sh) & 0x03030303u) << 4);
+    lo.z = (x.ql.z & 0x0F0F0F0Fu) | (((x.qh.z >> sh) & 0x03030303u) << 4);
+    lo.w = (x.ql.w & 0x0F0F0F0Fu) | (((x.qh.w >> sh) & 0x03030303u) << 4);
+    hi.x = ((x.ql.x >> 4) & 0x0F0F0F0Fu) | (((x.qh.x >> (sh + 4)) & 0x03030303u) << 4);
+    hi.y = ((x.ql.y >> 4) & 0x0F0F0F0Fu) | (((x.qh.y >> (sh + 4)) & 0x03030303u) << 4);
+    hi.z = ((x.ql.z >> 4) & 0x0F0F0F0Fu) | (((x.qh.z >> (sh + 4)) & 0x03030303u) << 4);
+    hi.w = ((x.ql.w >> 4) & 0x0F0F0F0Fu) | (((x.qh.w >> (sh + 4)) & 0x03030303u) << 4);
+    const uint32_t dsz = act_d_bytes(true, K);
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      const uint8_t *a = acts + t * stride;
+      const uint8_t *av = a + 256 * b + 16 * g16;
+      const int s_lo = dot4x4(lo, *(const int4 *)av), s_hi = dot4x4(hi, *(const int4 *)(av + 64));
+      const int16_t *bs = (const int16_t *)(a + K + dsz) + 16 * b + g16;
+      const int isum = x.sc_lo * (s_lo - 32 * bs[0]) + x.sc_hi * (s_hi - 32 * bs[4]);
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[b], (float)isum, acc[t]);
+    }
+  }
+};
+
+// IQ3_S: y = d * (1 + 2 s) * grid[index][i] * sign, 9-bit indices into the 512-entry codebook, one per 4 values
+// (QUANT_FORMATS.md:178-207). A unit is 16 bytes of qs: two sub-blocks of 32. The codebook sits in shared memory; the
+// signs go onto the codebook's bytes once, for every activation row.
+template <>
+struct Unit<QT_IQ3_S> {
+  static constexpr int kValues = 64;
+  struct Raw {
+    uint4 qs;
+    uint2 sg;
+    uint32_t qh, sc;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.qs = ldg_stream16(s + (uint64_t)r * (K / 4) + 16u * u);
+    const uint32_t c = u % 4;
+    const uint64_t blk = (uint64_t)r * (K / 256) + u / 4;
+    x.sg = __ldg((const uint2 *)(s + 64 * nblk + 32 * blk + 8 * c));
+    x.qh = __ldg((const uint16_t *)(s + 96 * nblk + 8 * blk + 2 * c));
+    x.sc = __ldg(s + 104 * nblk + 4 * blk + c);
+    x.d = __half2float(__ldg((const __half *)(s + 108 * nblk) + blk));
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc,
+                                             const uint32_t *grid) {
+    const uint32_t b = u / 4, c = u % 4;
+    int g[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const uint32_t word = i < 4 ? x.qs.x : i < 8 ? x.qs.y : i < 12 ? x.qs.z : x.qs.w;
+      const uint32_t idx = ((word >> (8 * (i & 3))) & 0xFF) | (((x.qh >> i) & 1u) << 8);
+      const uint32_t nib = ((i < 8 ? x.sg.x : x.sg.y) >> (4 * (i & 7))) & 0xF;
+      const uint32_t mask = ((nib & 1u) | ((nib & 2u) << 7) | ((nib & 4u) << 14) | ((nib & 8u) << 21)) * 0xFFu;
+      g[i] = (int)__vsub4(grid[idx] ^ mask, mask);
+    }
+    const int sc0 = 2 * (int)(x.sc & 0xF) + 1, sc1 = 2 * (int)((x.sc >> 4) & 0xF) + 1;
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      const uint8_t *a = acts + t * stride;
+      const int4 *av = (const int4 *)(a + 256 * b + 64 * c);
+      const int4 a0 = av[0], a1 = av[1], a2 = av[2], a3 = av[3];
+      int s0 = __dp4a(g[0], a0.x, 0), s1 = __dp4a(g[8], a2.x, 0);
+      s0 = __dp4a(g[1], a0.y, s0), s1 = __dp4a(g[9], a2.y, s1);
+      s0 = __dp4a(g[2], a0.z, s0), s1 = __dp4a(g[10], a2.z, s1);
+      s0 = __dp4a(g[3], a0.w, s0), s1 = __dp4a(g[11], a2.w, s1);
+      s0 = __dp4a(g[4], a1.x, s0), s1 = __dp4a(g[12], a3.x, s1);
+      s0 = __dp4a(g[5], a1.y, s0), s1 = __dp4a(g[13], a3.y, s1);
+      s0 = __dp4a(g[6], a1.z, s0), s1 = __dp4a(g[14], a3.z, s1);
+      s0 = __dp4a(g[7], a1.w, s0), s1 = __dp4a(g[15], a3.w, s1);
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[b], (float)(sc0 * s0 + sc1 * s1), acc[t]);
+    }
+  }
+};
+
+template <int QT, int M>
+__device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride,
+                                         float *acc, const uint32_t *grid) {
+  if constexpr (QT == QT_IQ3_S)
+    Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, grid);
+  else
+    Unit<QT>::template dot<M>(x, K, u, acts, stride, acc);
+}
+
+// NMAT 2: h[row][r] = swiglu(gate_r . x, up_r . x); NMAT 1: y[row][r] = down_r . h. One CTA of 8 warps per (row tile,
+// group); G lanes share a weight row (G = the row's units, up to 32), each taking UPL of its units (UPL 0: as many as
+// the row has, found at run time). Launch: grid (R / rows_per_cta, groups at most), 256 threads, dynamic shared memory
+// M * act_row_stride (+ 2 KB for IQ3_S's codebook).
+template <int QT, int NMAT, int M, int G, int UPL>
+__global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, const uint32_t *__restrict__ grid_global) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  constexpr bool q8k = act_is_q8k(QT);
+  uint32_t slot, start, n;
+  if (a.groups) {
+    if (blockIdx.y >= *a.ngroups) return;
+    const MoeGroup g = a.groups[blockIdx.y];
+    slot = g.slot, start = g.start, n = g.n;
+  } else {
+    start = blockIdx.y * M;
+    if (start >= a.dense_rows) return;
+    slot = 0, n = min((uint32_t)M, a.dense_rows - start);
+  }
+  const uint32_t K = a.K, stride = act_row_stride(q8k, K), dsz = act_d_bytes(q8k, K);
+  uint32_t *grid = (uint32_t *)(smem + M * stride);
+  if constexpr (QT == QT_IQ3_S)
+    for (uint32_t i = threadIdx.x; i < 512; i += 256) grid[i] = grid_global[i];
+  // The group's activation rows into shared memory; rows past n get zero scales, so they add nothing.
+  for (uint32_t t = 0; t < (uint32_t)M; t++) {
+    uint8_t *dst = smem + t * stride;
+    if (t < n) {
+      const uint64_t row = a.act_row ? a.act_row[start + t] : start + t;
+      const int4 *src = (const int4 *)(a.act.q + row * K);
+      for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int4 *)dst)[i] = src[i];
+      if (q8k) {
+        for (uint32_t i = threadIdx.x; i < K / 256; i += 256) ((float *)(dst + K))[i] = a.act.d[row * (K / 256) + i];
+        for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int16_t *)(dst + K + dsz))[i] = a.act.bs[row * (K / 16) + i];
+      } else {
+        for (uint32_t i = threadIdx.x; i < K / 32; i += 256) ((float *)(dst + K))[i] = a.act.d[row * (K / 32) + i];
+      }
+    } else {
+      for (uint32_t i = threadIdx.x; i < dsz / 4; i += 256) ((float *)(dst + K))[i] = 0.0f;
+    }
+  }
+  __syncthreads();
+
+  const uint32_t upr = K / Unit<QT>::kValues;  // units per weight row
+  const uint64_t nblk = (uint64_t)a.R * (K / block_values(QT));
+  const uint8_t *w0 = a.w0 + (uint64_t)slot * a.slice_bytes;
+  const uint8_t *w1 = NMAT == 2 ? a.w1 + (uint64_t)slot * a.slice_bytes : nullptr;
+  const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, li = lane % G, sub = lane / G;
+  constexpr uint32_t RPP = 32 / G;  // weight rows a warp takes per pass
+  const uint32_t rows_per_warp = a.rows_per_cta / 8;
+  const uint32_t r_begin = blockIdx.x * a.rows_per_cta + warp * rows_per_warp;
+  constexpr int NU = UPL > 0 ? UPL : 1;
+  using Raw = typename Unit<QT>::Raw;
+
+  for (uint32_t rr = 0; rr < rows_per_warp; rr += RPP) {
+    const uint32_t r = r_begin + rr + sub;
+    float acc[NMAT][M];
+#pragma unroll
+    for (int m = 0; m < NMAT; m++)
+#pragma unroll
+      for (int t = 0; t < M; t++) acc[m][t] = 0.0f;
+    if (r < a.R) {
+      if constexpr (UPL > 0) {
+        Raw raw[NMAT][NU];
+#pragma unroll
+        for (int j = 0; j < NU; j++) {
+          raw[0][j] = Unit<QT>::fetch(w0, nblk, K, r, li + G * j, grid);
+          if constexpr (NMAT == 2) raw[1][j] = Unit<QT>::fetch(w1, nblk, K, r, li + G * j, grid);
+        }
+#pragma unroll
+        for (int j = 0; j < NU; j++) {
+          unit_dot<QT, M>(raw[0][j], K, li + G * j, smem, stride, acc[0], grid);
+          if constexpr (NMAT == 2) unit_dot<QT, M>(raw[1][j], K, li + G * j, smem, stride, acc[1], grid);
+        }
+      } else {
+        for (uint32_t u = li; u < upr; u += G) {
+          const Raw x0 = Unit<QT>::fetch(w0, nblk, K, r, u, grid);
+          unit_dot<QT, M>(x0, K, u, smem, stride, acc[0], grid);
+          if constexpr (NMAT == 2) {
+            const Raw x1 = Unit<QT>::fetch(w1, nblk, K, r, u, grid);
+            unit_dot<QT, M>(x1, K, u, smem, stride, acc[1], grid);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < NMAT; m++)
+#pragma unroll
+      for (int t = 0; t < M; t++)
+#pragma unroll
+        for (int off = G / 2; off > 0; off >>= 1) acc[m][t] += __shfl_xor_sync(0xffffffffu, acc[m][t], off);
+    if (li == 0 && r < a.R) {
+#pragma unroll
+      for (int t = 0; t < M; t++)
+        if ((uint32_t)t < n) {
+          float v = acc[0][t];
+          if constexpr (NMAT == 2) v = swiglu(acc[0][t], acc[1][t], a.limit);
+          a.out[(uint64_t)(start + t) * a.out_stride + r] = v;
+        }
+    }
+  }
+}
+
+// Launches the instantiation for (M, K): host side of the kernels above. Returns cudaErrorInvalidValue for a shape no
+// instantiation takes. max_groups: the grid's second extent.
+template <int QT, int NMAT>
+cudaError_t launch_expert_rows(const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st);
+
+}  // namespace moe

@@ -1,0 +1,51 @@
+// Instantiates and dispatches k_expert_rows for one weight type; included by the per-type .cu files with
+// EXPERT_ROWS_QT set, so that the types compile side by side.
+#pragma once
+
+#include "expert_rows.cuh"
+
+namespace moe {
+
+template <int QT, int NMAT, int M, int G, int UPL>
+static cudaError_t launch_one(ExpertRowsArgs a, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st) {
+  constexpr bool q8k = act_is_q8k(QT);
+  const uint32_t rpp = 32 / G;
+  if (a.rows_per_cta < 8 * rpp) a.rows_per_cta = 8 * rpp;
+  const size_t smem = (size_t)M * act_row_stride(q8k, a.K) + (QT == QT_IQ3_S ? 2048 : 0);
+  auto kernel = k_expert_rows<QT, NMAT, M, G, UPL>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  const dim3 grid((a.R + a.rows_per_cta - 1) / a.rows_per_cta, max_groups);
+  kernel<<<grid, 256, smem, st>>>(a, grid_global);
+  return cudaGetLastError();
+}
+
+template <int QT, int NMAT, int M>
+static cudaError_t launch_shape(const ExpertRowsArgs &a, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st) {
+  const uint32_t upr = a.K / Unit<QT>::kValues;
+  // The three row lengths the kernels are specialised for are 2048, 512 and 256 values; any other takes the general
+  // instantiation, which finds a row's units at run time.
+  constexpr uint32_t U2048 = 2048 / Unit<QT>::kValues, U512 = 512 / Unit<QT>::kValues, U256 = 256 / Unit<QT>::kValues;
+  if (upr == U2048) return launch_one<QT, NMAT, M, 32, U2048 / 32>(a, max_groups, grid_global, st);
+  if (upr == U512) return launch_one<QT, NMAT, M, (U512 < 32 ? U512 : 32), 1>(a, max_groups, grid_global, st);
+  if (upr == U256) return launch_one<QT, NMAT, M, (U256 < 32 ? U256 : 32), 1>(a, max_groups, grid_global, st);
+  return launch_one<QT, NMAT, M, 32, 0>(a, max_groups, grid_global, st);
+}
+
+template <int QT, int NMAT>
+cudaError_t launch_expert_rows(const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st) {
+  switch (M) {
+    case 1: return launch_shape<QT, NMAT, 1>(a, max_groups, grid_global, st);
+    case 2: return launch_shape<QT, NMAT, 2>(a, max_groups, grid_global, st);
+    case 4: return launch_shape<QT, NMAT, 4>(a, max_groups, grid_global, st);
+    case 8: return launch_shape<QT, NMAT, 8>(a, max_groups, grid_global, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template cudaError_t launch_expert_rows<EXPERT_ROWS_QT, 1>(const ExpertRowsArgs &, int, uint32_t, const uint32_t *, cudaStream_t);
+template cudaError_t launch_expert_rows<EXPERT_ROWS_QT, 2>(const ExpertRowsArgs &, int, uint32_t, const uint32_t *, cudaStream_t);
+
+}  // namespace moe

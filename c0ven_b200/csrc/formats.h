@@ -1,0 +1,57 @@
+// The GGUF block formats the layer reads and the "runs" layout the GPU holds them in: a slice of n blocks is one run
+// per field, the quants first and the f16 scales last, field f of block k at run_offset(f, n) + k * field_size(f).
+// The formats and the run order are the reference's (shared/quant.h:36-176; docs/spec/QUANT_FORMATS.md, "Wide loads");
+// the layout is a permutation of the file's bytes, so an expert costs the bytes it has in the file.
+#pragma once
+
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define FMT_HD __host__ __device__
+#else
+#define FMT_HD
+#endif
+
+namespace moe {
+
+enum : uint32_t { QT_Q8_0 = 8, QT_Q4_K = 12, QT_Q6_K = 14, QT_IQ3_S = 21 };
+
+FMT_HD constexpr uint32_t block_values(uint32_t t) { return t == QT_Q8_0 ? 32u : (t == QT_Q4_K || t == QT_Q6_K || t == QT_IQ3_S) ? 256u : 0u; }
+FMT_HD constexpr uint32_t block_bytes(uint32_t t) {
+  return t == QT_Q8_0 ? 34u : t == QT_Q4_K ? 144u : t == QT_Q6_K ? 210u : t == QT_IQ3_S ? 110u : 0u;
+}
+FMT_HD constexpr bool type_known(uint32_t t) { return block_bytes(t) != 0; }
+// Whether the type's dot takes activations as q8_K (256 values, f32 scale, sums of 16) rather than q8_0 (32 values,
+// f16 scale): docs/spec/MODEL_LAYER.md, section 6.
+FMT_HD constexpr bool act_is_q8k(uint32_t t) { return t != QT_Q8_0; }
+FMT_HD constexpr uint64_t row_bytes(uint32_t t, uint64_t n) { return n / block_values(t) * block_bytes(t); }
+
+struct Field {
+  uint32_t offset, size;
+};
+FMT_HD constexpr uint32_t nfields(uint32_t t) { return t == QT_Q8_0 ? 2u : t == QT_Q4_K ? 3u : t == QT_Q6_K ? 4u : t == QT_IQ3_S ? 5u : 0u; }
+// Field f of type t, in run order.
+FMT_HD constexpr Field field(uint32_t t, uint32_t f) {
+  switch (t) {
+    case QT_Q8_0: return f == 0 ? Field{2, 32} : Field{0, 2};                                                  // qs, d
+    case QT_Q4_K: return f == 0 ? Field{16, 128} : f == 1 ? Field{4, 12} : Field{0, 4};                         // qs, scales, d+dmin
+    case QT_Q6_K: return f == 0 ? Field{0, 128} : f == 1 ? Field{128, 64} : f == 2 ? Field{192, 16} : Field{208, 2};  // ql, qh, scales, d
+    case QT_IQ3_S:
+      return f == 0 ? Field{2, 64} : f == 1 ? Field{74, 32} : f == 2 ? Field{66, 8} : f == 3 ? Field{106, 4} : Field{0, 2};  // qs, signs, qh, scales, d
+    default: return Field{0, 0};
+  }
+}
+FMT_HD constexpr uint64_t run_offset(uint32_t t, uint32_t f, uint64_t n) {
+  uint64_t off = 0;
+  for (uint32_t g = 0; g < f; g++) off += field(t, g).size;
+  return off * n;
+}
+
+// Host repack, threaded (runs.cpp). Both are permutations of the slice's bytes.
+void to_runs(uint32_t type, const uint8_t *file_blocks, uint64_t nblocks, uint8_t *dst);
+void from_runs(uint32_t type, const uint8_t *runs, uint64_t nblocks, uint8_t *dst);
+// nslices slices of nblocks each, one after another, on up to `threads` threads.
+void to_runs_slices(uint32_t type, const uint8_t *file_blocks, uint64_t nblocks, uint64_t nslices, uint8_t *dst,
+                    unsigned threads);
+
+}  // namespace moe

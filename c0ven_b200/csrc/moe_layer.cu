@@ -1,0 +1,452 @@
+// The C ABI of include/moe_layer.h over the kernels of this directory: one layer's weights in the runs layout, the
+// buffers a call needs, and the order of a call's stages. It does, for one GPU that holds every expert, what the
+// reference's Model::step and Model::prompt_runs record for a layer's MoE block
+// (core/models/qwen4exp/model.cpp:1348-1418, prompt.cpp:606-656) with its CPU path's arithmetic
+// (core/cpu/experts.cpp:152-284).
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "cuda_rt.h"
+#include "expert_rows.cuh"
+#include "formats.h"
+#include "iq3s_grid.h"
+#include "moe_layer.h"
+#include "route_kernels.cuh"
+
+namespace moe {
+
+template <int QT, int NMAT>
+cudaError_t launch_expert_rows(const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st);
+
+static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid,
+                               cudaStream_t st) {
+#define ROWS_CASE(T)                                                                                            \
+  case T:                                                                                                       \
+    return nmat == 2 ? launch_expert_rows<T, 2>(a, M, max_groups, grid, st) : launch_expert_rows<T, 1>(a, M, max_groups, grid, st);
+  switch (qt) {
+    ROWS_CASE(QT_Q8_0)
+    ROWS_CASE(QT_Q4_K)
+    ROWS_CASE(QT_Q6_K)
+    ROWS_CASE(QT_IQ3_S)
+    default: return cudaErrorInvalidValue;
+  }
+#undef ROWS_CASE
+}
+
+// Quantised activation rows on the device, in the format a weight type's dot takes.
+struct ActBuffers {
+  DeviceBuffer<int8_t> q;
+  DeviceBuffer<float> d;
+  DeviceBuffer<int16_t> bs;
+  bool q8k = false;
+  void alloc(uint64_t rows, uint32_t K, bool k) {
+    q8k = k;
+    q.alloc(rows * K);
+    d.alloc(rows * (k ? K / 256 : K / 32));
+    if (k) bs.alloc(rows * (K / 16));
+  }
+  ActView view(uint64_t row0, uint32_t K) const {
+    return ActView{q.get() + row0 * K, d.get() + row0 * (q8k ? K / 256 : K / 32), q8k ? bs.get() + row0 * (K / 16) : nullptr};
+  }
+};
+
+enum Stage { ST_QUANT, ST_ROUTER, ST_PACK, ST_GATE_UP, ST_DOWN, ST_SHARED, ST_COMBINE, ST_COPIES };
+
+}  // namespace moe
+
+using namespace moe;
+
+struct moe_layer {
+  moe_layer_config cfg{};
+  uint32_t E = 0, F = 0, NE = 0, K = 0, N = 0, local = 0, Tmax = 0;
+  bool has_shared = false, profile = false;
+  std::unique_ptr<Stream> stream;
+  // Weights.
+  DeviceBuffer<float> router, bias;
+  DeviceBuffer<uint8_t> wg, wu, wd, sg, su, sd;
+  DeviceBuffer<uint32_t> grid;
+  uint64_t gate_slice = 0, down_slice = 0;
+  // A call's buffers.
+  DeviceBuffer<float> x, out, rl, w, gs, h, y, s;
+  DeviceBuffer<int32_t> ids;
+  DeviceBuffer<uint32_t> chunk_hist, chunk_off, cnt, base, counters, inv, row_src;
+  DeviceBuffer<MoeTile> tiles;
+  DeviceBuffer<MoeGroup> groups;
+  ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
+  bool shared_x_same = true, rows_attr_set = false;
+  uint32_t last_T = 0;
+  // Profiling: one event before each stage and one after the last.
+  std::vector<std::unique_ptr<Event>> ev;
+  bool ev_valid = false;
+  moe_layer_stats stats{};
+  std::string err;
+  std::mutex mu;
+};
+
+static thread_local std::string g_create_error;
+
+namespace {
+
+void launched(moe_layer *l, cudaError_t e, const char *what) {
+  cuda_check(e, what, __FILE__, __LINE__);
+  l->stats.kernels++;
+}
+
+void mark(moe_layer *l, int stage, cudaStream_t st) {
+  if (l->profile) l->ev[stage]->record(st);
+}
+
+void upload_matrix(DeviceBuffer<uint8_t> &dst, uint32_t type, const void *src, uint64_t nblk, uint64_t nslices, cudaStream_t st) {
+  const uint64_t bytes = nblk * nslices * block_bytes(type);
+  std::vector<uint8_t> runs(bytes);
+  to_runs_slices(type, (const uint8_t *)src, nblk, nslices, runs.data(), std::max(1u, std::thread::hardware_concurrency()));
+  dst.alloc(bytes + 16);  // room for a 16-byte load that starts inside the last run
+  CUDA_OK(cudaMemcpyAsync(dst.get(), runs.data(), bytes, cudaMemcpyHostToDevice, st));
+  CUDA_OK(cudaStreamSynchronize(st));
+}
+
+void check_config(const moe_layer_config &c, const moe_layer_weights &w) {
+  auto bad = [](const std::string &m) { throw BadArgument(m); };
+  if (c.n_embd == 0 || c.n_embd % 256) bad("n_embd must be a multiple of 256");
+  if (c.n_ff == 0 || c.n_ff % 256) bad("n_ff must be a multiple of 256");
+  if (c.n_experts == 0 || c.n_experts % 32 || c.n_experts > 512) bad("n_experts must be a multiple of 32, at most 512");
+  if (c.n_used == 0 || c.n_used > 16 || c.n_used > c.n_experts) bad("n_used must be 1 .. 16 and at most n_experts");
+  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K or IQ3_S");
+  if (c.shexp_gate_type && (!type_known(c.shexp_gate_type) || !type_known(c.shexp_down_type)))
+    bad("the shared expert's types must be Q8_0, Q4_K, Q6_K or IQ3_S");
+  if (c.expert_first + (c.expert_count ? c.expert_count : c.n_experts - c.expert_first) > c.n_experts)
+    bad("expert_first + expert_count passes n_experts");
+  if (!w.router || !w.gate_exps || !w.up_exps || !w.down_exps) bad("router and the experts' three tensors are required");
+  if (c.shexp_gate_type && (!w.shexp_gate_inp || !w.gate_shexp || !w.up_shexp || !w.down_shexp))
+    bad("a shared expert needs its gate vector and three matrices");
+}
+
+void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w) {
+  check_config(c, w);
+  int ndev = 0;
+  CUDA_OK(cudaGetDeviceCount(&ndev));
+  if (c.device < 0 || c.device >= ndev) throw BadArgument("no CUDA device " + std::to_string(c.device));
+  CUDA_OK(cudaSetDevice(c.device));
+  l->cfg = c;
+  l->E = c.n_embd, l->F = c.n_ff, l->NE = c.n_experts, l->K = c.n_used, l->N = c.n_experts + 1;
+  l->local = c.expert_count ? c.expert_count : c.n_experts - c.expert_first;
+  l->Tmax = c.max_tokens ? c.max_tokens : 4352;
+  l->has_shared = c.shexp_gate_type != 0;
+  l->profile = c.flags & MOE_FLAG_PROFILE;
+  l->stream = std::make_unique<Stream>();
+  cudaStream_t st = l->stream->get();
+  const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, T = l->Tmax;
+  const uint64_t A = (uint64_t)T * K;
+
+  // The router's rows, then the shared expert's gate vector as row NE (zeros without one).
+  std::vector<float> rw((size_t)l->N * E, 0.0f);
+  std::memcpy(rw.data(), w.router, (size_t)NE * E * sizeof(float));
+  if (l->has_shared) std::memcpy(rw.data() + (size_t)NE * E, w.shexp_gate_inp, E * sizeof(float));
+  l->router.alloc(rw.size());
+  CUDA_OK(cudaMemcpyAsync(l->router.get(), rw.data(), rw.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+  if (w.router_bias) {
+    l->bias.alloc(NE);
+    CUDA_OK(cudaMemcpyAsync(l->bias.get(), w.router_bias, NE * sizeof(float), cudaMemcpyHostToDevice, st));
+  }
+  l->grid.alloc(512);
+  CUDA_OK(cudaMemcpyAsync(l->grid.get(), kIq3sGrid, sizeof(kIq3sGrid), cudaMemcpyHostToDevice, st));
+  CUDA_OK(cudaStreamSynchronize(st));
+
+  const uint64_t gblk = (uint64_t)F * (E / block_values(c.gate_type)), dblk = (uint64_t)E * (F / block_values(c.down_type));
+  l->gate_slice = gblk * block_bytes(c.gate_type), l->down_slice = dblk * block_bytes(c.down_type);
+  upload_matrix(l->wg, c.gate_type, w.gate_exps, gblk, l->local, st);
+  upload_matrix(l->wu, c.gate_type, w.up_exps, gblk, l->local, st);
+  upload_matrix(l->wd, c.down_type, w.down_exps, dblk, l->local, st);
+  if (l->has_shared) {
+    upload_matrix(l->sg, c.shexp_gate_type, w.gate_shexp, (uint64_t)F * (E / block_values(c.shexp_gate_type)), 1, st);
+    upload_matrix(l->su, c.shexp_gate_type, w.up_shexp, (uint64_t)F * (E / block_values(c.shexp_gate_type)), 1, st);
+    upload_matrix(l->sd, c.shexp_down_type, w.down_shexp, (uint64_t)E * (F / block_values(c.shexp_down_type)), 1, st);
+  }
+
+  const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
+  l->x.alloc((size_t)T * E), l->out.alloc((size_t)T * E);
+  l->rl.alloc((size_t)T * l->N), l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T);
+  l->chunk_hist.alloc((size_t)nchunks * NE), l->chunk_off.alloc((size_t)nchunks * NE);
+  l->cnt.alloc(NE), l->base.alloc(NE), l->counters.alloc(4), l->inv.alloc(A), l->row_src.alloc(A);
+  l->tiles.alloc(A / kTileRows + NE), l->groups.alloc(A / kGroupMax + NE);
+  l->h.alloc((A + T) * F), l->y.alloc(A * E);
+  l->xq_routed.alloc(T, E, act_is_q8k(c.gate_type));
+  l->hq_routed.alloc(A, F, act_is_q8k(c.down_type));
+  if (l->has_shared) {
+    l->s.alloc((size_t)T * E);
+    l->shared_x_same = act_is_q8k(c.shexp_gate_type) == act_is_q8k(c.gate_type);
+    if (!l->shared_x_same) l->xq_shared.alloc(T, E, act_is_q8k(c.shexp_gate_type));
+    l->hq_shared.alloc(T, F, act_is_q8k(c.shexp_down_type));
+  }
+  CUDA_OK(cudaMemsetAsync(l->counters.get(), 0, 4 * sizeof(uint32_t), st));
+  for (int i = 0; i <= MOE_STAGES; i++) l->ev.push_back(std::make_unique<Event>());
+  CUDA_OK(cudaStreamSynchronize(st));
+}
+
+void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, const ActBuffers &dst, uint64_t row0, cudaStream_t st) {
+  const uint64_t nblk = rows * (Kv / 256);
+  if (nblk == 0) return;
+  const ActView v = dst.view(row0, Kv);
+  const unsigned grid = (unsigned)((nblk + 7) / 8);
+  if (dst.q8k)
+    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs);
+  else
+    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d);
+  launched(l, cudaGetLastError(), "quantize");
+}
+
+// Rows a group's kernel takes at once: a group holds at most min(T, 8) rows, an expert having one row per token at most.
+int group_rows(uint32_t T) { return T > 4 ? 8 : T > 2 ? 4 : (int)T; }
+
+// The whole block on device buffers, queued on st.
+void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {
+  const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, N = l->N;
+  const uint64_t A = (uint64_t)T * K;
+  const moe_layer_config &c = l->cfg;
+  if (l->local != NE) throw BadArgument("this call needs every expert on the GPU; an expert-parallel layer goes stage by stage");
+
+  mark(l, ST_QUANT, st);
+  quantize_rows(l, x, T, E, l->xq_routed, 0, st);
+  if (l->has_shared && !l->shared_x_same) quantize_rows(l, x, T, E, l->xq_shared, 0, st);
+
+  mark(l, ST_ROUTER, st);
+  if (T <= 64) {
+    const size_t smem = (size_t)8 * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float);
+    if (!l->rows_attr_set) {
+      CUDA_OK(cudaFuncSetAttribute(k_router_logits_rows<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      l->rows_attr_set = true;
+    }
+    k_router_logits_rows<8><<<dim3((N + 15) / 16, (T + 7) / 8), 128, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+  } else {
+    k_router_logits_tiles<<<dim3((N + 63) / 64, (T + 127) / 128), 256, 0, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+  }
+  launched(l, cudaGetLastError(), "router logits");
+  const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
+  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->chunk_hist.get());
+  launched(l, cudaGetLastError(), "router top-k");
+
+  mark(l, ST_PACK, st);
+  const PackOut po{l->cnt.get(), l->base.get(), l->chunk_off.get(), l->tiles.get(), l->groups.get(), l->counters.get()};
+  k_pack_scan<<<1, 512, 0, st>>>(l->chunk_hist.get(), nchunks, NE, c.expert_first, po);
+  launched(l, cudaGetLastError(), "pack scan");
+  const uint32_t chunk_len = kChunkTokens * K;
+  k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->base.get(), l->chunk_off.get(), K,
+                                                             l->inv.get(), l->row_src.get());
+  launched(l, cudaGetLastError(), "pack fill");
+
+  const int M = group_rows(T);
+  const uint32_t max_groups = (uint32_t)std::min<uint64_t>(A, A / kGroupMax + NE);
+  mark(l, ST_GATE_UP, st);
+  {
+    ExpertRowsArgs a{};
+    a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F, a.rows_per_cta = 32;
+    a.act = l->xq_routed.view(0, E), a.act_row = l->row_src.get();
+    a.groups = l->groups.get(), a.ngroups = l->counters.get() + 1;
+    a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
+    launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
+    quantize_rows(l, l->h.get(), A, F, l->hq_routed, 0, st);
+  }
+  mark(l, ST_DOWN, st);
+  {
+    ExpertRowsArgs a{};
+    a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E, a.rows_per_cta = 128;
+    a.act = l->hq_routed.view(0, F), a.act_row = nullptr;
+    a.groups = l->groups.get(), a.ngroups = l->counters.get() + 1;
+    a.out = l->y.get(), a.out_stride = E;
+    launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), st), "experts down");
+  }
+  mark(l, ST_SHARED, st);
+  if (l->has_shared) {
+    const uint32_t dense_groups = (T + M - 1) / M;
+    ExpertRowsArgs a{};
+    a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.rows_per_cta = 32;
+    a.act = (l->shared_x_same ? l->xq_routed : l->xq_shared).view(0, E);
+    a.dense_rows = T, a.out = l->h.get() + A * F, a.out_stride = F, a.limit = c.swiglu_limit;
+    launched(l, launch_rows(c.shexp_gate_type, 2, a, M, dense_groups, l->grid.get(), st), "shared gate/up");
+    quantize_rows(l, l->h.get() + A * F, T, F, l->hq_shared, 0, st);
+    ExpertRowsArgs b{};
+    b.w0 = l->sd.get(), b.K = F, b.R = E, b.rows_per_cta = 128;
+    b.act = l->hq_shared.view(0, F), b.dense_rows = T, b.out = l->s.get(), b.out_stride = E;
+    launched(l, launch_rows(c.shexp_down_type, 1, b, M, dense_groups, l->grid.get(), st), "shared down");
+  }
+  mark(l, ST_COMBINE, st);
+  k_combine<<<T, 256, 0, st>>>(l->y.get(), l->inv.get(), l->w.get(), l->gs.get(), l->has_shared ? l->s.get() : nullptr, K, E, out);
+  launched(l, cudaGetLastError(), "combine");
+  mark(l, ST_COPIES, st);
+  l->last_T = T;
+  l->stats.calls++, l->stats.rows += T, l->stats.assignments += A;
+}
+
+template <class Fn>
+moe_status guarded(moe_layer *l, Fn &&fn) {
+  try {
+    if (l) CUDA_OK(cudaSetDevice(l->cfg.device));
+    fn();
+    return MOE_OK;
+  } catch (const BadArgument &e) {
+    (l ? l->err : g_create_error) = e.what();
+    return MOE_BAD_ARGUMENT;
+  } catch (const Timeout &e) {
+    (l ? l->err : g_create_error) = e.what();
+    return MOE_TIMEOUT;
+  } catch (const std::exception &e) {
+    (l ? l->err : g_create_error) = e.what();
+    return MOE_ERROR;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+MOE_API moe_status moe_layer_create(const moe_layer_config *config, const moe_layer_weights *weights, moe_layer **out) {
+  if (!config || !weights || !out) {
+    g_create_error = "config, weights and out are required";
+    return MOE_BAD_ARGUMENT;
+  }
+  *out = nullptr;
+  auto l = std::make_unique<moe_layer>();
+  moe_layer *raw = l.get();
+  const moe_status s = guarded(nullptr, [&] { create(raw, *config, *weights); });
+  if (s == MOE_OK) *out = l.release();
+  return s;
+}
+
+MOE_API void moe_layer_destroy(moe_layer *l) {
+  if (!l) return;
+  cudaSetDevice(l->cfg.device);
+  if (l->stream) cudaStreamSynchronize(l->stream->get());
+  delete l;
+}
+
+MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, float *out) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!x || !out || T == 0 || T > l->Tmax) throw BadArgument("x and out are required, and 1 <= T <= max_tokens");
+    cudaStream_t st = l->stream->get();
+    const size_t bytes = (size_t)T * l->E * sizeof(float);
+    CUDA_OK(cudaMemcpyAsync(l->x.get(), x, bytes, cudaMemcpyHostToDevice, st));
+    forward_device(l, l->x.get(), T, l->out.get(), st);
+    CUDA_OK(cudaMemcpyAsync(out, l->out.get(), bytes, cudaMemcpyDeviceToHost, st));
+    if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
+    l->stats.h2d_bytes += bytes, l->stats.d2h_bytes += bytes;
+    l->stream->wait(0);
+  });
+}
+
+MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, uint32_t T, float *out_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!x_dev || !out_dev || T == 0 || T > l->Tmax) throw BadArgument("x and out are required, and 1 <= T <= max_tokens");
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    forward_device(l, x_dev, T, out_dev, st);
+    if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
+  });
+}
+
+MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  return guarded(l, [&] { l->stream->wait(timeout_ms); });
+}
+
+MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, uint32_t *inv, moe_tile *tiles, uint32_t tiles_cap,
+                                        uint32_t *ntiles) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T == 0) throw BadArgument("no call has run yet");
+    cudaStream_t st = l->stream->get();
+    const size_t A = (size_t)l->last_T * l->K;
+    uint32_t counters[4];
+    CUDA_OK(cudaMemcpyAsync(counters, l->counters.get(), sizeof(counters), cudaMemcpyDeviceToHost, st));
+    if (ids) CUDA_OK(cudaMemcpyAsync(ids, l->ids.get(), A * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    if (w) CUDA_OK(cudaMemcpyAsync(w, l->w.get(), A * sizeof(float), cudaMemcpyDeviceToHost, st));
+    if (inv) CUDA_OK(cudaMemcpyAsync(inv, l->inv.get(), A * sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    l->stream->wait(0);
+    if (tiles && tiles_cap) {
+      static_assert(sizeof(moe_tile) == sizeof(MoeTile), "tile layout");
+      const size_t n = std::min<size_t>(tiles_cap, counters[0]);
+      CUDA_OK(cudaMemcpyAsync(tiles, l->tiles.get(), n * sizeof(moe_tile), cudaMemcpyDeviceToHost, st));
+      l->stream->wait(0);
+    }
+    if (ntiles) *ntiles = counters[0];
+    l->stats.last_tiles = counters[0], l->stats.last_experts_hit = counters[2];
+  });
+}
+
+MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out) {
+  if (!l || !out) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T) {
+      uint32_t counters[4];
+      l->stream->wait(0);
+      CUDA_OK(cudaMemcpy(counters, l->counters.get(), sizeof(counters), cudaMemcpyDeviceToHost));
+      l->stats.last_tiles = counters[0], l->stats.last_experts_hit = counters[2];
+    }
+    *out = l->stats;
+  });
+}
+
+MOE_API moe_status moe_layer_stage_ms(moe_layer *l, float *ms) {
+  if (!l || !ms) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!l->profile || !l->ev_valid) throw BadArgument("the layer was not created with MOE_FLAG_PROFILE, or no call has run");
+    CUDA_OK(cudaEventSynchronize(l->ev[MOE_STAGES]->get()));
+    for (int i = 0; i < MOE_STAGES; i++) ms[i] = Event::ms(*l->ev[i], *l->ev[i + 1]);
+  });
+}
+
+MOE_API void *moe_layer_stream(moe_layer *l) { return l ? (void *)l->stream->get() : nullptr; }
+
+MOE_API const char *moe_last_error(const moe_layer *l) { return l ? l->err.c_str() : g_create_error.c_str(); }
+
+MOE_API moe_status moe_to_runs(uint32_t type, const void *file_blocks, uint64_t nblocks, void *dst) {
+  if (!type_known(type) || !file_blocks || !dst) return MOE_BAD_ARGUMENT;
+  to_runs(type, (const uint8_t *)file_blocks, nblocks, (uint8_t *)dst);
+  return MOE_OK;
+}
+
+MOE_API moe_status moe_from_runs(uint32_t type, const void *runs, uint64_t nblocks, void *dst) {
+  if (!type_known(type) || !runs || !dst) return MOE_BAD_ARGUMENT;
+  from_runs(type, (const uint8_t *)runs, nblocks, (uint8_t *)dst);
+  return MOE_OK;
+}
+
+MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap) {
+  static const moe_abi_row rows[] = {
+#define ROW(S, F) {#S "." #F, (uint32_t)offsetof(S, F), (uint32_t)sizeof(((S *)0)->F)}
+      ROW(moe_layer_config, n_embd), ROW(moe_layer_config, n_ff), ROW(moe_layer_config, n_experts), ROW(moe_layer_config, n_used),
+      ROW(moe_layer_config, gate_type), ROW(moe_layer_config, down_type), ROW(moe_layer_config, shexp_gate_type),
+      ROW(moe_layer_config, shexp_down_type), ROW(moe_layer_config, expert_first), ROW(moe_layer_config, expert_count),
+      ROW(moe_layer_config, max_tokens), ROW(moe_layer_config, device), ROW(moe_layer_config, swiglu_limit), ROW(moe_layer_config, flags),
+      ROW(moe_layer_weights, router), ROW(moe_layer_weights, shexp_gate_inp), ROW(moe_layer_weights, router_bias),
+      ROW(moe_layer_weights, gate_exps), ROW(moe_layer_weights, up_exps), ROW(moe_layer_weights, down_exps),
+      ROW(moe_layer_weights, gate_shexp), ROW(moe_layer_weights, up_shexp), ROW(moe_layer_weights, down_shexp),
+      ROW(moe_tile, expert), ROW(moe_tile, slot), ROW(moe_tile, start), ROW(moe_tile, count),
+      ROW(moe_layer_stats, calls), ROW(moe_layer_stats, rows), ROW(moe_layer_stats, assignments), ROW(moe_layer_stats, kernels),
+      ROW(moe_layer_stats, h2d_bytes), ROW(moe_layer_stats, d2h_bytes), ROW(moe_layer_stats, last_tiles),
+      ROW(moe_layer_stats, last_experts_hit), ROW(moe_layer_stats, last_tensor_rows),
+      ROW(moe_abi_row, name), ROW(moe_abi_row, offset), ROW(moe_abi_row, size),
+#undef ROW
+      {"moe_layer_config", 0, (uint32_t)sizeof(moe_layer_config)},
+      {"moe_layer_weights", 0, (uint32_t)sizeof(moe_layer_weights)},
+      {"moe_tile", 0, (uint32_t)sizeof(moe_tile)},
+      {"moe_layer_stats", 0, (uint32_t)sizeof(moe_layer_stats)},
+      {"moe_abi_row", 0, (uint32_t)sizeof(moe_abi_row)},
+  };
+  const uint32_t n = (uint32_t)(sizeof(rows) / sizeof(rows[0]));
+  if (table)
+    for (uint32_t i = 0; i < n && i < cap; i++) table[i] = rows[i];
+  return n;
+}
+
+}  // extern "C"

@@ -1,0 +1,411 @@
+// The block's routing and elementwise stages: activation quantisers, router logits, top-k with renormalised weights,
+// the stable pack into expert order with its tiles and groups, and the weighted combine. They replace the reference's
+// quantize_a8 (kernels/include/a8.h:9-16), the router product (kernels/common.cl:114-158, kernels/gemm.cl:51-115),
+// router / p_router (kernels/models/qwen4exp/layer.cl:765-847, prompt.cl:652-678, route.h:39-98), p_moe_count / scan /
+// fill (prompt.cl:682-738), moe_group (layer.cl:894-978) and moe_combine / p_moe_combine (layer.cl:869-883,
+// prompt.cl:769-786).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "expert_rows.cuh"
+
+namespace moe {
+
+struct MoeTile {
+  uint32_t expert, slot, start, count;
+};
+constexpr uint32_t kTileRows = 64;      // MOE_TILE (shared/moe_tile.h:9)
+constexpr uint32_t kChunkTokens = 32;   // rows one CTA of the top-k kernel routes: a chunk of the pack
+constexpr uint32_t kRouterPieces = 8;   // pieces a router product is summed in
+
+// ---------------------------------------------------------------------------------------------------------------
+// Activation quantisers. One warp per 256 values.
+
+// q8_0: per 32 values d = max|x| / 127, q = round(x * (1 / d)), 0 when d is 0; d kept as the f16 the CPU stores
+// (docs/spec/QUANT_FORMATS.md:463-465, :525-526).
+__global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
+                                                   float *__restrict__ d) {
+  const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
+  if (blk >= nblk256) return;
+  const uint32_t lane = threadIdx.x % 32;
+  const float4 a = ((const float4 *)(x + blk * 256))[2 * lane], b = ((const float4 *)(x + blk * 256))[2 * lane + 1];
+  float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                     fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));  // 4 lanes hold a block of 32
+  const float dd = amax / 127.0f, id = dd != 0.0f ? 1.0f / dd : 0.0f;
+  char4 lo, hi;
+  lo.x = (signed char)roundf(a.x * id), lo.y = (signed char)roundf(a.y * id);
+  lo.z = (signed char)roundf(a.z * id), lo.w = (signed char)roundf(a.w * id);
+  hi.x = (signed char)roundf(b.x * id), hi.y = (signed char)roundf(b.y * id);
+  hi.z = (signed char)roundf(b.z * id), hi.w = (signed char)roundf(b.w * id);
+  ((char4 *)(q + blk * 256))[2 * lane] = lo;
+  ((char4 *)(q + blk * 256))[2 * lane + 1] = hi;
+  if (lane % 4 == 0) d[blk * 8 + lane / 4] = __half2float(__float2half_rn(dd));
+}
+
+// q8_K: per 256 values iscale = -127 / max with max the value of largest magnitude (the first of equals),
+// q = min(127, nearest-even(iscale * x)), d = 1 / iscale, and the sums of each 16 codes (QUANT_FORMATS.md:528-535).
+__global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
+                                                   float *__restrict__ d, int16_t *__restrict__ bs) {
+  const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
+  if (blk >= nblk256) return;
+  const uint32_t lane = threadIdx.x % 32;
+  const float4 a = ((const float4 *)(x + blk * 256))[2 * lane], b = ((const float4 *)(x + blk * 256))[2 * lane + 1];
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  float amax = 0.0f, mx = 0.0f;
+  uint32_t at = 8 * lane;
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+    if (fabsf(v[i]) > amax) amax = fabsf(v[i]), mx = v[i], at = 8 * lane + i;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float oa = __shfl_xor_sync(0xffffffffu, amax, off), om = __shfl_xor_sync(0xffffffffu, mx, off);
+    const uint32_t oat = __shfl_xor_sync(0xffffffffu, at, off);
+    if (oa > amax || (oa == amax && oat < at)) amax = oa, mx = om, at = oat;
+  }
+  if (amax == 0.0f) {
+    ((char4 *)(q + blk * 256))[2 * lane] = make_char4(0, 0, 0, 0);
+    ((char4 *)(q + blk * 256))[2 * lane + 1] = make_char4(0, 0, 0, 0);
+    if (lane == 0) d[blk] = 0.0f;
+    if (lane % 2 == 0) bs[blk * 16 + lane / 2] = 0;
+    return;
+  }
+  const float iscale = -127.0f / mx;
+  int c[8], sum = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) c[i] = min(127, __float2int_rn(__fmul_rn(iscale, v[i]))), sum += c[i];
+  ((char4 *)(q + blk * 256))[2 * lane] = make_char4((signed char)c[0], (signed char)c[1], (signed char)c[2], (signed char)c[3]);
+  ((char4 *)(q + blk * 256))[2 * lane + 1] = make_char4((signed char)c[4], (signed char)c[5], (signed char)c[6], (signed char)c[7]);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  if (lane % 2 == 0) bs[blk * 16 + lane / 2] = (int16_t)sum;
+  if (lane == 0) d[blk] = 1.0f / iscale;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Router logits: rl[t][e] = W[e] . x[t] for the NE experts and, as row NE, the shared expert's gate vector. Every
+// product is summed in kRouterPieces equal pieces of the row, each a chain of fused multiply-adds from 0 in index
+// order, the pieces then added in order, and an expert's bias last. Both kernels and the CPU oracle keep this one
+// order, so that the logits, and with them the chosen experts, agree bit for bit whatever the row count.
+
+// Few rows (up to 8 per CTA pass): 4 weight rows per warp, 8 lanes a row, lane s taking piece s.
+template <int TM>
+__global__ void __launch_bounds__(128) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
+                                                           const float *__restrict__ W, uint32_t N,
+                                                           const float *__restrict__ bias, uint32_t NE,
+                                                           float *__restrict__ rl) {
+  extern __shared__ __align__(16) float xs[];  // TM rows, each piece padded by 4 floats to spread the banks
+  const uint32_t piece = E / kRouterPieces, pstride = piece + 4, rstride = kRouterPieces * pstride;
+  const uint32_t t0 = blockIdx.y * TM, tn = min((uint32_t)TM, T - t0);
+  for (uint32_t i = threadIdx.x; i < TM * (E / 4); i += 128) {
+    const uint32_t t = i / (E / 4), k4 = i % (E / 4), k = 4 * k4;
+    const float4 v = t < tn ? ((const float4 *)(x + (uint64_t)(t0 + t) * E))[k4] : make_float4(0, 0, 0, 0);
+    *(float4 *)(xs + t * rstride + (k / piece) * pstride + k % piece) = v;
+  }
+  __syncthreads();
+  const uint32_t lane = threadIdx.x % 32, s = lane % 8;
+  const uint32_t row = (blockIdx.x * 4 + threadIdx.x / 32) * 4 + lane / 8;
+  float p[TM];
+#pragma unroll
+  for (int t = 0; t < TM; t++) p[t] = 0.0f;
+  if (row < N) {
+    const float4 *w = (const float4 *)(W + (uint64_t)row * E + s * piece);
+    const float *xp = xs + s * pstride;
+#pragma unroll 8
+    for (uint32_t i = 0; i < piece / 4; i++) {
+      const float4 wv = __ldg(w + i);
+#pragma unroll
+      for (int t = 0; t < TM; t++) {
+        const float4 xv = *(const float4 *)(xp + t * rstride + 4 * i);
+        p[t] = fmaf(xv.x, wv.x, p[t]);
+        p[t] = fmaf(xv.y, wv.y, p[t]);
+        p[t] = fmaf(xv.z, wv.z, p[t]);
+        p[t] = fmaf(xv.w, wv.w, p[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < TM; t++) {
+    float tot = __shfl_sync(0xffffffffu, p[t], lane & ~7u);
+#pragma unroll
+    for (int j = 1; j < (int)kRouterPieces; j++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, p[t], (lane & ~7u) + j));
+    if (s == 0 && row < N && (uint32_t)t < tn) {
+      if (bias && row < NE) tot = __fadd_rn(tot, bias[row]);
+      rl[(uint64_t)(t0 + t) * N + row] = tot;
+    }
+  }
+}
+
+// Many rows: a 128 x 64 tile of (rows, experts) per CTA of 256 threads, 8 x 4 outputs a thread, 16 values of the
+// hidden size a step; the tile's partial sums fold into the totals at every piece's end.
+__global__ void __launch_bounds__(256) k_router_logits_tiles(const float *__restrict__ x, uint32_t T, uint32_t E,
+                                                            const float *__restrict__ W, uint32_t N,
+                                                            const float *__restrict__ bias, uint32_t NE,
+                                                            float *__restrict__ rl) {
+  constexpr int BM = 128, BN = 64, BK = 16;
+  __shared__ __align__(16) float As[2][BK][BM + 4], Bs[2][BK][BN + 4];
+  const uint32_t tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, piece = E / kRouterPieces;
+  float p[8][4], tot[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) p[i][j] = 0.0f, tot[i][j] = 0.0f;
+  // A thread's loads: two float4 of x (rows am, am + 64; values 4 * aq ..), one of W (row bn; values 4 * bq ..).
+  const uint32_t am = tid / 4, aq = tid % 4, bn = tid / 4, bq = tid % 4;
+  float4 ra0, ra1, rb;
+  auto fetch = [&](uint32_t k0) {
+    const uint32_t r0 = m0 + am, r1 = m0 + am + 64, e = n0 + bn;
+    ra0 = r0 < T ? *(const float4 *)(x + (uint64_t)r0 * E + k0 + 4 * aq) : make_float4(0, 0, 0, 0);
+    ra1 = r1 < T ? *(const float4 *)(x + (uint64_t)r1 * E + k0 + 4 * aq) : make_float4(0, 0, 0, 0);
+    rb = e < N ? __ldg((const float4 *)(W + (uint64_t)e * E + k0 + 4 * bq)) : make_float4(0, 0, 0, 0);
+  };
+  auto stash = [&](int buf) {
+    As[buf][4 * aq + 0][am] = ra0.x, As[buf][4 * aq + 1][am] = ra0.y, As[buf][4 * aq + 2][am] = ra0.z, As[buf][4 * aq + 3][am] = ra0.w;
+    As[buf][4 * aq + 0][am + 64] = ra1.x, As[buf][4 * aq + 1][am + 64] = ra1.y, As[buf][4 * aq + 2][am + 64] = ra1.z,
+                      As[buf][4 * aq + 3][am + 64] = ra1.w;
+    Bs[buf][4 * bq + 0][bn] = rb.x, Bs[buf][4 * bq + 1][bn] = rb.y, Bs[buf][4 * bq + 2][bn] = rb.z, Bs[buf][4 * bq + 3][bn] = rb.w;
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  const uint32_t steps = E / BK;
+  for (uint32_t s = 0; s < steps; s++) {
+    const int buf = s & 1;
+    if (s + 1 < steps) fetch((s + 1) * BK);
+#pragma unroll
+    for (int k = 0; k < BK; k++) {
+      const float4 a0 = *(const float4 *)&As[buf][k][ty * 8], a1 = *(const float4 *)&As[buf][k][ty * 8 + 4];
+      const float4 b = *(const float4 *)&Bs[buf][k][tx * 4];
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) p[i][j] = fmaf(av[i], bv[j], p[i][j]);
+    }
+    if (s + 1 < steps) stash(buf ^ 1);
+    __syncthreads();
+    if (((s + 1) * BK) % piece == 0) {
+      const bool first = (s + 1) * BK == piece;
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          tot[i][j] = first ? p[i][j] : __fadd_rn(tot[i][j], p[i][j]);
+          p[i][j] = 0.0f;
+        }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const uint32_t t = m0 + ty * 8 + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const uint32_t e = n0 + tx * 4 + j;
+      if (e >= N) continue;
+      float v = tot[i][j];
+      if (bias && e < NE) v = __fadd_rn(v, bias[e]);
+      rl[(uint64_t)t * N + e] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Top-k. One warp per row, lane holding experts lane + 32 j. Keys order the logits as floats do (the reference's
+// topk_key, kernels/include/topk.h:12-15), -0 taken as +0; winners come out largest first, ties to the lower expert
+// (route.h:33-38). Weights: p_k = exp(v_k - max) / sum, w_k = p_k / max(sum of the K p's, 6.1035e-5)
+// (layer.cl:784-787). The CTA's rows are one chunk of the pack: it leaves the chunk's count of every expert.
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t u = __float_as_uint(v + 0.0f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+constexpr int kMaxPerLane = 16;  // experts a lane holds at most: 512 / 32
+
+__global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, uint32_t T, uint32_t NE,
+                                                                  uint32_t K, int32_t *__restrict__ ids,
+                                                                  float *__restrict__ w, float *__restrict__ gs,
+                                                                  uint32_t *__restrict__ chunk_hist) {
+  __shared__ uint32_t hist[512];
+  for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  const uint32_t lane = threadIdx.x % 32, t = blockIdx.x * kChunkTokens + threadIdx.x / 32, per = NE / 32;
+  if (t < T) {
+    const float *v = rl + (uint64_t)t * (NE + 1);
+    uint32_t key[kMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; j++) {
+      key[j] = 0;
+      if ((uint32_t)j < per) {
+        const float f = v[lane + 32 * j];
+        key[j] = order_key(f);
+        mx = fmaxf(mx, f);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; j++)
+      if ((uint32_t)j < per) sum += expf(key_value(key[j]) - mx);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    // K rounds of arg-max over (key, lower expert first).
+    float pk = 0.0f;
+    uint32_t my_id = 0;
+    for (uint32_t k = 0; k < K; k++) {
+      unsigned long long best = 0;
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; j++) {
+        const unsigned long long c = ((unsigned long long)key[j] << 32) | (uint32_t)~(lane + 32 * j);
+        if ((uint32_t)j < per && c > best) best = c;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
+        if (o > best) best = o;
+      }
+      const uint32_t e = ~(uint32_t)best, bkey = (uint32_t)(best >> 32);
+      if (e % 32 == lane) {
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; j++)
+          if ((uint32_t)j == e / 32) key[j] = 0;
+      }
+      if (lane == k) {
+        my_id = e;
+        pk = expf(key_value(bkey) - mx) / sum;
+      }
+    }
+    float tot = 0.0f;
+    for (uint32_t k = 0; k < K; k++) tot += __shfl_sync(0xffffffffu, pk, k);
+    if (lane < K) {
+      ids[(uint64_t)t * K + lane] = (int32_t)my_id;
+      w[(uint64_t)t * K + lane] = pk / fmaxf(tot, 6.1035e-5f);
+      atomicAdd(&hist[my_id], 1u);
+    }
+    if (lane == 0) gs[t] = 1.0f / (1.0f + expf(-v[NE]));
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
+}
+
+// The same counts for expert ids that come from elsewhere (the rows another GPU sent): chunk c holds entries
+// [c * chunk_len, (c + 1) * chunk_len) of ids.
+__global__ void __launch_bounds__(256) k_chunk_hist(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len,
+                                                   uint32_t NE, uint32_t *__restrict__ chunk_hist) {
+  __shared__ uint32_t hist[512];
+  for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  const uint32_t a0 = blockIdx.x * chunk_len, a1 = min(A, a0 + chunk_len);
+  for (uint32_t a = a0 + threadIdx.x; a < a1; a += blockDim.x) atomicAdd(&hist[ids[a]], 1u);
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Pack. Assignments a = t * K + k go into expert order by a stable counting sort: experts ascending, and inside an
+// expert's run ascending a. The reference's fill takes rows by atomic increments, so its order inside a run depends on
+// scheduling (prompt.cl:730-737); this one has no atomics on the order and gives the same permutation every time.
+
+struct PackOut {
+  uint32_t *cnt, *base;    // NE each
+  uint32_t *chunk_off;     // [chunks][NE]: rows of the expert's run taken by earlier chunks
+  MoeTile *tiles;          // expert order, <= 64 rows each (prompt.cl:719-723)
+  MoeGroup *groups;        // <= 8 rows each
+  uint32_t *counters;      // [0] tiles, [1] groups, [2] experts hit, [3] rows
+};
+
+// One CTA of 512 threads, thread e for expert e: sums the chunks' counts, scans them over the experts, writes tiles
+// and groups. first_expert: the id of slot 0.
+__global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
+                                                  uint32_t first_expert, PackOut o) {
+  __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512];
+  const uint32_t e = threadIdx.x;
+  uint32_t run = 0;
+  if (e < NE) {
+#pragma unroll 4
+    for (uint32_t c = 0; c < nchunks; c++) {
+      const uint32_t v = chunk_hist[(uint64_t)c * NE + e];
+      o.chunk_off[(uint64_t)c * NE + e] = run;
+      run += v;
+    }
+  }
+  const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = (n + kGroupMax - 1) / kGroupMax;
+  s_rows[e] = n, s_tiles[e] = nt, s_groups[e] = ng, s_hit[e] = n > 0;
+  __syncthreads();
+  for (uint32_t off = 1; off < 512; off <<= 1) {
+    const uint32_t a = e >= off ? s_rows[e - off] : 0, b = e >= off ? s_tiles[e - off] : 0;
+    const uint32_t c = e >= off ? s_groups[e - off] : 0, d = e >= off ? s_hit[e - off] : 0;
+    __syncthreads();
+    s_rows[e] += a, s_tiles[e] += b, s_groups[e] += c, s_hit[e] += d;
+    __syncthreads();
+  }
+  if (e < NE) {
+    const uint32_t first = s_rows[e] - n;
+    o.cnt[e] = n;
+    o.base[e] = first;
+    const uint32_t tile0 = s_tiles[e] - nt, group0 = s_groups[e] - ng;
+    for (uint32_t i = 0; i < nt; i++)
+      o.tiles[tile0 + i] = MoeTile{first_expert + e, e, first + i * kTileRows, min(kTileRows, n - i * kTileRows)};
+    for (uint32_t i = 0; i < ng; i++)
+      o.groups[group0 + i] = MoeGroup{e, first + i * kGroupMax, min((uint32_t)kGroupMax, n - i * kGroupMax)};
+  }
+  if (e == 511) o.counters[0] = s_tiles[e], o.counters[1] = s_groups[e], o.counters[2] = s_hit[e], o.counters[3] = s_rows[e];
+}
+
+// One CTA per chunk, thread e for expert e: walks the chunk's ids in order and hands out its expert's rows in that
+// order. inv[a] = row; row_src[row] = a / src_div (the activation row the assignment reads: its token).
+__global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len, uint32_t NE,
+                                                  const uint32_t *__restrict__ base, const uint32_t *__restrict__ chunk_off,
+                                                  uint32_t src_div, uint32_t *__restrict__ inv, uint32_t *__restrict__ row_src) {
+  extern __shared__ int32_t s_ids[];
+  const uint32_t a0 = blockIdx.x * chunk_len, n = min(A, a0 + chunk_len) - a0;
+  for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) s_ids[i] = ids[a0 + i];
+  __syncthreads();
+  const uint32_t e = threadIdx.x;
+  if (e >= NE) return;
+  uint32_t row = base[e] + chunk_off[(uint64_t)blockIdx.x * NE + e];
+  for (uint32_t i = 0; i < n; i++)
+    if ((uint32_t)s_ids[i] == e) {
+      inv[a0 + i] = row;
+      row_src[row] = (a0 + i) / src_div;
+      row++;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Combine: out[t] = sum over k, in rank order, of w[t][k] * y[inv[t K + k]] + gs[t] * s[t], in f32 (layer.cl:874-877).
+// One CTA per row.
+__global__ void __launch_bounds__(256) k_combine(const float *__restrict__ y, const uint32_t *__restrict__ inv,
+                                                const float *__restrict__ w, const float *__restrict__ gs,
+                                                const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out) {
+  const uint32_t t = blockIdx.x;
+  __shared__ uint32_t rows[16];
+  __shared__ float wk[16];
+  if (threadIdx.x < K) rows[threadIdx.x] = inv[(uint64_t)t * K + threadIdx.x], wk[threadIdx.x] = w[(uint64_t)t * K + threadIdx.x];
+  __syncthreads();
+  const float g = s ? gs[t] : 0.0f;
+  for (uint32_t i = threadIdx.x; i < E / 4; i += 256) {
+    float4 acc = make_float4(0, 0, 0, 0);
+    for (uint32_t k = 0; k < K; k++) {
+      const float4 v = ((const float4 *)(y + (uint64_t)rows[k] * E))[i];
+      acc.x = fmaf(wk[k], v.x, acc.x), acc.y = fmaf(wk[k], v.y, acc.y);
+      acc.z = fmaf(wk[k], v.z, acc.z), acc.w = fmaf(wk[k], v.w, acc.w);
+    }
+    if (s) {
+      const float4 v = ((const float4 *)(s + (uint64_t)t * E))[i];
+      acc.x = fmaf(g, v.x, acc.x), acc.y = fmaf(g, v.y, acc.y), acc.z = fmaf(g, v.z, acc.z), acc.w = fmaf(g, v.w, acc.w);
+    }
+    ((float4 *)(out + (uint64_t)t * E))[i] = acc;
+  }
+}
+
+}  // namespace moe

@@ -1,0 +1,117 @@
+"""The host side of the MoE layer: the calls the reference's model program makes for a layer's MoE block
+(core/models/qwen4exp/model.cpp:1348-1418, prompt.cpp:606-656) and its CPU path's interface
+(CpuExperts::compute_many, core/cpu/experts.h:32-53), over the C ABI of include/moe_layer.h."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+
+
+class MoEError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"status {status}: {message}")
+        self.status = status
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class MoELayer:
+    """One layer's router, experts and shared expert on one GPU.
+
+    layer: a dict with n_embd, n_ff, n_experts, n_used, the four types, router [NE][E] f32, shexp_gate_inp [E] f32,
+    optional router_bias [NE] f32, and the experts' matrices as uint8 arrays in the GGUF file's block layout
+    (gate_exps, up_exps [NE][F][row bytes], down_exps [NE][E][row bytes], gate_shexp, up_shexp, down_shexp) — what
+    c0ven_b200.synth.make_layer returns.
+    """
+
+    def __init__(self, layer: dict, max_tokens: int = 4352, device: int = 0, profile: bool = False,
+                 expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False):
+        self._h = None
+        L = _lib.lib()
+        self.n_embd, self.n_ff = layer["n_embd"], layer["n_ff"]
+        self.n_experts, self.n_used = layer["n_experts"], layer["n_used"]
+        self.max_tokens = max_tokens
+        count = expert_count or self.n_experts - expert_first
+        has_shared = layer.get("gate_shexp") is not None
+        cfg = _lib.Config(self.n_embd, self.n_ff, self.n_experts, self.n_used, layer["gate_type"], layer["down_type"],
+                          layer["shexp_gate_type"] if has_shared else 0, layer["shexp_down_type"] if has_shared else 0,
+                          expert_first, count, max_tokens, device, float(layer.get("swiglu_limit", 0.0)),
+                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0))
+        sl = slice(expert_first, expert_first + count)
+        keep = [np.ascontiguousarray(layer["router"], dtype=np.float32),
+                np.ascontiguousarray(layer["shexp_gate_inp"], dtype=np.float32) if has_shared else None,
+                np.ascontiguousarray(layer["router_bias"], dtype=np.float32) if layer.get("router_bias") is not None else None,
+                np.ascontiguousarray(layer["gate_exps"][sl]), np.ascontiguousarray(layer["up_exps"][sl]),
+                np.ascontiguousarray(layer["down_exps"][sl]),
+                np.ascontiguousarray(layer["gate_shexp"]) if has_shared else None,
+                np.ascontiguousarray(layer["up_shexp"]) if has_shared else None,
+                np.ascontiguousarray(layer["down_shexp"]) if has_shared else None]
+        w = _lib.Weights(*[a.ctypes.data if a is not None else None for a in keep])
+        h = C.c_void_p()
+        st = L.moe_layer_create(C.byref(cfg), C.byref(w), C.byref(h))
+        if st != _lib.MOE_OK:
+            raise MoEError(st, L.moe_last_error(None).decode())
+        self._h = h
+
+    def _check(self, st: int):
+        if st != _lib.MOE_OK:
+            raise MoEError(st, _lib.lib().moe_last_error(self._h).decode())
+
+    def close(self):
+        if self._h is not None:
+            _lib.lib().moe_layer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward(self, x: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
+        """The block on host rows x [T][E] f32; copies in, computes, copies out, waits."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.ndim != 2 or x.shape[1] != self.n_embd:
+            raise ValueError("x must be [T][n_embd]")
+        if out is None:
+            out = np.empty_like(x)
+        self._check(_lib.lib().moe_layer_forward(self._h, _ptr(x), x.shape[0], _ptr(out)))
+        return out
+
+    def forward_device(self, x_ptr: int, T: int, out_ptr: int, stream: int | None = None):
+        """The block on device buffers (addresses), queued without waiting."""
+        self._check(_lib.lib().moe_layer_forward_device(self._h, x_ptr, T, out_ptr, stream))
+
+    def sync(self, timeout_ms: int = 0):
+        self._check(_lib.lib().moe_layer_sync(self._h, timeout_ms))
+
+    def route(self, T: int):
+        """The last call's ids [T][K], w [T][K], inv [T*K] and tiles [n][4] (expert, slot, start, count)."""
+        K = self.n_used
+        ids = np.empty((T, K), dtype=np.int32)
+        w = np.empty((T, K), dtype=np.float32)
+        inv = np.empty(T * K, dtype=np.uint32)
+        cap = T * K // 64 + self.n_experts + 1
+        tiles = np.empty((cap, 4), dtype=np.uint32)
+        n = C.c_uint32(0)
+        self._check(_lib.lib().moe_layer_read_route(self._h, _ptr(ids), _ptr(w), _ptr(inv), _ptr(tiles), cap, C.byref(n)))
+        return ids, w, inv, tiles[:n.value].copy()
+
+    def stats(self) -> dict:
+        s = _lib.Stats()
+        self._check(_lib.lib().moe_layer_read_stats(self._h, C.byref(s)))
+        return {n: getattr(s, n) for n, _ in _lib.Stats._fields_}
+
+    def stage_ms(self) -> dict:
+        ms = np.zeros(len(_lib.STAGES), dtype=np.float32)
+        self._check(_lib.lib().moe_layer_stage_ms(self._h, _ptr(ms)))
+        return dict(zip(_lib.STAGES, ms.tolist()))
+
+    @property
+    def stream(self) -> int:
+        return _lib.lib().moe_layer_stream(self._h)

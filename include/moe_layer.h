@@ -1,0 +1,155 @@
+/* The MoE expert layer's C ABI: router, pack, quantised expert FFN, shared expert and combine on one B200.
+ *
+ * The reference's own ABI (include/engine_api.h:308-421) is whole-engine: open, admit, submit, poll. Its MoE block
+ * has no entry point of its own; it runs inside Model::step (core/models/qwen4exp/model.cpp:1348-1418) and
+ * Model::prompt_runs (core/models/qwen4exp/prompt.cpp:606-656), with the CPU's share behind CpuExperts::compute_many
+ * (core/cpu/experts.h:32-53). This header is the layer-level boundary those call sites would bind, written to the
+ * same rules as engine_api.h:1-10: plain structs and buffers only, every call returns a status, no exception and no
+ * callback crosses, the library owns all device memory and streams. Weights come in the GGUF block formats of
+ * shared/quant.h:36-169 in the file's layout; results are the ones the reference's kernels leave in ids, w, inv and
+ * tiles (shared/moe_tile.h:9-18) and the block's output rows. */
+#ifndef MOE_LAYER_H
+#define MOE_LAYER_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(MOE_API_EXPORT)
+#define MOE_API __attribute__((visibility("default")))
+#else
+#define MOE_API
+#endif
+
+#define MOE_API_VERSION 1
+
+/* engine_status's values (include/engine_api.h:28-34). */
+typedef enum {
+  MOE_OK = 0,
+  MOE_ERROR = 1, /* see moe_last_error */
+  MOE_BAD_ARGUMENT = 2,
+  MOE_BUSY = 3,
+  MOE_TIMEOUT = 4
+} moe_status;
+
+/* Weight types, ggml's numbers (shared/quant.h:10-33). */
+#define MOE_TYPE_Q8_0 8
+#define MOE_TYPE_Q4_K 12
+#define MOE_TYPE_Q6_K 14
+#define MOE_TYPE_IQ3_S 21
+
+typedef struct moe_layer moe_layer;
+
+/* The shape CpuExperts takes as ExpertShape (core/cpu/experts.h:23-30), with the router's sizes and where the layer
+ * lives. Zero means the default given. */
+typedef struct {
+  uint32_t n_embd;            /* hidden size, a multiple of 256 */
+  uint32_t n_ff;              /* an expert's inner size, a multiple of 256 */
+  uint32_t n_experts;         /* routed experts, a multiple of 32, at most 512 */
+  uint32_t n_used;            /* experts per row, at most 16 */
+  uint32_t gate_type;         /* the routed experts' gate and up */
+  uint32_t down_type;         /* the routed experts' down */
+  uint32_t shexp_gate_type;   /* the shared expert's gate and up; 0: no shared expert */
+  uint32_t shexp_down_type;
+  uint32_t expert_first;      /* expert parallel: this GPU holds experts [expert_first, expert_first + expert_count) */
+  uint32_t expert_count;      /* 0: all of them */
+  uint32_t max_tokens;        /* rows a call may bring; default 4352, the reference's prompt chunk */
+  int32_t device;             /* CUDA device ordinal */
+  float swiglu_limit;         /* ExpertShape::swiglu_limit; 0: off */
+  uint32_t flags;             /* MOE_FLAG_* */
+} moe_layer_config;
+
+#define MOE_FLAG_PROFILE 1u     /* time every stage of a call with events (moe_layer_stage_ms) */
+#define MOE_FLAG_NO_TENSOR 2u   /* every expert product by the integer-dot kernels, whatever its rows */
+
+/* Host pointers, read during moe_layer_create and not kept. Experts are the file's tensors
+ * blk.N.ffn_{gate,up,down}_exps.weight cut to this GPU's experts: expert e's slice at e * its bytes, rows of whole
+ * blocks (docs/spec/MODEL_LAYER.md 4.1). */
+typedef struct {
+  const float *router;          /* ffn_gate_inp, [n_experts][n_embd] f32 */
+  const float *shexp_gate_inp;  /* ffn_gate_inp_shexp, [n_embd] f32; null with no shared expert */
+  const float *router_bias;     /* [n_experts] f32 added to the logits, or null */
+  const void *gate_exps;        /* [expert_count][n_ff][n_embd values] */
+  const void *up_exps;
+  const void *down_exps;        /* [expert_count][n_embd][n_ff values] */
+  const void *gate_shexp;       /* [n_ff][n_embd values] */
+  const void *up_shexp;
+  const void *down_shexp;       /* [n_embd][n_ff values] */
+} moe_layer_weights;
+
+/* MoeTile (shared/moe_tile.h:11-16). slot is the expert's index among this GPU's experts. */
+typedef struct {
+  uint32_t expert;
+  uint32_t slot;
+  uint32_t start;
+  uint32_t count; /* 1 .. 64 */
+} moe_tile;
+
+/* Counters since create, read by snapshot as engine_stats is (include/engine_api.h:225-306). */
+typedef struct {
+  uint64_t calls;             /* forwards run */
+  uint64_t rows;              /* rows in them */
+  uint64_t assignments;       /* rows x n_used */
+  uint64_t kernels;           /* kernels this library launched */
+  uint64_t h2d_bytes;         /* copied for host-buffer calls */
+  uint64_t d2h_bytes;
+  uint64_t last_tiles;        /* of the last call */
+  uint64_t last_experts_hit;  /* distinct experts the last call's rows routed to */
+  uint64_t last_tensor_rows;  /* of its assignments, those the tensor-core kernels computed */
+} moe_layer_stats;
+
+#define MOE_STAGES 8
+/* Stage names, in order: "quantize", "router", "pack", "gate_up", "down", "shared", "combine", "copies". */
+
+/* Uploads the weights in the layout the kernels read and allocates every buffer a call needs. */
+MOE_API moe_status moe_layer_create(const moe_layer_config *config, const moe_layer_weights *weights, moe_layer **out);
+MOE_API void moe_layer_destroy(moe_layer *l);
+
+/* The block on T rows: out[t] = sum over k of w[t][k] * expert ids[t][k] (x[t]) + sigmoid(gate . x[t]) * shared(x[t]).
+ * x and out are HOST buffers of T * n_embd floats; the call copies them to and from the GPU and returns when out is
+ * written. */
+MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, float *out);
+
+/* The same on DEVICE buffers, queued on the layer's stream (or on stream, a cudaStream_t, when not null); returns
+ * without waiting. */
+MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, uint32_t T, float *out_dev, void *stream);
+
+/* Waits for the layer's stream. MOE_TIMEOUT after timeout_ms (0: 60 s), never an unbounded wait. */
+MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms);
+
+/* The last call's routing, copied to host buffers (any may be null): ids and w, T * n_used each, in rank order; inv,
+ * the row each assignment t * n_used + k took in expert order; tiles, up to tiles_cap of them; *ntiles, how many
+ * there are. Waits for the stream. */
+MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, uint32_t *inv, moe_tile *tiles,
+                                        uint32_t tiles_cap, uint32_t *ntiles);
+
+MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out);
+/* With MOE_FLAG_PROFILE: the last call's time in each stage, milliseconds, MOE_STAGES floats. Waits for the stream. */
+MOE_API moe_status moe_layer_stage_ms(moe_layer *l, float *ms);
+/* The layer's cudaStream_t. */
+MOE_API void *moe_layer_stream(moe_layer *l);
+
+/* The last error's message, valid until the next call on l (or, for create's failures, with l null). */
+MOE_API const char *moe_last_error(const moe_layer *l);
+
+/* The layout the GPU holds a slice of nblocks blocks in: one run per field of the block, quants first, as the
+ * reference's to_runs and from_runs make it (core/load/runs.cpp:12-41; shared/quant.h:172-176). Host only: a
+ * permutation of the slice's bytes, src and dst nblocks * block bytes each. */
+MOE_API moe_status moe_to_runs(uint32_t type, const void *file_blocks, uint64_t nblocks, void *dst);
+MOE_API moe_status moe_from_runs(uint32_t type, const void *runs, uint64_t nblocks, void *dst);
+
+/* For the ABI test, as engine_abi_layout (include/engine_api.h:414-421): one row per field, "struct.field" with its
+ * offset and size, then one row per struct. Returns the number of rows; table may be null. */
+typedef struct {
+  const char *name;
+  uint32_t offset;
+  uint32_t size;
+} moe_abi_row;
+MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
