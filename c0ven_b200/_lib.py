@@ -21,7 +21,8 @@ class Config(C.Structure):
     _fields_ = [("n_embd", C.c_uint32), ("n_ff", C.c_uint32), ("n_experts", C.c_uint32), ("n_used", C.c_uint32),
                 ("gate_type", C.c_uint32), ("down_type", C.c_uint32), ("shexp_gate_type", C.c_uint32),
                 ("shexp_down_type", C.c_uint32), ("expert_first", C.c_uint32), ("expert_count", C.c_uint32),
-                ("max_tokens", C.c_uint32), ("device", C.c_int32), ("swiglu_limit", C.c_float), ("flags", C.c_uint32)]
+                ("max_tokens", C.c_uint32), ("device", C.c_int32), ("swiglu_limit", C.c_float), ("flags", C.c_uint32),
+                ("tensor_min_rows", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class Weights(C.Structure):

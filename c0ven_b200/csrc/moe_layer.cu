@@ -13,6 +13,7 @@
 
 #include "cuda_rt.h"
 #include "expert_rows.cuh"
+#include "expert_tiles.cuh"
 #include "formats.h"
 #include "iq3s_grid.h"
 #include "moe_layer.h"
@@ -38,17 +39,36 @@ static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, i
 #undef ROWS_CASE
 }
 
+template <int QT, int NMAT>
+cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, uint32_t max_tiles, const uint32_t *grid_global, cudaStream_t st);
+
+static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a, uint32_t max_tiles, const uint32_t *grid, cudaStream_t st) {
+#define TILES_CASE(T)                                                                                  \
+  case T:                                                                                              \
+    return nmat == 2 ? launch_expert_tiles<T, 2>(a, max_tiles, grid, st) : launch_expert_tiles<T, 1>(a, max_tiles, grid, st);
+  switch (qt) {
+    TILES_CASE(QT_Q8_0)
+    TILES_CASE(QT_Q4_K)
+    TILES_CASE(QT_Q6_K)
+    TILES_CASE(QT_IQ3_S)
+    default: return cudaErrorInvalidValue;
+  }
+#undef TILES_CASE
+}
+
 // Quantised activation rows on the device, in the format a weight type's dot takes.
 struct ActBuffers {
   DeviceBuffer<int8_t> q;
   DeviceBuffer<float> d;
   DeviceBuffer<int16_t> bs;
+  DeviceBuffer<__half> h;  // the codes dequantised, f16: the tensor-core kernels' operand
   bool q8k = false;
-  void alloc(uint64_t rows, uint32_t K, bool k) {
+  void alloc(uint64_t rows, uint32_t K, bool k, bool with_f16) {
     q8k = k;
     q.alloc(rows * K);
     d.alloc(rows * (k ? K / 256 : K / 32));
     if (k) bs.alloc(rows * (K / 16));
+    if (with_f16) h.alloc(rows * K);
   }
   ActView view(uint64_t row0, uint32_t K) const {
     return ActView{q.get() + row0 * K, d.get() + row0 * (q8k ? K / 256 : K / 32), q8k ? bs.get() + row0 * (K / 16) : nullptr};
@@ -74,11 +94,13 @@ struct moe_layer {
   // A call's buffers.
   DeviceBuffer<float> x, out, rl, w, gs, h, y, s;
   DeviceBuffer<int32_t> ids;
-  DeviceBuffer<uint32_t> chunk_hist, chunk_off, cnt, base, counters, inv, row_src;
+  DeviceBuffer<uint32_t> chunk_hist, chunk_off, cnt, base, counters, inv, row_src, error;
   DeviceBuffer<MoeTile> tiles;
   DeviceBuffer<MoeGroup> groups;
+  DeviceBuffer<BigTile> big;
+  uint32_t tensor_min = 0;  // rows from which an expert goes to the tensor-core kernels; 0: never
   ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
-  bool shared_x_same = true, rows_attr_set = false;
+  bool shared_x_same = true, rows_attr_set = false, shared_on_tensor = false;
   uint32_t last_T = 0;
   // Profiling: one event before each stage and one after the last.
   std::vector<std::unique_ptr<Event>> ev;
@@ -138,6 +160,8 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->Tmax = c.max_tokens ? c.max_tokens : 4352;
   l->has_shared = c.shexp_gate_type != 0;
   l->profile = c.flags & MOE_FLAG_PROFILE;
+  l->tensor_min = (c.flags & MOE_FLAG_NO_TENSOR) ? 0 : (c.tensor_min_rows ? c.tensor_min_rows : 16);
+  if (l->tensor_min && (c.n_embd % kTileK || c.n_ff % kTileM)) l->tensor_min = 0;
   l->stream = std::make_unique<Stream>();
   cudaStream_t st = l->stream->get();
   const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, T = l->Tmax;
@@ -172,18 +196,20 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->x.alloc((size_t)T * E), l->out.alloc((size_t)T * E);
   l->rl.alloc((size_t)T * l->N), l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T);
   l->chunk_hist.alloc((size_t)nchunks * NE), l->chunk_off.alloc((size_t)nchunks * NE);
-  l->cnt.alloc(NE), l->base.alloc(NE), l->counters.alloc(4), l->inv.alloc(A), l->row_src.alloc(A);
-  l->tiles.alloc(A / kTileRows + NE), l->groups.alloc(A / kGroupMax + NE);
+  l->cnt.alloc(NE), l->base.alloc(NE), l->counters.alloc(8), l->inv.alloc(A), l->row_src.alloc(A), l->error.alloc(1);
+  l->tiles.alloc(A / kTileRows + NE), l->groups.alloc(A / kGroupMax + NE), l->big.alloc(A / kTileN + NE);
   l->h.alloc((A + T) * F), l->y.alloc(A * E);
-  l->xq_routed.alloc(T, E, act_is_q8k(c.gate_type));
-  l->hq_routed.alloc(A, F, act_is_q8k(c.down_type));
+  const bool f16 = l->tensor_min != 0;
+  l->xq_routed.alloc(T, E, act_is_q8k(c.gate_type), f16);
+  l->hq_routed.alloc(A, F, act_is_q8k(c.down_type), f16);
   if (l->has_shared) {
     l->s.alloc((size_t)T * E);
     l->shared_x_same = act_is_q8k(c.shexp_gate_type) == act_is_q8k(c.gate_type);
-    if (!l->shared_x_same) l->xq_shared.alloc(T, E, act_is_q8k(c.shexp_gate_type));
-    l->hq_shared.alloc(T, F, act_is_q8k(c.shexp_down_type));
+    if (!l->shared_x_same) l->xq_shared.alloc(T, E, act_is_q8k(c.shexp_gate_type), f16);
+    l->hq_shared.alloc(T, F, act_is_q8k(c.shexp_down_type), f16);
   }
-  CUDA_OK(cudaMemsetAsync(l->counters.get(), 0, 4 * sizeof(uint32_t), st));
+  CUDA_OK(cudaMemsetAsync(l->counters.get(), 0, 8 * sizeof(uint32_t), st));
+  CUDA_OK(cudaMemsetAsync(l->error.get(), 0, sizeof(uint32_t), st));
   for (int i = 0; i <= MOE_STAGES; i++) l->ev.push_back(std::make_unique<Event>());
   CUDA_OK(cudaStreamSynchronize(st));
 }
@@ -193,10 +219,11 @@ void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, c
   if (nblk == 0) return;
   const ActView v = dst.view(row0, Kv);
   const unsigned grid = (unsigned)((nblk + 7) / 8);
+  __half *deq = dst.h.get() ? dst.h.get() + row0 * Kv : nullptr;
   if (dst.q8k)
-    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs);
+    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, deq);
   else
-    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d);
+    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, deq);
   launched(l, cudaGetLastError(), "quantize");
 }
 
@@ -231,28 +258,49 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   launched(l, cudaGetLastError(), "router top-k");
 
   mark(l, ST_PACK, st);
-  const PackOut po{l->cnt.get(), l->base.get(), l->chunk_off.get(), l->tiles.get(), l->groups.get(), l->counters.get()};
-  k_pack_scan<<<1, 512, 0, st>>>(l->chunk_hist.get(), nchunks, NE, c.expert_first, po);
+  const PackOut po{l->cnt.get(), l->base.get(), l->chunk_off.get(), l->tiles.get(), l->groups.get(), l->big.get(), l->counters.get()};
+  const uint32_t tm = l->tensor_min;
+  k_pack_scan<<<1, 512, 0, st>>>(l->chunk_hist.get(), nchunks, NE, c.expert_first, tm, po);
   launched(l, cudaGetLastError(), "pack scan");
   const uint32_t chunk_len = kChunkTokens * K;
   k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->base.get(), l->chunk_off.get(), K,
                                                              l->inv.get(), l->row_src.get());
   launched(l, cudaGetLastError(), "pack fill");
 
-  const int M = group_rows(T);
-  const uint32_t max_groups = (uint32_t)std::min<uint64_t>(A, A / kGroupMax + NE);
+  // The most groups and big tiles the step can have: an expert below tensor_min rows has (tensor_min - 1) / 8 + 1 groups
+  // at most, and one at or above it a tile per 256 rows and one more.
+  const int M = group_rows(tm ? std::min(T, tm - 1) : T);
+  const uint32_t max_groups =
+      tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(A, (uint64_t)NE * ((tm - 2) / kGroupMax + 1)) : 0) : (uint32_t)std::min<uint64_t>(A, A / kGroupMax + NE);
+  const uint32_t max_big = tm && T >= tm ? (uint32_t)(A / kTileN + std::min<uint64_t>(NE, A / tm)) : 0;
   mark(l, ST_GATE_UP, st);
-  {
+  if (max_big) {
+    ExpertTilesArgs a{};
+    a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F;
+    a.act = l->xq_routed.h.get(), a.act_row = l->row_src.get();
+    a.tiles = l->big.get(), a.ntiles = l->counters.get() + 4;
+    a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
+    launched(l, launch_tiles(c.gate_type, 2, a, max_big, l->grid.get(), st), "experts gate/up tiles");
+  }
+  if (max_groups) {
     ExpertRowsArgs a{};
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F, a.rows_per_cta = 32;
     a.act = l->xq_routed.view(0, E), a.act_row = l->row_src.get();
     a.groups = l->groups.get(), a.ngroups = l->counters.get() + 1;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
     launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
-    quantize_rows(l, l->h.get(), A, F, l->hq_routed, 0, st);
   }
+  quantize_rows(l, l->h.get(), A, F, l->hq_routed, 0, st);
   mark(l, ST_DOWN, st);
-  {
+  if (max_big) {
+    ExpertTilesArgs a{};
+    a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;
+    a.act = l->hq_routed.h.get(), a.act_row = nullptr;
+    a.tiles = l->big.get(), a.ntiles = l->counters.get() + 4;
+    a.out = l->y.get(), a.out_stride = E, a.error = l->error.get();
+    launched(l, launch_tiles(c.down_type, 1, a, max_big, l->grid.get(), st), "experts down tiles");
+  }
+  if (max_groups) {
     ExpertRowsArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E, a.rows_per_cta = 128;
     a.act = l->hq_routed.view(0, F), a.act_row = nullptr;
@@ -261,7 +309,22 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
     launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), st), "experts down");
   }
   mark(l, ST_SHARED, st);
-  if (l->has_shared) {
+  if (l->has_shared && tm && T >= tm) {
+    const ActBuffers &xs = l->shared_x_same ? l->xq_routed : l->xq_shared;
+    const uint32_t dense_tiles = (T + kTileN - 1) / kTileN;
+    ExpertTilesArgs a{};
+    a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.act = xs.h.get(), a.dense_rows = T;
+    a.out = l->h.get() + A * F, a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
+    launched(l, launch_tiles(c.shexp_gate_type, 2, a, dense_tiles, l->grid.get(), st), "shared gate/up tiles");
+    quantize_rows(l, l->h.get() + A * F, T, F, l->hq_shared, 0, st);
+    ExpertTilesArgs b{};
+    b.w0 = l->sd.get(), b.K = F, b.R = E, b.act = l->hq_shared.h.get(), b.dense_rows = T;
+    b.out = l->s.get(), b.out_stride = E, b.error = l->error.get();
+    launched(l, launch_tiles(c.shexp_down_type, 1, b, dense_tiles, l->grid.get(), st), "shared down tiles");
+    l->shared_on_tensor = true;
+  } else if (l->has_shared) {
+    l->shared_on_tensor = false;
+    const int M = group_rows(T);
     const uint32_t dense_groups = (T + M - 1) / M;
     ExpertRowsArgs a{};
     a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.rows_per_cta = 32;
@@ -280,6 +343,23 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   mark(l, ST_COPIES, st);
   l->last_T = T;
   l->stats.calls++, l->stats.rows += T, l->stats.assignments += A;
+}
+
+// After the stream has drained: a kernel whose wait ran out left the error word set.
+void check_device_error(moe_layer *l) {
+  uint32_t e = 0;
+  CUDA_OK(cudaMemcpy(&e, l->error.get(), sizeof(e), cudaMemcpyDeviceToHost));
+  if (e) {
+    CUDA_OK(cudaMemset(l->error.get(), 0, sizeof(e)));
+    throw Timeout("a tensor-core kernel gave up waiting on a barrier; the call's results are not valid");
+  }
+}
+
+void read_counters(moe_layer *l) {
+  uint32_t c[8];
+  CUDA_OK(cudaMemcpy(c, l->counters.get(), sizeof(c), cudaMemcpyDeviceToHost));
+  l->stats.last_tiles = c[0], l->stats.last_experts_hit = c[2];
+  l->stats.last_tensor_rows = c[5] + (l->shared_on_tensor ? l->last_T : 0);
 }
 
 template <class Fn>
@@ -337,6 +417,7 @@ MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, f
     if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
     l->stats.h2d_bytes += bytes, l->stats.d2h_bytes += bytes;
     l->stream->wait(0);
+    check_device_error(l);
   });
 }
 
@@ -353,7 +434,10 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
 
 MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms) {
   if (!l) return MOE_BAD_ARGUMENT;
-  return guarded(l, [&] { l->stream->wait(timeout_ms); });
+  return guarded(l, [&] {
+    l->stream->wait(timeout_ms);
+    check_device_error(l);
+  });
 }
 
 MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, uint32_t *inv, moe_tile *tiles, uint32_t tiles_cap,
@@ -364,7 +448,7 @@ MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, ui
     if (l->last_T == 0) throw BadArgument("no call has run yet");
     cudaStream_t st = l->stream->get();
     const size_t A = (size_t)l->last_T * l->K;
-    uint32_t counters[4];
+    uint32_t counters[8];
     CUDA_OK(cudaMemcpyAsync(counters, l->counters.get(), sizeof(counters), cudaMemcpyDeviceToHost, st));
     if (ids) CUDA_OK(cudaMemcpyAsync(ids, l->ids.get(), A * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
     if (w) CUDA_OK(cudaMemcpyAsync(w, l->w.get(), A * sizeof(float), cudaMemcpyDeviceToHost, st));
@@ -377,7 +461,7 @@ MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, ui
       l->stream->wait(0);
     }
     if (ntiles) *ntiles = counters[0];
-    l->stats.last_tiles = counters[0], l->stats.last_experts_hit = counters[2];
+    read_counters(l);
   });
 }
 
@@ -386,10 +470,8 @@ MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out) {
   std::lock_guard<std::mutex> lk(l->mu);
   return guarded(l, [&] {
     if (l->last_T) {
-      uint32_t counters[4];
       l->stream->wait(0);
-      CUDA_OK(cudaMemcpy(counters, l->counters.get(), sizeof(counters), cudaMemcpyDeviceToHost));
-      l->stats.last_tiles = counters[0], l->stats.last_experts_hit = counters[2];
+      read_counters(l);
     }
     *out = l->stats;
   });
@@ -428,6 +510,7 @@ MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap) {
       ROW(moe_layer_config, gate_type), ROW(moe_layer_config, down_type), ROW(moe_layer_config, shexp_gate_type),
       ROW(moe_layer_config, shexp_down_type), ROW(moe_layer_config, expert_first), ROW(moe_layer_config, expert_count),
       ROW(moe_layer_config, max_tokens), ROW(moe_layer_config, device), ROW(moe_layer_config, swiglu_limit), ROW(moe_layer_config, flags),
+      ROW(moe_layer_config, tensor_min_rows), ROW(moe_layer_config, reserved),
       ROW(moe_layer_weights, router), ROW(moe_layer_weights, shexp_gate_inp), ROW(moe_layer_weights, router_bias),
       ROW(moe_layer_weights, gate_exps), ROW(moe_layer_weights, up_exps), ROW(moe_layer_weights, down_exps),
       ROW(moe_layer_weights, gate_shexp), ROW(moe_layer_weights, up_shexp), ROW(moe_layer_weights, down_shexp),

@@ -11,6 +11,7 @@
 #include <cstdint>
 
 #include "expert_rows.cuh"
+#include "expert_tiles.cuh"
 
 namespace moe {
 
@@ -27,7 +28,7 @@ constexpr uint32_t kRouterPieces = 8;   // pieces a router product is summed in
 // q8_0: per 32 values d = max|x| / 127, q = round(x * (1 / d)), 0 when d is 0; d kept as the f16 the CPU stores
 // (docs/spec/QUANT_FORMATS.md:463-465, :525-526).
 __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
-                                                   float *__restrict__ d) {
+                                                   float *__restrict__ d, __half *__restrict__ deq) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
@@ -44,13 +45,21 @@ __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x,
   hi.z = (signed char)roundf(b.z * id), hi.w = (signed char)roundf(b.w * id);
   ((char4 *)(q + blk * 256))[2 * lane] = lo;
   ((char4 *)(q + blk * 256))[2 * lane + 1] = hi;
-  if (lane % 4 == 0) d[blk * 8 + lane / 4] = __half2float(__float2half_rn(dd));
+  const float dh = __half2float(__float2half_rn(dd));
+  if (lane % 4 == 0) d[blk * 8 + lane / 4] = dh;
+  if (deq) {  // the codes dequantised, as f16: what the tensor-core kernels take for this row
+    const __half2 h0 = __floats2half2_rn(dh * (float)lo.x, dh * (float)lo.y), h1 = __floats2half2_rn(dh * (float)lo.z, dh * (float)lo.w);
+    const __half2 h2 = __floats2half2_rn(dh * (float)hi.x, dh * (float)hi.y), h3 = __floats2half2_rn(dh * (float)hi.z, dh * (float)hi.w);
+    uint4 o;
+    o.x = *(const uint32_t *)&h0, o.y = *(const uint32_t *)&h1, o.z = *(const uint32_t *)&h2, o.w = *(const uint32_t *)&h3;
+    ((uint4 *)(deq + blk * 256))[lane] = o;
+  }
 }
 
 // q8_K: per 256 values iscale = -127 / max with max the value of largest magnitude (the first of equals),
 // q = min(127, nearest-even(iscale * x)), d = 1 / iscale, and the sums of each 16 codes (QUANT_FORMATS.md:528-535).
 __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
-                                                   float *__restrict__ d, int16_t *__restrict__ bs) {
+                                                   float *__restrict__ d, int16_t *__restrict__ bs, __half *__restrict__ deq) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
@@ -72,6 +81,7 @@ __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x,
     ((char4 *)(q + blk * 256))[2 * lane + 1] = make_char4(0, 0, 0, 0);
     if (lane == 0) d[blk] = 0.0f;
     if (lane % 2 == 0) bs[blk * 16 + lane / 2] = 0;
+    if (deq) ((uint4 *)(deq + blk * 256))[lane] = make_uint4(0, 0, 0, 0);
     return;
   }
   const float iscale = -127.0f / mx;
@@ -82,7 +92,15 @@ __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x,
   ((char4 *)(q + blk * 256))[2 * lane + 1] = make_char4((signed char)c[4], (signed char)c[5], (signed char)c[6], (signed char)c[7]);
   sum += __shfl_xor_sync(0xffffffffu, sum, 1);
   if (lane % 2 == 0) bs[blk * 16 + lane / 2] = (int16_t)sum;
-  if (lane == 0) d[blk] = 1.0f / iscale;
+  const float dd = 1.0f / iscale;
+  if (lane == 0) d[blk] = dd;
+  if (deq) {
+    const __half2 h0 = __floats2half2_rn(dd * (float)c[0], dd * (float)c[1]), h1 = __floats2half2_rn(dd * (float)c[2], dd * (float)c[3]);
+    const __half2 h2 = __floats2half2_rn(dd * (float)c[4], dd * (float)c[5]), h3 = __floats2half2_rn(dd * (float)c[6], dd * (float)c[7]);
+    uint4 o;
+    o.x = *(const uint32_t *)&h0, o.y = *(const uint32_t *)&h1, o.z = *(const uint32_t *)&h2, o.w = *(const uint32_t *)&h3;
+    ((uint4 *)(deq + blk * 256))[lane] = o;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -319,15 +337,19 @@ struct PackOut {
   uint32_t *cnt, *base;    // NE each
   uint32_t *chunk_off;     // [chunks][NE]: rows of the expert's run taken by earlier chunks
   MoeTile *tiles;          // expert order, <= 64 rows each (prompt.cl:719-723)
-  MoeGroup *groups;        // <= 8 rows each
-  uint32_t *counters;      // [0] tiles, [1] groups, [2] experts hit, [3] rows
+  MoeGroup *groups;        // <= 8 rows each: the experts with fewer than tensor_min rows
+  BigTile *big;            // <= kTileN rows each: the others, for the tensor-core kernels
+  uint32_t *counters;      // [0] tiles, [1] groups, [2] experts hit, [3] rows, [4] big tiles, [5] their rows
 };
+
+// Whether an expert with n rows goes to the tensor-core kernels (tensor_min 0: none does).
+__host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { return tensor_min != 0 && n >= tensor_min; }
 
 // One CTA of 512 threads, thread e for expert e: sums the chunks' counts, scans them over the experts, writes tiles
 // and groups. first_expert: the id of slot 0.
 __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
-                                                  uint32_t first_expert, PackOut o) {
-  __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512];
+                                                  uint32_t first_expert, uint32_t tensor_min, PackOut o) {
+  __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512];
   const uint32_t e = threadIdx.x;
   uint32_t run = 0;
   if (e < NE) {
@@ -338,14 +360,17 @@ __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ 
       run += v;
     }
   }
-  const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = (n + kGroupMax - 1) / kGroupMax;
-  s_rows[e] = n, s_tiles[e] = nt, s_groups[e] = ng, s_hit[e] = n > 0;
+  const bool tensor = n_is_tensor(run, tensor_min);
+  const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = tensor ? 0 : (n + kGroupMax - 1) / kGroupMax;
+  const uint32_t nb = tensor ? (n + kTileN - 1) / kTileN : 0;
+  s_rows[e] = n, s_tiles[e] = nt, s_groups[e] = ng, s_hit[e] = n > 0, s_big[e] = nb, s_bigrows[e] = tensor ? n : 0;
   __syncthreads();
   for (uint32_t off = 1; off < 512; off <<= 1) {
     const uint32_t a = e >= off ? s_rows[e - off] : 0, b = e >= off ? s_tiles[e - off] : 0;
     const uint32_t c = e >= off ? s_groups[e - off] : 0, d = e >= off ? s_hit[e - off] : 0;
+    const uint32_t f = e >= off ? s_big[e - off] : 0, g = e >= off ? s_bigrows[e - off] : 0;
     __syncthreads();
-    s_rows[e] += a, s_tiles[e] += b, s_groups[e] += c, s_hit[e] += d;
+    s_rows[e] += a, s_tiles[e] += b, s_groups[e] += c, s_hit[e] += d, s_big[e] += f, s_bigrows[e] += g;
     __syncthreads();
   }
   if (e < NE) {
@@ -357,8 +382,13 @@ __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ 
       o.tiles[tile0 + i] = MoeTile{first_expert + e, e, first + i * kTileRows, min(kTileRows, n - i * kTileRows)};
     for (uint32_t i = 0; i < ng; i++)
       o.groups[group0 + i] = MoeGroup{e, first + i * kGroupMax, min((uint32_t)kGroupMax, n - i * kGroupMax)};
+    const uint32_t big0 = s_big[e] - nb;
+    for (uint32_t i = 0; i < nb; i++) o.big[big0 + i] = BigTile{e, first + i * kTileN, min(kTileN, n - i * kTileN)};
   }
-  if (e == 511) o.counters[0] = s_tiles[e], o.counters[1] = s_groups[e], o.counters[2] = s_hit[e], o.counters[3] = s_rows[e];
+  if (e == 511) {
+    o.counters[0] = s_tiles[e], o.counters[1] = s_groups[e], o.counters[2] = s_hit[e], o.counters[3] = s_rows[e];
+    o.counters[4] = s_big[e], o.counters[5] = s_bigrows[e];
+  }
 }
 
 // One CTA per chunk, thread e for expert e: walks the chunk's ids in order and hands out its expert's rows in that

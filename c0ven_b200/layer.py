@@ -30,7 +30,7 @@ class MoELayer:
     """
 
     def __init__(self, layer: dict, max_tokens: int = 4352, device: int = 0, profile: bool = False,
-                 expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False):
+                 expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0):
         self._h = None
         L = _lib.lib()
         self.n_embd, self.n_ff = layer["n_embd"], layer["n_ff"]
@@ -41,7 +41,7 @@ class MoELayer:
         cfg = _lib.Config(self.n_embd, self.n_ff, self.n_experts, self.n_used, layer["gate_type"], layer["down_type"],
                           layer["shexp_gate_type"] if has_shared else 0, layer["shexp_down_type"] if has_shared else 0,
                           expert_first, count, max_tokens, device, float(layer.get("swiglu_limit", 0.0)),
-                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0))
+                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, 0)
         sl = slice(expert_first, expert_first + count)
         keep = [np.ascontiguousarray(layer["router"], dtype=np.float32),
                 np.ascontiguousarray(layer["shexp_gate_inp"], dtype=np.float32) if has_shared else None,

@@ -59,6 +59,9 @@ typedef struct {
   int32_t device;             /* CUDA device ordinal */
   float swiglu_limit;         /* ExpertShape::swiglu_limit; 0: off */
   uint32_t flags;             /* MOE_FLAG_* */
+  uint32_t tensor_min_rows;   /* an expert with at least this many rows in a call goes to the tensor-core kernels, one
+                                 with fewer to the integer-dot kernels; default 16 */
+  uint32_t reserved;
 } moe_layer_config;
 
 #define MOE_FLAG_PROFILE 1u     /* time every stage of a call with events (moe_layer_stage_ms) */
