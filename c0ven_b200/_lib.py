@@ -14,7 +14,8 @@ STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", 
 
 SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_layer_forward_device", "moe_layer_sync",
            "moe_layer_read_route", "moe_layer_read_stats", "moe_layer_stage_ms", "moe_layer_stream", "moe_last_error",
-           "moe_abi_layout", "moe_to_runs", "moe_from_runs")
+           "moe_abi_layout", "moe_to_runs", "moe_from_runs",
+           "moe_route_rows_static", "moe_route_rows_static_error")
 
 
 class Config(C.Structure):
@@ -77,6 +78,8 @@ def lib():
         L.moe_last_error.restype = C.c_char_p
         L.moe_to_runs.argtypes = [u32, vp, C.c_uint64, vp]
         L.moe_from_runs.argtypes = [u32, vp, C.c_uint64, vp]
+        L.moe_route_rows_static.argtypes = [vp, u32, u32, vp, vp, u32, u32, vp, vp, vp, vp]
+        L.moe_route_rows_static_error.restype = C.c_char_p
         L.moe_abi_layout.argtypes = [C.POINTER(AbiRow), u32]
         L.moe_abi_layout.restype = u32
         _lib = L

@@ -27,7 +27,7 @@ constexpr uint32_t kRouterPieces = 8;   // pieces a router product is summed in
 
 // q8_0: per 32 values d = max|x| / 127, q = round(x * (1 / d)), 0 when d is 0; d kept as the f16 the CPU stores
 // (docs/spec/QUANT_FORMATS.md:463-465, :525-526).
-__global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
+static __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
                                                    float *__restrict__ d, __half *__restrict__ deq) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x,
 
 // q8_K: per 256 values iscale = -127 / max with max the value of largest magnitude (the first of equals),
 // q = min(127, nearest-even(iscale * x)), d = 1 / iscale, and the sums of each 16 codes (QUANT_FORMATS.md:528-535).
-__global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
+static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
                                                    float *__restrict__ d, int16_t *__restrict__ bs, __half *__restrict__ deq) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x,
 
 // Few rows (up to 8 per CTA pass): 4 weight rows per warp, 8 lanes a row, lane s taking piece s.
 template <int TM>
-__global__ void __launch_bounds__(128) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
+static __global__ void __launch_bounds__(128) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
                                                            const float *__restrict__ W, uint32_t N,
                                                            const float *__restrict__ bias, uint32_t NE,
                                                            float *__restrict__ rl) {
@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(128) k_router_logits_rows(const float *__restr
 
 // Many rows: a 128 x 64 tile of (rows, experts) per CTA of 256 threads, 8 x 4 outputs a thread, 16 values of the
 // hidden size a step; the tile's partial sums fold into the totals at every piece's end.
-__global__ void __launch_bounds__(256) k_router_logits_tiles(const float *__restrict__ x, uint32_t T, uint32_t E,
+static __global__ void __launch_bounds__(256) k_router_logits_tiles(const float *__restrict__ x, uint32_t T, uint32_t E,
                                                             const float *__restrict__ W, uint32_t N,
                                                             const float *__restrict__ bias, uint32_t NE,
                                                             float *__restrict__ rl) {
@@ -247,7 +247,7 @@ __device__ __forceinline__ float key_value(uint32_t key) {
 
 constexpr int kMaxPerLane = 16;  // experts a lane holds at most: 512 / 32
 
-__global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, uint32_t T, uint32_t NE,
+static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, uint32_t T, uint32_t NE,
                                                                   uint32_t K, int32_t *__restrict__ ids,
                                                                   float *__restrict__ w, float *__restrict__ gs,
                                                                   uint32_t *__restrict__ chunk_hist) {
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *
 
 // The same counts for expert ids that come from elsewhere (the rows another GPU sent): chunk c holds entries
 // [c * chunk_len, (c + 1) * chunk_len) of ids.
-__global__ void __launch_bounds__(256) k_chunk_hist(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len,
+static __global__ void __launch_bounds__(256) k_chunk_hist(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len,
                                                    uint32_t NE, uint32_t *__restrict__ chunk_hist) {
   __shared__ uint32_t hist[512];
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
@@ -347,7 +347,7 @@ __host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { r
 
 // One CTA of 512 threads, thread e for expert e: sums the chunks' counts, scans them over the experts, writes tiles
 // and groups. first_expert: the id of slot 0.
-__global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
+static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
                                                   uint32_t first_expert, uint32_t tensor_min, PackOut o) {
   __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512];
   const uint32_t e = threadIdx.x;
@@ -393,7 +393,7 @@ __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ 
 
 // One CTA per chunk, thread e for expert e: walks the chunk's ids in order and hands out its expert's rows in that
 // order. inv[a] = row; row_src[row] = a / src_div (the activation row the assignment reads: its token).
-__global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len, uint32_t NE,
+static __global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len, uint32_t NE,
                                                   const uint32_t *__restrict__ base, const uint32_t *__restrict__ chunk_off,
                                                   uint32_t src_div, uint32_t *__restrict__ inv, uint32_t *__restrict__ row_src) {
   extern __shared__ int32_t s_ids[];
@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restrict__ i
 // ---------------------------------------------------------------------------------------------------------------
 // Combine: out[t] = sum over k, in rank order, of w[t][k] * y[inv[t K + k]] + gs[t] * s[t], in f32 (layer.cl:874-877).
 // One CTA per row.
-__global__ void __launch_bounds__(256) k_combine(const float *__restrict__ y, const uint32_t *__restrict__ inv,
+static __global__ void __launch_bounds__(256) k_combine(const float *__restrict__ y, const uint32_t *__restrict__ inv,
                                                 const float *__restrict__ w, const float *__restrict__ gs,
                                                 const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out) {
   const uint32_t t = blockIdx.x;

@@ -137,6 +137,26 @@ MOE_API void *moe_layer_stream(moe_layer *l);
 /* The last error's message, valid until the next call on l (or, for create's failures, with l null). */
 MOE_API const char *moe_last_error(const moe_layer *l);
 
+/* No counterpart in the reference. The router alone (logits, softmax, top n_used, renormalised weights, and the shared
+ * expert's gate), for callers that must not allocate while a step runs: an engine that shared out all device memory at
+ * load, or a step loop that cannot take the allocator's device-wide wait. It calls no cudaMalloc, cudaFree or
+ * allocating library routine; the scratch between its two kernels is a fixed array inside the library (about 136 KB on
+ * every GPU that loads it, held until the process ends), so T is at most MOE_ROUTE_STATIC_MAX_ROWS, n_experts at
+ * most 512 and n_embd at most 4096; more is refused with MOE_BAD_ARGUMENT.
+ *   x_dev [T][n_embd] f32; router_dev [n_experts + 1][n_embd] f32, the router's rows and then the shared expert's gate
+ *   vector (zeros if there is none); bias_dev [n_experts] or null; out: ids_dev, w_dev [T][n_used] in rank order,
+ *   gate_dev [T] = sigmoid(gate . x). All DEVICE pointers of the current device, the caller's; queued on stream (a
+ *   cudaStream_t; null: the default stream) without waiting.
+ * The first call on a device looks up the array's device address and sets one kernel attribute: make that call before
+ * any stream capture begins. All calls share the one array: two calls whose kernels may overlap on a GPU (different
+ * streams, no ordering between them) race on it; order them. Nothing in it needs clearing between calls.
+ * moe_route_rows_static_error: the calling thread's last message from it. */
+#define MOE_ROUTE_STATIC_MAX_ROWS 64
+MOE_API moe_status moe_route_rows_static(const float *x_dev, uint32_t T, uint32_t n_embd, const float *router_dev,
+                                         const float *bias_dev, uint32_t n_experts, uint32_t n_used, int32_t *ids_dev,
+                                         float *w_dev, float *gate_dev, void *stream);
+MOE_API const char *moe_route_rows_static_error(void);
+
 /* The layout the GPU holds a slice of nblocks blocks in: one run per field of the block, quants first, as the
  * reference's to_runs and from_runs make it (core/load/runs.cpp:12-41; shared/quant.h:172-176). Host only: a
  * permutation of the slice's bytes, src and dst nblocks * block bytes each. */
