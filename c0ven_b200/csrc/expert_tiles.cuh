@@ -87,6 +87,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+// The arrival happens when every cp.async this thread issued before it has landed; it counts as one of the barrier's
+// expected arrivals.
+__device__ __forceinline__ void mbar_arrive_after_copies(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void copy_async16(uint32_t dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -341,7 +349,8 @@ struct TileSmem {
   static constexpr uint32_t kStageBytes = NMAT * kWBytes + kXBytes;
   static constexpr uint32_t kBarriers = kStages * kStageBytes;  // full[kStages], empty[kStages], acc, then tmem address, abort
   static constexpr uint32_t kGrid = kBarriers + 128;            // IQ3_S's codebook, 2 KB
-  static constexpr uint32_t kBytes = kGrid + 2048 + 1024;       // and room to align the base to 1024
+  static constexpr uint32_t kRowIdx = kGrid + 2048;             // the tile's activation rows, kTileN words
+  static constexpr uint32_t kBytes = kRowIdx + 4 * kTileN + 1024;  // and room to align the base to 1024
 };
 
 // NMAT 2: out = swiglu(gate x, up x); NMAT 1: out = down h. Launch: grid (R / 128, tiles at most), 288 threads
@@ -376,16 +385,21 @@ __global__ void __launch_bounds__(288, 1) k_expert_tiles(const ExpertTilesArgs a
   uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 1);
   volatile uint32_t *abort = tmem_slot + 1;
   uint32_t *grid = (uint32_t *)(smem + SM::kGrid);
+  uint32_t *rowidx = (uint32_t *)(smem + SM::kRowIdx);
   constexpr uint32_t kCols = NMAT == 2 ? 512 : 256;
 
+  // A stage is full when every worker has stored its decoded weights (one arrival) and its copies of the rows'
+  // activations have landed (one more, made by the copy unit).
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kTileWorkers), mbar_init(empty_bar(s), 1);
+    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), 2 * kTileWorkers), mbar_init(empty_bar(s), 1);
     mbar_init(acc_bar, 1);
     *abort = 0;
     fence_barrier_init();
   }
   if constexpr (QT == QT_IQ3_S)
     for (uint32_t i = tid; i < 512; i += blockDim.x) grid[i] = grid_global[i];
+  for (uint32_t n = tid; n < kTileN; n += blockDim.x)
+    rowidx[n] = n < count ? (a.act_row ? a.act_row[start + n] : start + n) : 0xFFFFFFFFu;
   if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kCols);
   tc_fence_before();
   __syncthreads();
@@ -398,40 +412,47 @@ __global__ void __launch_bounds__(288, 1) k_expert_tiles(const ExpertTilesArgs a
     const uint8_t *w0 = a.w0 + (uint64_t)slot * a.slice_bytes;
     const uint8_t *w1 = NMAT == 2 ? a.w1 + (uint64_t)slot * a.slice_bytes : nullptr;
     constexpr uint32_t UPT = Dec::kUnits / kTileWorkers;  // weight units a thread takes per matrix and stage
-    // Activation chunks of 16 bytes: row n, chunk kc; a thread takes row (tid % 8) + 8 j of chunk column tid / 8 ...
-    const uint32_t nchunks = N * 8;
+    using Raw = typename Dec::Raw;
+    const uint32_t nchunks = N * 8;  // 16-byte pieces of the rows' activations in a stage
     bool ok = true;
-    for (uint32_t it = 0; it < KT && ok; it++) {
+    Raw raw[2][NMAT][UPT];  // this stage's quants and the next one's, fetched a stage ahead
+    auto fetch = [&](Raw (&r)[NMAT][UPT], uint32_t k0) {
+#pragma unroll
+      for (uint32_t j = 0; j < UPT; j++) {
+        r[0][j] = Dec::fetch(w0, nblk, K, r0, k0, tid + j * kTileWorkers);
+        if constexpr (NMAT == 2) r[1][j] = Dec::fetch(w1, nblk, K, r0, k0, tid + j * kTileWorkers);
+      }
+    };
+    auto stage_step = [&](Raw (&r)[NMAT][UPT], uint32_t it) {
       const uint32_t s = it % S, k0 = it * kTileK;
       uint8_t *stage = smem + s * SM::kStageBytes;
-      typename Dec::Raw raw[NMAT][UPT];
-#pragma unroll
-      for (uint32_t j = 0; j < UPT; j++) {
-        raw[0][j] = Dec::fetch(w0, nblk, K, r0, k0, tid + j * kTileWorkers);
-        if constexpr (NMAT == 2) raw[1][j] = Dec::fetch(w1, nblk, K, r0, k0, tid + j * kTileWorkers);
-      }
       if (it >= S) ok = mbar_wait(empty_bar(s), ((it / S) - 1) & 1, abort, a.error);
-      if (!ok) break;
+      if (!ok) return;
       tc_fence_after();
+      // The rows' activations: 16-byte asynchronous copies by token index, straight into the operand layout. Piece c
+      // is (row n, chunk kc); 8 consecutive threads take the 8 rows of a core matrix. Rows past count are never read
+      // back (their columns of the result are dropped), so they are left as they are.
+      const uint32_t xt = smem_u32(stage + NMAT * SM::kWBytes);
+      for (uint32_t c = tid; c < nchunks; c += kTileWorkers) {
+        const uint32_t n = (c & 7) | ((c >> 6) << 3), kc = (c >> 3) & 7, row = rowidx[n];
+        if (row != 0xFFFFFFFFu) copy_async16(xt + (n >> 3) * kSbo + kc * kLbo + (n & 7) * 16, a.act + (uint64_t)row * K + k0 + 8 * kc);
+      }
+      mbar_arrive_after_copies(full_bar(s));
 #pragma unroll
       for (uint32_t j = 0; j < UPT; j++) {
-        decode_store<QT>(raw[0][j], stage, tid + j * kTileWorkers, grid, k0);
-        if constexpr (NMAT == 2) decode_store<QT>(raw[1][j], stage + SM::kWBytes, tid + j * kTileWorkers, grid, k0);
-      }
-      uint8_t *xt = stage + NMAT * SM::kWBytes;
-      for (uint32_t c = tid; c < nchunks; c += kTileWorkers) {
-        // c -> (row n, chunk kc): 8 consecutive threads take the 8 rows of a core matrix, so a quarter-warp's stores
-        // fill 128 contiguous bytes.
-        const uint32_t n = (c & 7) | ((c >> 6) << 3), kc = (c >> 3) & 7;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (n < count) {
-          const uint64_t row = a.act_row ? a.act_row[start + n] : start + n;
-          v = ldg16(a.act + row * K + k0 + 8 * kc);
-        }
-        *(uint4 *)(xt + (n >> 3) * kSbo + kc * kLbo + (n & 7) * 16) = v;
+        decode_store<QT>(r[0][j], stage, tid + j * kTileWorkers, grid, k0);
+        if constexpr (NMAT == 2) decode_store<QT>(r[1][j], stage + SM::kWBytes, tid + j * kTileWorkers, grid, k0);
       }
       fence_async_smem();
       mbar_arrive(full_bar(s));
+    };
+    fetch(raw[0], 0);
+    for (uint32_t it = 0; it < KT && ok; it += 2) {
+      if (it + 1 < KT) fetch(raw[1], (it + 1) * kTileK);
+      stage_step(raw[0], it);
+      if (!ok || it + 1 >= KT) break;
+      if (it + 2 < KT) fetch(raw[0], (it + 2) * kTileK);
+      stage_step(raw[1], it + 1);
     }
     // Epilogue: warp w reads TMEM lanes 32 (w % 4) .., its row of the weights; warps w and w + 4 share the columns.
     if (ok) ok = mbar_wait(acc_bar, 0, abort, a.error);
@@ -462,6 +483,7 @@ __global__ void __launch_bounds__(288, 1) k_expert_tiles(const ExpertTilesArgs a
       const uint32_t s = it % S;
       ok = mbar_wait(full_bar(s), (it / S) & 1, abort, a.error);
       if (!ok) break;
+      fence_async_smem();  // the copies' writes, like the workers' stores, must be visible to the tensor core's reads
       tc_fence_after();
       const uint32_t stage = smem_u32(smem + s * SM::kStageBytes), xt = stage + NMAT * SM::kWBytes;
 #pragma unroll
