@@ -158,19 +158,41 @@ def run_gpu(args, w):
     layer = build_layer(w)
     x_host = torch.from_numpy(synth.make_input(T, E, seed=1 + rank)).pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
-    gpu = MoELayer(layer, max_tokens=T, device=local, profile=True)
-    stream = torch.cuda.ExternalStream(gpu.stream, device=local)
-    x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
     flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
+    if world == 1:
+        gpu = MoELayer(layer, max_tokens=T, device=local, profile=True, tensor_min_rows=args.tensor_min)
+        x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
+
+        def step():
+            gpu.forward_device(x_dev.data_ptr(), T, out_dev.data_ptr())
+
+        def step_host():
+            gpu.forward(x_host.numpy(), out_host.numpy())
+    else:
+        # Expert parallel: every rank holds 512 / N experts and brings its own T rows (weak scaling).
+        from c0ven_b200 import ep
+
+        stages = ep.GpuStages(layer, rank, world, max_tokens=T, device=local, y_f16=True, profile=True,
+                              tensor_min_rows=args.tensor_min)
+        moe, gpu = ep.ExpertParallelMoE(stages), stages.moe
+        x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
+
+        def step():
+            moe.forward(x_dev, out_dev)
+
+        def step_host():
+            with torch.cuda.stream(stages.stream):
+                xd = x_host.to("cuda", non_blocking=True)
+                od = moe.forward(xd)
+                out_host.copy_(od, non_blocking=True)
+            gpu.sync()
+    stream = torch.cuda.ExternalStream(gpu.stream, device=local)
 
     def barrier():
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
         torch.cuda.synchronize()
-
-    def step():
-        gpu.forward_device(x_dev.data_ptr(), T, out_dev.data_ptr())
 
     for _ in range(args.warmup):
         step()
@@ -200,14 +222,15 @@ def run_gpu(args, w):
     ms = float(t.item())
     st = gpu.stats()
 
-    # End to end: host buffers through moe_layer_forward, the copies inside the timed region.
-    xh, oh = x_host.numpy(), out_host.numpy()
+    # End to end: host buffers (pinned) in, host buffers out, the copies inside the timed region. One GPU: the C ABI's
+    # moe_layer_forward; expert parallel: the same stages with the copies on the layer's stream.
+    xh = x_host.numpy()
     for _ in range(2):
-        gpu.forward(xh, oh)
+        step_host()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        gpu.forward(xh, oh)
+        step_host()
     torch.cuda.synchronize()
     e2e_s = (time.perf_counter() - t0) / args.steps
     t = torch.tensor([e2e_s], device="cuda")
@@ -215,7 +238,20 @@ def run_gpu(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_s = float(t.item())
 
+    def teardown():
+        # Tensors the collectives touched are freed before the layer's stream goes, and the group before the process.
+        nonlocal x_dev, out_dev, flush
+        torch.cuda.synchronize()
+        del x_dev, out_dev, flush
+        if world > 1:
+            stages.close()
+            dist.barrier()
+            dist.destroy_process_group()
+        else:
+            gpu.close()
+
     if rank != 0:
+        teardown()
         return
     peaks = measured_peaks()
     alg = algorithmic(w, T, st["last_experts_hit"])
@@ -244,13 +280,15 @@ def run_gpu(args, w):
                 config=dict(workload=w["name"], rows=T, runs=w.get("runs"), hidden=E, ffn=F, experts=NE, top_k=K,
                             weights=synth.TYPE_NAMES[w["gate_type"]], zipf_s=w.get("zipf_s", 0.0),
                             experts_hit=st["last_experts_hit"], tiles=st["last_tiles"],
-                            parallelism="1 GPU" if world == 1 else f"replicas x{world}", l2="flushed between timed steps"),
+                            parallelism="1 GPU" if world == 1 else f"expert parallel x{world}: {NE // world} experts and {T} rows per GPU, "
+                            "all-to-all of q8 rows out and f16 results back", l2="flushed between timed steps"),
                 roofline=roof, stage_ms=stage, layer_bytes=alg["bytes_layer"], layer_flops=alg["flops_layer"],
                 cpu_baseline=cpu, clocks=clocks.summary(),
                 e2e=dict(value=world * T / e2e_s, unit=UNIT, h2d_bytes_per_step=T * E * 4, d2h_bytes_per_step=T * E * 4,
                          ms_per_step=e2e_s * 1e3),
                 gpu_launches=launches)
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
+    teardown()
 
 
 def main():
@@ -262,6 +300,7 @@ def main():
     ap.add_argument("--workload", default="ragged3521_q4_k_zipf", choices=[k for k, v in synth.CONFIGS.items() if isinstance(v["tokens"], int)])
     ap.add_argument("--cpu-tokens", type=int, default=3521, help="rows of the batch the CPU baseline takes per pass")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     w = workload(args.workload)

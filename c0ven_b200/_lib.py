@@ -15,7 +15,9 @@ STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", 
 SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_layer_forward_device", "moe_layer_sync",
            "moe_layer_read_route", "moe_layer_read_stats", "moe_layer_stage_ms", "moe_layer_stream", "moe_last_error",
            "moe_abi_layout", "moe_to_runs", "moe_from_runs",
-           "moe_route_rows_static", "moe_route_rows_static_error")
+           "moe_route_rows_static", "moe_route_rows_static_error", "moe_layer_route_device", "moe_layer_read_counts", "moe_layer_counts_device",
+           "moe_layer_wire_row_bytes", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
+           "moe_layer_combine_device")
 
 
 class Config(C.Structure):
@@ -23,7 +25,7 @@ class Config(C.Structure):
                 ("gate_type", C.c_uint32), ("down_type", C.c_uint32), ("shexp_gate_type", C.c_uint32),
                 ("shexp_down_type", C.c_uint32), ("expert_first", C.c_uint32), ("expert_count", C.c_uint32),
                 ("max_tokens", C.c_uint32), ("device", C.c_int32), ("swiglu_limit", C.c_float), ("flags", C.c_uint32),
-                ("tensor_min_rows", C.c_uint32), ("reserved", C.c_uint32)]
+                ("tensor_min_rows", C.c_uint32), ("max_expert_rows", C.c_uint32)]
 
 
 class Weights(C.Structure):
@@ -78,6 +80,15 @@ def lib():
         L.moe_last_error.restype = C.c_char_p
         L.moe_to_runs.argtypes = [u32, vp, C.c_uint64, vp]
         L.moe_from_runs.argtypes = [u32, vp, C.c_uint64, vp]
+        L.moe_layer_route_device.argtypes = [vp, vp, u32, vp]
+        L.moe_layer_read_counts.argtypes = [vp, vp, vp]
+        L.moe_layer_counts_device.argtypes = [vp, vp, vp]
+        L.moe_layer_wire_row_bytes.argtypes = [vp]
+        L.moe_layer_wire_row_bytes.restype = u32
+        L.moe_layer_gather_rows_device.argtypes = [vp, vp, vp, vp]
+        L.moe_layer_experts_device.argtypes = [vp, vp, vp, u32, vp, u32, vp]
+        L.moe_layer_shared_device.argtypes = [vp, vp]
+        L.moe_layer_combine_device.argtypes = [vp, vp, u32, vp, vp]
         L.moe_route_rows_static.argtypes = [vp, u32, u32, vp, vp, u32, u32, vp, vp, vp, vp]
         L.moe_route_rows_static_error.restype = C.c_char_p
         L.moe_abi_layout.argtypes = [C.POINTER(AbiRow), u32]

@@ -22,12 +22,14 @@ struct MoeGroup {
 };
 constexpr int kGroupMax = 8;
 
-// Quantised activation rows: codes [rows][K]; q8_0: d [rows][K/32] (the f16 scale, widened); q8_K: d [rows][K/256]
-// and bs [rows][K/16], the sums of each 16 codes.
+// Quantised activation rows: a row's K codes at q + row * q_stride; its scales at d + row * d_stride bytes (q8_0: K/32
+// floats, the f16 scale widened; q8_K: K/256 floats); q8_K's sums of each 16 codes at bs + row * bs_stride bytes. The
+// strides let the three parts be arrays of their own or pieces of one packed row.
 struct ActView {
   const int8_t *q;
   const float *d;
   const int16_t *bs;
+  uint32_t q_stride, d_stride, bs_stride;
 };
 
 struct ExpertRowsArgs {
@@ -295,13 +297,15 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
     uint8_t *dst = smem + t * stride;
     if (t < n) {
       const uint64_t row = a.act_row ? a.act_row[start + t] : start + t;
-      const int4 *src = (const int4 *)(a.act.q + row * K);
+      const int4 *src = (const int4 *)(a.act.q + row * a.act.q_stride);
+      const float *sd = (const float *)((const uint8_t *)a.act.d + row * a.act.d_stride);
       for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int4 *)dst)[i] = src[i];
       if (q8k) {
-        for (uint32_t i = threadIdx.x; i < K / 256; i += 256) ((float *)(dst + K))[i] = a.act.d[row * (K / 256) + i];
-        for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int16_t *)(dst + K + dsz))[i] = a.act.bs[row * (K / 16) + i];
+        const int16_t *sb = (const int16_t *)((const uint8_t *)a.act.bs + row * a.act.bs_stride);
+        for (uint32_t i = threadIdx.x; i < K / 256; i += 256) ((float *)(dst + K))[i] = sd[i];
+        for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int16_t *)(dst + K + dsz))[i] = sb[i];
       } else {
-        for (uint32_t i = threadIdx.x; i < K / 32; i += 256) ((float *)(dst + K))[i] = a.act.d[row * (K / 32) + i];
+        for (uint32_t i = threadIdx.x; i < K / 32; i += 256) ((float *)(dst + K))[i] = sd[i];
       }
     } else {
       for (uint32_t i = threadIdx.x; i < dsz / 4; i += 256) ((float *)(dst + K))[i] = 0.0f;

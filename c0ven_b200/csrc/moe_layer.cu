@@ -63,19 +63,47 @@ struct ActBuffers {
   DeviceBuffer<int16_t> bs;
   DeviceBuffer<__half> h;  // the codes dequantised, f16: the tensor-core kernels' operand
   bool q8k = false;
-  void alloc(uint64_t rows, uint32_t K, bool k, bool with_f16) {
-    q8k = k;
+  uint32_t K = 0;
+  void alloc(uint64_t rows, uint32_t Kv, bool k, bool with_f16) {
+    q8k = k, K = Kv;
     q.alloc(rows * K);
     d.alloc(rows * (k ? K / 256 : K / 32));
     if (k) bs.alloc(rows * (K / 16));
     if (with_f16) h.alloc(rows * K);
   }
-  ActView view(uint64_t row0, uint32_t K) const {
-    return ActView{q.get() + row0 * K, d.get() + row0 * (q8k ? K / 256 : K / 32), q8k ? bs.get() + row0 * (K / 16) : nullptr};
+  ActView view(uint64_t row0 = 0) const {
+    const uint32_t dn = q8k ? K / 256 : K / 32;
+    return ActView{q.get() + row0 * K, d.get() + row0 * dn, q8k ? bs.get() + row0 * (K / 16) : nullptr, K, dn * 4, K / 8};
   }
 };
 
+// Where a call's expert kernels read their activation rows: int8 rows for the integer-dot kernels, f16 rows for the
+// tensor-core kernels, and the map from an expert-order row to its activation row (null: the same row).
+struct ActSource {
+  ActView view;
+  const __half *h;
+  const uint32_t *act_row;
+};
+
+// One pack: `rows` assignments sorted by expert over `nexp` experts.
+struct PackBuffers {
+  DeviceBuffer<uint32_t> chunk_hist, chunk_off, cnt, base, counters, inv, row_src;
+  DeviceBuffer<MoeTile> tiles;
+  DeviceBuffer<MoeGroup> groups;
+  DeviceBuffer<BigTile> big;
+  uint32_t nexp = 0;
+  void alloc(uint64_t max_rows, uint32_t n, uint32_t chunk_len) {
+    nexp = n;
+    const uint64_t nchunks = (max_rows + chunk_len - 1) / chunk_len + 1;
+    chunk_hist.alloc(nchunks * n), chunk_off.alloc(nchunks * n);
+    cnt.alloc(n), base.alloc(n), counters.alloc(8), inv.alloc(max_rows), row_src.alloc(max_rows);
+    tiles.alloc(max_rows / kTileRows + n), groups.alloc(max_rows / kGroupMax + n), big.alloc(max_rows / kTileN + n);
+  }
+  PackOut out() const { return PackOut{cnt.get(), base.get(), chunk_off.get(), tiles.get(), groups.get(), big.get(), counters.get()}; }
+};
+
 enum Stage { ST_QUANT, ST_ROUTER, ST_PACK, ST_GATE_UP, ST_DOWN, ST_SHARED, ST_COMBINE, ST_COPIES };
+constexpr uint32_t kLocalChunk = 512;  // entries per chunk when packing rows that came from other GPUs
 
 }  // namespace moe
 
@@ -84,7 +112,8 @@ using namespace moe;
 struct moe_layer {
   moe_layer_config cfg{};
   uint32_t E = 0, F = 0, NE = 0, K = 0, N = 0, local = 0, Tmax = 0;
-  bool has_shared = false, profile = false;
+  uint64_t Rmax = 0;  // expert rows a call may bring: max_tokens * n_used, or max_expert_rows
+  bool has_shared = false, profile = false, can_tensor = false;
   std::unique_ptr<Stream> stream;
   // Weights.
   DeviceBuffer<float> router, bias;
@@ -93,15 +122,14 @@ struct moe_layer {
   uint64_t gate_slice = 0, down_slice = 0;
   // A call's buffers.
   DeviceBuffer<float> x, out, rl, w, gs, h, y, s;
-  DeviceBuffer<int32_t> ids;
-  DeviceBuffer<uint32_t> chunk_hist, chunk_off, cnt, base, counters, inv, row_src, error;
-  DeviceBuffer<MoeTile> tiles;
-  DeviceBuffer<MoeGroup> groups;
-  DeviceBuffer<BigTile> big;
-  uint32_t tensor_min = 0;  // rows from which an expert goes to the tensor-core kernels; 0: never
+  DeviceBuffer<int32_t> ids, ids_local;
+  DeviceBuffer<uint32_t> error;
+  DeviceBuffer<__half> wire_h;  // rows from other GPUs, dequantised for the tensor-core kernels
+  PackBuffers pack, pack_local;  // the step's own rows over every expert; the rows received, over this GPU's experts
   ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
   bool shared_x_same = true, rows_attr_set = false, shared_on_tensor = false;
-  uint32_t last_T = 0;
+  uint32_t last_T = 0, last_tensor_min = 0;
+  PackBuffers *last_pack = nullptr;
   // Profiling: one event before each stage and one after the last.
   std::vector<std::unique_ptr<Event>> ev;
   bool ev_valid = false;
@@ -160,12 +188,15 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->Tmax = c.max_tokens ? c.max_tokens : 4352;
   l->has_shared = c.shexp_gate_type != 0;
   l->profile = c.flags & MOE_FLAG_PROFILE;
-  l->tensor_min = (c.flags & MOE_FLAG_NO_TENSOR) ? 0 : (c.tensor_min_rows ? c.tensor_min_rows : 16);
-  if (l->tensor_min && (c.n_embd % kTileK || c.n_ff % kTileM)) l->tensor_min = 0;
+  l->can_tensor = !(c.flags & MOE_FLAG_NO_TENSOR) && c.n_embd % kTileK == 0 && c.n_ff % kTileM == 0;
   l->stream = std::make_unique<Stream>();
   cudaStream_t st = l->stream->get();
   const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, T = l->Tmax;
   const uint64_t A = (uint64_t)T * K;
+  const bool ep = l->local != NE;
+  l->Rmax = c.max_expert_rows ? c.max_expert_rows : A;
+  if (l->Rmax < A && !ep) l->Rmax = A;
+  const uint64_t R = l->Rmax;
 
   // The router's rows, then the shared expert's gate vector as row NE (zeros without one).
   std::vector<float> rw((size_t)l->N * E, 0.0f);
@@ -192,55 +223,60 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
     upload_matrix(l->sd, c.shexp_down_type, w.down_shexp, (uint64_t)E * (F / block_values(c.shexp_down_type)), 1, st);
   }
 
-  const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
   l->x.alloc((size_t)T * E), l->out.alloc((size_t)T * E);
-  l->rl.alloc((size_t)T * l->N), l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T);
-  l->chunk_hist.alloc((size_t)nchunks * NE), l->chunk_off.alloc((size_t)nchunks * NE);
-  l->cnt.alloc(NE), l->base.alloc(NE), l->counters.alloc(8), l->inv.alloc(A), l->row_src.alloc(A), l->error.alloc(1);
-  l->tiles.alloc(A / kTileRows + NE), l->groups.alloc(A / kGroupMax + NE), l->big.alloc(A / kTileN + NE);
-  l->h.alloc((A + T) * F), l->y.alloc(A * E);
-  const bool f16 = l->tensor_min != 0;
-  l->xq_routed.alloc(T, E, act_is_q8k(c.gate_type), f16);
-  l->hq_routed.alloc(A, F, act_is_q8k(c.down_type), f16);
+  l->rl.alloc((size_t)T * l->N), l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T), l->error.alloc(1);
+  l->pack.alloc(A, NE, kChunkTokens * K);
+  if (ep) {
+    l->pack_local.alloc(R, l->local, kLocalChunk);
+    l->ids_local.alloc(R);
+    if (l->can_tensor) l->wire_h.alloc(R * E);
+  }
+  l->h.alloc((R + T) * F), l->y.alloc(R * E);
+  l->xq_routed.alloc(T, E, act_is_q8k(c.gate_type), l->can_tensor);
+  l->hq_routed.alloc(R, F, act_is_q8k(c.down_type), l->can_tensor);
   if (l->has_shared) {
     l->s.alloc((size_t)T * E);
     l->shared_x_same = act_is_q8k(c.shexp_gate_type) == act_is_q8k(c.gate_type);
-    if (!l->shared_x_same) l->xq_shared.alloc(T, E, act_is_q8k(c.shexp_gate_type), f16);
-    l->hq_shared.alloc(T, F, act_is_q8k(c.shexp_down_type), f16);
+    if (!l->shared_x_same) l->xq_shared.alloc(T, E, act_is_q8k(c.shexp_gate_type), l->can_tensor);
+    l->hq_shared.alloc(T, F, act_is_q8k(c.shexp_down_type), l->can_tensor);
   }
-  CUDA_OK(cudaMemsetAsync(l->counters.get(), 0, 8 * sizeof(uint32_t), st));
+  CUDA_OK(cudaMemsetAsync(l->pack.counters.get(), 0, 8 * sizeof(uint32_t), st));
   CUDA_OK(cudaMemsetAsync(l->error.get(), 0, sizeof(uint32_t), st));
   for (int i = 0; i <= MOE_STAGES; i++) l->ev.push_back(std::make_unique<Event>());
   CUDA_OK(cudaStreamSynchronize(st));
 }
 
-void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, const ActBuffers &dst, uint64_t row0, cudaStream_t st) {
+void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, const ActBuffers &dst, cudaStream_t st) {
   const uint64_t nblk = rows * (Kv / 256);
   if (nblk == 0) return;
-  const ActView v = dst.view(row0, Kv);
+  const ActView v = dst.view();
   const unsigned grid = (unsigned)((nblk + 7) / 8);
-  __half *deq = dst.h.get() ? dst.h.get() + row0 * Kv : nullptr;
   if (dst.q8k)
-    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, deq);
+    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get());
   else
-    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, deq);
+    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get());
   launched(l, cudaGetLastError(), "quantize");
 }
 
-// Rows a group's kernel takes at once: a group holds at most min(T, 8) rows, an expert having one row per token at most.
-int group_rows(uint32_t T) { return T > 4 ? 8 : T > 2 ? 4 : (int)T; }
+// Rows a group's kernel takes at once, for groups that hold at most n rows.
+int group_rows(uint64_t n) { return n > 4 ? 8 : n > 2 ? 4 : (int)n; }
 
-// The whole block on device buffers, queued on st.
-void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {
-  const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, N = l->N;
+// Rows from which an expert goes to the tensor-core kernels in a call of R expert rows; 0: none does. With few rows in
+// all, the step is bound by reading each expert once and the integer-dot kernels do that best; with many, every
+// expert's rows fill tensor-core tiles better than groups of 8.
+uint32_t tensor_min_for(const moe_layer *l, uint64_t R) {
+  if (!l->can_tensor) return 0;
+  if (l->cfg.tensor_min_rows) return l->cfg.tensor_min_rows;
+  return R >= 1280 ? 1 : 16;
+}
+
+// Quantise x, the router's logits and top-k, and the pack of the step's T * K assignments over every expert.
+void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
+  const uint32_t E = l->E, NE = l->NE, K = l->K, N = l->N;
   const uint64_t A = (uint64_t)T * K;
-  const moe_layer_config &c = l->cfg;
-  if (l->local != NE) throw BadArgument("this call needs every expert on the GPU; an expert-parallel layer goes stage by stage");
-
   mark(l, ST_QUANT, st);
-  quantize_rows(l, x, T, E, l->xq_routed, 0, st);
-  if (l->has_shared && !l->shared_x_same) quantize_rows(l, x, T, E, l->xq_shared, 0, st);
-
+  quantize_rows(l, x, T, E, l->xq_routed, st);
+  if (l->has_shared && !l->shared_x_same) quantize_rows(l, x, T, E, l->xq_shared, st);
   mark(l, ST_ROUTER, st);
   if (T <= 64) {
     const size_t smem = (size_t)8 * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float);
@@ -254,94 +290,121 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   }
   launched(l, cudaGetLastError(), "router logits");
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
-  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->chunk_hist.get());
+  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->pack.chunk_hist.get());
   launched(l, cudaGetLastError(), "router top-k");
-
   mark(l, ST_PACK, st);
-  const PackOut po{l->cnt.get(), l->base.get(), l->chunk_off.get(), l->tiles.get(), l->groups.get(), l->big.get(), l->counters.get()};
-  const uint32_t tm = l->tensor_min;
-  k_pack_scan<<<1, 512, 0, st>>>(l->chunk_hist.get(), nchunks, NE, c.expert_first, tm, po);
+  // On one GPU the pack also lists the groups and big tiles of the experts' kernels; expert parallel, it only sorts.
+  const uint32_t tm = l->local == NE ? tensor_min_for(l, A) : 0;
+  l->last_tensor_min = tm;
+  k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, l->pack.out());
   launched(l, cudaGetLastError(), "pack scan");
   const uint32_t chunk_len = kChunkTokens * K;
-  k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->base.get(), l->chunk_off.get(), K,
-                                                             l->inv.get(), l->row_src.get());
+  k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->pack.base.get(),
+                                                             l->pack.chunk_off.get(), K, l->pack.inv.get(), l->pack.row_src.get());
   launched(l, cudaGetLastError(), "pack fill");
+  l->last_T = T, l->last_pack = &l->pack;
+}
 
-  // The most groups and big tiles the step can have: an expert below tensor_min rows has (tensor_min - 1) / 8 + 1 groups
-  // at most, and one at or above it a tile per 256 rows and one more.
-  const int M = group_rows(tm ? std::min(T, tm - 1) : T);
+// The routed experts on the R rows a pack lists: gate/up and SwiGLU into h, h quantised, down into y (expert order).
+void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint32_t tm, float *y, cudaStream_t st) {
+  const uint32_t E = l->E, F = l->F, nexp = pk.nexp;
+  const moe_layer_config &c = l->cfg;
+  // The most groups and big tiles the rows can make: an expert below tm rows has (tm - 2) / 8 + 1 groups at most, and one
+  // at or above it a tile per 256 rows and one more.
+  const int M = group_rows(tm ? std::min<uint64_t>(R, tm - 1) : R);
   const uint32_t max_groups =
-      tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(A, (uint64_t)NE * ((tm - 2) / kGroupMax + 1)) : 0) : (uint32_t)std::min<uint64_t>(A, A / kGroupMax + NE);
-  const uint32_t max_big = tm && T >= tm ? (uint32_t)(A / kTileN + std::min<uint64_t>(NE, A / tm)) : 0;
+      tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(R, (uint64_t)nexp * ((tm - 2) / kGroupMax + 1)) : 0) : (uint32_t)std::min<uint64_t>(R, R / kGroupMax + nexp);
+  const uint32_t max_big = tm && R >= tm ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm)) : 0;
   mark(l, ST_GATE_UP, st);
   if (max_big) {
     ExpertTilesArgs a{};
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F;
-    a.act = l->xq_routed.h.get(), a.act_row = l->row_src.get();
-    a.tiles = l->big.get(), a.ntiles = l->counters.get() + 4;
+    a.act = src.h, a.act_row = src.act_row;
+    a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
     launched(l, launch_tiles(c.gate_type, 2, a, max_big, l->grid.get(), st), "experts gate/up tiles");
   }
   if (max_groups) {
     ExpertRowsArgs a{};
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F, a.rows_per_cta = 32;
-    a.act = l->xq_routed.view(0, E), a.act_row = l->row_src.get();
-    a.groups = l->groups.get(), a.ngroups = l->counters.get() + 1;
+    a.act = src.view, a.act_row = src.act_row;
+    a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
     launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
   }
-  quantize_rows(l, l->h.get(), A, F, l->hq_routed, 0, st);
+  quantize_rows(l, l->h.get(), R, F, l->hq_routed, st);
   mark(l, ST_DOWN, st);
   if (max_big) {
     ExpertTilesArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;
     a.act = l->hq_routed.h.get(), a.act_row = nullptr;
-    a.tiles = l->big.get(), a.ntiles = l->counters.get() + 4;
-    a.out = l->y.get(), a.out_stride = E, a.error = l->error.get();
+    a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
+    a.out = y, a.out_stride = E, a.error = l->error.get();
     launched(l, launch_tiles(c.down_type, 1, a, max_big, l->grid.get(), st), "experts down tiles");
   }
   if (max_groups) {
     ExpertRowsArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E, a.rows_per_cta = 128;
-    a.act = l->hq_routed.view(0, F), a.act_row = nullptr;
-    a.groups = l->groups.get(), a.ngroups = l->counters.get() + 1;
-    a.out = l->y.get(), a.out_stride = E;
+    a.act = l->hq_routed.view(), a.act_row = nullptr;
+    a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
+    a.out = y, a.out_stride = E;
     launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), st), "experts down");
   }
+}
+
+// The shared expert on the step's T rows, into s. Its h rows sit after the routed experts' in h.
+void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
   mark(l, ST_SHARED, st);
-  if (l->has_shared && tm && T >= tm) {
-    const ActBuffers &xs = l->shared_x_same ? l->xq_routed : l->xq_shared;
+  if (!l->has_shared) return;
+  const uint32_t E = l->E, F = l->F;
+  const moe_layer_config &c = l->cfg;
+  const ActBuffers &xs = l->shared_x_same ? l->xq_routed : l->xq_shared;
+  float *hs = l->h.get() + l->Rmax * F;
+  if (l->can_tensor && T >= (l->cfg.tensor_min_rows ? l->cfg.tensor_min_rows : 16)) {
     const uint32_t dense_tiles = (T + kTileN - 1) / kTileN;
     ExpertTilesArgs a{};
     a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.act = xs.h.get(), a.dense_rows = T;
-    a.out = l->h.get() + A * F, a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
+    a.out = hs, a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
     launched(l, launch_tiles(c.shexp_gate_type, 2, a, dense_tiles, l->grid.get(), st), "shared gate/up tiles");
-    quantize_rows(l, l->h.get() + A * F, T, F, l->hq_shared, 0, st);
+    quantize_rows(l, hs, T, F, l->hq_shared, st);
     ExpertTilesArgs b{};
     b.w0 = l->sd.get(), b.K = F, b.R = E, b.act = l->hq_shared.h.get(), b.dense_rows = T;
     b.out = l->s.get(), b.out_stride = E, b.error = l->error.get();
     launched(l, launch_tiles(c.shexp_down_type, 1, b, dense_tiles, l->grid.get(), st), "shared down tiles");
     l->shared_on_tensor = true;
-  } else if (l->has_shared) {
-    l->shared_on_tensor = false;
-    const int M = group_rows(T);
-    const uint32_t dense_groups = (T + M - 1) / M;
-    ExpertRowsArgs a{};
-    a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.rows_per_cta = 32;
-    a.act = (l->shared_x_same ? l->xq_routed : l->xq_shared).view(0, E);
-    a.dense_rows = T, a.out = l->h.get() + A * F, a.out_stride = F, a.limit = c.swiglu_limit;
-    launched(l, launch_rows(c.shexp_gate_type, 2, a, M, dense_groups, l->grid.get(), st), "shared gate/up");
-    quantize_rows(l, l->h.get() + A * F, T, F, l->hq_shared, 0, st);
-    ExpertRowsArgs b{};
-    b.w0 = l->sd.get(), b.K = F, b.R = E, b.rows_per_cta = 128;
-    b.act = l->hq_shared.view(0, F), b.dense_rows = T, b.out = l->s.get(), b.out_stride = E;
-    launched(l, launch_rows(c.shexp_down_type, 1, b, M, dense_groups, l->grid.get(), st), "shared down");
+    return;
   }
+  l->shared_on_tensor = false;
+  const int M = group_rows(T);
+  const uint32_t dense_groups = (T + M - 1) / M;
+  ExpertRowsArgs a{};
+  a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.rows_per_cta = 32;
+  a.act = xs.view(), a.dense_rows = T, a.out = hs, a.out_stride = F, a.limit = c.swiglu_limit;
+  launched(l, launch_rows(c.shexp_gate_type, 2, a, M, dense_groups, l->grid.get(), st), "shared gate/up");
+  quantize_rows(l, hs, T, F, l->hq_shared, st);
+  ExpertRowsArgs b{};
+  b.w0 = l->sd.get(), b.K = F, b.R = E, b.rows_per_cta = 128;
+  b.act = l->hq_shared.view(), b.dense_rows = T, b.out = l->s.get(), b.out_stride = E;
+  launched(l, launch_rows(c.shexp_down_type, 1, b, M, dense_groups, l->grid.get(), st), "shared down");
+}
+
+template <class Y>
+void stage_combine(moe_layer *l, const Y *y, uint32_t T, float *out, cudaStream_t st) {
   mark(l, ST_COMBINE, st);
-  k_combine<<<T, 256, 0, st>>>(l->y.get(), l->inv.get(), l->w.get(), l->gs.get(), l->has_shared ? l->s.get() : nullptr, K, E, out);
+  k_combine<Y><<<T, 256, 0, st>>>(y, l->pack.inv.get(), l->w.get(), l->gs.get(), l->has_shared ? l->s.get() : nullptr, l->K, l->E, out);
   launched(l, cudaGetLastError(), "combine");
   mark(l, ST_COPIES, st);
-  l->last_T = T;
+}
+
+// The whole block on device buffers, queued on st: a GPU that holds every expert.
+void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {
+  if (l->local != l->NE) throw BadArgument("this call needs every expert on the GPU; an expert-parallel layer goes stage by stage");
+  const uint64_t A = (uint64_t)T * l->K;
+  stage_route(l, x, T, st);
+  const ActSource src{l->xq_routed.view(), l->xq_routed.h.get(), l->pack.row_src.get()};
+  stage_experts(l, src, l->pack, A, l->last_tensor_min, l->y.get(), st);
+  stage_shared(l, T, st);
+  stage_combine<float>(l, l->y.get(), T, out, st);
   l->stats.calls++, l->stats.rows += T, l->stats.assignments += A;
 }
 
@@ -357,7 +420,7 @@ void check_device_error(moe_layer *l) {
 
 void read_counters(moe_layer *l) {
   uint32_t c[8];
-  CUDA_OK(cudaMemcpy(c, l->counters.get(), sizeof(c), cudaMemcpyDeviceToHost));
+  CUDA_OK(cudaMemcpy(c, l->last_pack->counters.get(), sizeof(c), cudaMemcpyDeviceToHost));
   l->stats.last_tiles = c[0], l->stats.last_experts_hit = c[2];
   l->stats.last_tensor_rows = c[5] + (l->shared_on_tensor ? l->last_T : 0);
 }
@@ -432,6 +495,119 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
   });
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Expert parallel, stage by stage. The caller moves the rows between GPUs (all-to-all) between the stages.
+
+MOE_API moe_status moe_layer_route_device(moe_layer *l, const float *x_dev, uint32_t T, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!x_dev || T == 0 || T > l->Tmax) throw BadArgument("x is required, and 1 <= T <= max_tokens");
+    stage_route(l, x_dev, T, stream ? (cudaStream_t)stream : l->stream->get());
+    l->stats.calls++, l->stats.rows += T, l->stats.assignments += (uint64_t)T * l->K;
+  });
+}
+
+MOE_API moe_status moe_layer_read_counts(moe_layer *l, uint32_t *cnt, void *stream) {
+  if (!l || !cnt) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    CUDA_OK(cudaMemcpyAsync(cnt, l->pack.cnt.get(), l->NE * sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    Stream::wait_on(st, 0);
+  });
+}
+
+MOE_API moe_status moe_layer_counts_device(moe_layer *l, uint32_t *cnt_dev, void *stream) {
+  if (!l || !cnt_dev) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    CUDA_OK(cudaMemcpyAsync(cnt_dev, l->pack.cnt.get(), l->NE * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
+  });
+}
+
+MOE_API uint32_t moe_layer_wire_row_bytes(const moe_layer *l) { return l ? wire_row_bytes(act_is_q8k(l->cfg.gate_type), l->E) : 0; }
+
+MOE_API moe_status moe_layer_gather_rows_device(moe_layer *l, void *rows_dev, int32_t *ids_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!rows_dev || !ids_dev || l->last_T == 0) throw BadArgument("rows and ids are required, after moe_layer_route_device");
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    const uint32_t A = l->last_T * l->K;
+    k_gather_wire<<<(A + 7) / 8, 256, 0, st>>>(l->xq_routed.view(), l->E, l->xq_routed.q8k, l->pack.row_src.get(), l->pack.inv.get(),
+                                             l->ids.get(), A, (uint8_t *)rows_dev, ids_dev);
+    launched(l, cudaGetLastError(), "gather rows");
+  });
+}
+
+MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, const int32_t *ids_dev, uint32_t R, void *y_dev,
+                                            uint32_t y_f16, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->local == l->NE) throw BadArgument("this layer holds every expert: use moe_layer_forward_device");
+    if (R > l->Rmax) throw BadArgument("more rows than max_expert_rows");
+    if (R == 0) return;
+    if (!rows_dev || !ids_dev || !y_dev) throw BadArgument("rows, ids and y are required");
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    const uint32_t E = l->E, nexp = l->local;
+    const bool q8k = l->xq_routed.q8k;
+    const uint32_t wb = wire_row_bytes(q8k, E), tm = tensor_min_for(l, R);
+    // Sort the rows by expert among this GPU's experts: a stable pack, chunks of 512 entries.
+    PackBuffers &pk = l->pack_local;
+    const uint32_t nchunks = (R + kLocalChunk - 1) / kLocalChunk;
+    k_chunk_hist<<<nchunks, 256, 0, st>>>(ids_dev, R, kLocalChunk, nexp, l->cfg.expert_first, pk.chunk_hist.get());
+    launched(l, cudaGetLastError(), "local counts");
+    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, pk.out());
+    launched(l, cudaGetLastError(), "local pack scan");
+    k_pack_fill<<<nchunks, 512, kLocalChunk * sizeof(int32_t), st>>>(ids_dev, R, kLocalChunk, nexp, pk.base.get(), pk.chunk_off.get(), 1,
+                                                                 pk.inv.get(), pk.row_src.get(), l->cfg.expert_first);
+    launched(l, cudaGetLastError(), "local pack fill");
+    const uint8_t *wire = (const uint8_t *)rows_dev;
+    const uint32_t dbytes = q8k ? E / 64 : E / 8;
+    ActSource src{ActView{(const int8_t *)wire, (const float *)(wire + E), (const int16_t *)(wire + E + dbytes), wb, wb, wb}, nullptr,
+                  pk.row_src.get()};
+    if (tm) {
+      const uint64_t nblk = (uint64_t)R * (E / 256);
+      k_wire_to_f16<<<(unsigned)((nblk + 7) / 8), 256, 0, st>>>(wire, E, q8k, nblk, l->wire_h.get());
+      launched(l, cudaGetLastError(), "wire rows to f16");
+      src.h = l->wire_h.get();
+    }
+    l->last_pack = &pk;
+    stage_experts(l, src, pk, R, tm, l->y.get(), st);
+    if (y_f16)
+      k_unpermute<__half><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (__half *)y_dev);
+    else
+      k_unpermute<float><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (float *)y_dev);
+    launched(l, cudaGetLastError(), "rows back in arrival order");
+  });
+}
+
+MOE_API moe_status moe_layer_shared_device(moe_layer *l, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T == 0) throw BadArgument("after moe_layer_route_device");
+    stage_shared(l, l->last_T, stream ? (cudaStream_t)stream : l->stream->get());
+  });
+}
+
+MOE_API moe_status moe_layer_combine_device(moe_layer *l, const void *y_dev, uint32_t y_f16, float *out_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!y_dev || !out_dev || l->last_T == 0) throw BadArgument("y and out are required, after moe_layer_route_device");
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    if (y_f16)
+      stage_combine<__half>(l, (const __half *)y_dev, l->last_T, out_dev, st);
+    else
+      stage_combine<float>(l, (const float *)y_dev, l->last_T, out_dev, st);
+    if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
+  });
+}
+
 MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms) {
   if (!l) return MOE_BAD_ARGUMENT;
   return guarded(l, [&] {
@@ -449,15 +625,15 @@ MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, ui
     cudaStream_t st = l->stream->get();
     const size_t A = (size_t)l->last_T * l->K;
     uint32_t counters[8];
-    CUDA_OK(cudaMemcpyAsync(counters, l->counters.get(), sizeof(counters), cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaMemcpyAsync(counters, l->pack.counters.get(), sizeof(counters), cudaMemcpyDeviceToHost, st));
     if (ids) CUDA_OK(cudaMemcpyAsync(ids, l->ids.get(), A * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
     if (w) CUDA_OK(cudaMemcpyAsync(w, l->w.get(), A * sizeof(float), cudaMemcpyDeviceToHost, st));
-    if (inv) CUDA_OK(cudaMemcpyAsync(inv, l->inv.get(), A * sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    if (inv) CUDA_OK(cudaMemcpyAsync(inv, l->pack.inv.get(), A * sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
     l->stream->wait(0);
     if (tiles && tiles_cap) {
       static_assert(sizeof(moe_tile) == sizeof(MoeTile), "tile layout");
       const size_t n = std::min<size_t>(tiles_cap, counters[0]);
-      CUDA_OK(cudaMemcpyAsync(tiles, l->tiles.get(), n * sizeof(moe_tile), cudaMemcpyDeviceToHost, st));
+      CUDA_OK(cudaMemcpyAsync(tiles, l->pack.tiles.get(), n * sizeof(moe_tile), cudaMemcpyDeviceToHost, st));
       l->stream->wait(0);
     }
     if (ntiles) *ntiles = counters[0];
@@ -510,7 +686,7 @@ MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap) {
       ROW(moe_layer_config, gate_type), ROW(moe_layer_config, down_type), ROW(moe_layer_config, shexp_gate_type),
       ROW(moe_layer_config, shexp_down_type), ROW(moe_layer_config, expert_first), ROW(moe_layer_config, expert_count),
       ROW(moe_layer_config, max_tokens), ROW(moe_layer_config, device), ROW(moe_layer_config, swiglu_limit), ROW(moe_layer_config, flags),
-      ROW(moe_layer_config, tensor_min_rows), ROW(moe_layer_config, reserved),
+      ROW(moe_layer_config, tensor_min_rows), ROW(moe_layer_config, max_expert_rows),
       ROW(moe_layer_weights, router), ROW(moe_layer_weights, shexp_gate_inp), ROW(moe_layer_weights, router_bias),
       ROW(moe_layer_weights, gate_exps), ROW(moe_layer_weights, up_exps), ROW(moe_layer_weights, down_exps),
       ROW(moe_layer_weights, gate_shexp), ROW(moe_layer_weights, up_shexp), ROW(moe_layer_weights, down_shexp),

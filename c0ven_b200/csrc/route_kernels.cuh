@@ -159,7 +159,7 @@ static __global__ void __launch_bounds__(128) k_router_logits_rows(const float *
 
 // Many rows: a 128 x 64 tile of (rows, experts) per CTA of 256 threads, 8 x 4 outputs a thread, 16 values of the
 // hidden size a step; the tile's partial sums fold into the totals at every piece's end.
-static __global__ void __launch_bounds__(256) k_router_logits_tiles(const float *__restrict__ x, uint32_t T, uint32_t E,
+static __global__ void __launch_bounds__(256, 2) k_router_logits_tiles(const float *__restrict__ x, uint32_t T, uint32_t E,
                                                             const float *__restrict__ W, uint32_t N,
                                                             const float *__restrict__ bias, uint32_t NE,
                                                             float *__restrict__ rl) {
@@ -172,19 +172,19 @@ static __global__ void __launch_bounds__(256) k_router_logits_tiles(const float 
   for (int i = 0; i < 8; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) p[i][j] = 0.0f, tot[i][j] = 0.0f;
-  // A thread's loads: two float4 of x (rows am, am + 64; values 4 * aq ..), one of W (row bn; values 4 * bq ..).
-  const uint32_t am = tid / 4, aq = tid % 4, bn = tid / 4, bq = tid % 4;
+  // A thread's loads: two float4 of x (row am, values 4 * aq .. and 4 * (aq + 2) ..), one of W (row bn; values 4 * bq ..).
+  // A warp's lanes hold consecutive rows, so its transposed stores fill consecutive banks.
+  const uint32_t am = tid % 128, aq = tid / 128, bn = tid % 64, bq = tid / 64;
   float4 ra0, ra1, rb;
   auto fetch = [&](uint32_t k0) {
-    const uint32_t r0 = m0 + am, r1 = m0 + am + 64, e = n0 + bn;
-    ra0 = r0 < T ? *(const float4 *)(x + (uint64_t)r0 * E + k0 + 4 * aq) : make_float4(0, 0, 0, 0);
-    ra1 = r1 < T ? *(const float4 *)(x + (uint64_t)r1 * E + k0 + 4 * aq) : make_float4(0, 0, 0, 0);
+    const uint32_t r = m0 + am, e = n0 + bn;
+    ra0 = r < T ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * aq)) : make_float4(0, 0, 0, 0);
+    ra1 = r < T ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * (aq + 2))) : make_float4(0, 0, 0, 0);
     rb = e < N ? __ldg((const float4 *)(W + (uint64_t)e * E + k0 + 4 * bq)) : make_float4(0, 0, 0, 0);
   };
   auto stash = [&](int buf) {
     As[buf][4 * aq + 0][am] = ra0.x, As[buf][4 * aq + 1][am] = ra0.y, As[buf][4 * aq + 2][am] = ra0.z, As[buf][4 * aq + 3][am] = ra0.w;
-    As[buf][4 * aq + 0][am + 64] = ra1.x, As[buf][4 * aq + 1][am + 64] = ra1.y, As[buf][4 * aq + 2][am + 64] = ra1.z,
-                      As[buf][4 * aq + 3][am + 64] = ra1.w;
+    As[buf][4 * aq + 8][am] = ra1.x, As[buf][4 * aq + 9][am] = ra1.y, As[buf][4 * aq + 10][am] = ra1.z, As[buf][4 * aq + 11][am] = ra1.w;
     Bs[buf][4 * bq + 0][bn] = rb.x, Bs[buf][4 * bq + 1][bn] = rb.y, Bs[buf][4 * bq + 2][bn] = rb.z, Bs[buf][4 * bq + 3][bn] = rb.w;
   };
   fetch(0);
@@ -318,12 +318,15 @@ static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const 
 // The same counts for expert ids that come from elsewhere (the rows another GPU sent): chunk c holds entries
 // [c * chunk_len, (c + 1) * chunk_len) of ids.
 static __global__ void __launch_bounds__(256) k_chunk_hist(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len,
-                                                   uint32_t NE, uint32_t *__restrict__ chunk_hist) {
+                                                   uint32_t NE, uint32_t first_expert, uint32_t *__restrict__ chunk_hist) {
   __shared__ uint32_t hist[512];
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
   __syncthreads();
   const uint32_t a0 = blockIdx.x * chunk_len, a1 = min(A, a0 + chunk_len);
-  for (uint32_t a = a0 + threadIdx.x; a < a1; a += blockDim.x) atomicAdd(&hist[ids[a]], 1u);
+  for (uint32_t a = a0 + threadIdx.x; a < a1; a += blockDim.x) {
+    const uint32_t e = (uint32_t)ids[a] - first_expert;
+    if (e < NE) atomicAdd(&hist[e], 1u);
+  }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
 }
@@ -395,7 +398,8 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
 // order. inv[a] = row; row_src[row] = a / src_div (the activation row the assignment reads: its token).
 static __global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restrict__ ids, uint32_t A, uint32_t chunk_len, uint32_t NE,
                                                   const uint32_t *__restrict__ base, const uint32_t *__restrict__ chunk_off,
-                                                  uint32_t src_div, uint32_t *__restrict__ inv, uint32_t *__restrict__ row_src) {
+                                                  uint32_t src_div, uint32_t *__restrict__ inv, uint32_t *__restrict__ row_src,
+                                                  uint32_t first_expert = 0) {
   extern __shared__ int32_t s_ids[];
   const uint32_t a0 = blockIdx.x * chunk_len, n = min(A, a0 + chunk_len) - a0;
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) s_ids[i] = ids[a0 + i];
@@ -404,7 +408,7 @@ static __global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restr
   if (e >= NE) return;
   uint32_t row = base[e] + chunk_off[(uint64_t)blockIdx.x * NE + e];
   for (uint32_t i = 0; i < n; i++)
-    if ((uint32_t)s_ids[i] == e) {
+    if ((uint32_t)s_ids[i] - first_expert == e) {
       inv[a0 + i] = row;
       row_src[row] = (a0 + i) / src_div;
       row++;
@@ -413,10 +417,17 @@ static __global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restr
 
 // ---------------------------------------------------------------------------------------------------------------
 // Combine: out[t] = sum over k, in rank order, of w[t][k] * y[inv[t K + k]] + gs[t] * s[t], in f32 (layer.cl:874-877).
-// One CTA per row.
-static __global__ void __launch_bounds__(256) k_combine(const float *__restrict__ y, const uint32_t *__restrict__ inv,
-                                                const float *__restrict__ w, const float *__restrict__ gs,
-                                                const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out) {
+// One CTA per row. y is f32, or f16 when it came back from other GPUs in that form.
+__device__ __forceinline__ float4 load_row4(const float *y, uint64_t row, uint32_t E, uint32_t i) { return ((const float4 *)(y + row * E))[i]; }
+__device__ __forceinline__ float4 load_row4(const __half *y, uint64_t row, uint32_t E, uint32_t i) {
+  const uint2 u = ((const uint2 *)(y + row * E))[i];
+  const float2 a = __half22float2(*(const __half2 *)&u.x), b = __half22float2(*(const __half2 *)&u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <class Y>
+static __global__ void __launch_bounds__(256) k_combine(const Y *__restrict__ y, const uint32_t *__restrict__ inv,
+                                                       const float *__restrict__ w, const float *__restrict__ gs,
+                                                       const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out) {
   const uint32_t t = blockIdx.x;
   __shared__ uint32_t rows[16];
   __shared__ float wk[16];
@@ -426,7 +437,7 @@ static __global__ void __launch_bounds__(256) k_combine(const float *__restrict_
   for (uint32_t i = threadIdx.x; i < E / 4; i += 256) {
     float4 acc = make_float4(0, 0, 0, 0);
     for (uint32_t k = 0; k < K; k++) {
-      const float4 v = ((const float4 *)(y + (uint64_t)rows[k] * E))[i];
+      const float4 v = load_row4(y, rows[k], E, i);
       acc.x = fmaf(wk[k], v.x, acc.x), acc.y = fmaf(wk[k], v.y, acc.y);
       acc.z = fmaf(wk[k], v.z, acc.z), acc.w = fmaf(wk[k], v.w, acc.w);
     }
@@ -435,6 +446,71 @@ static __global__ void __launch_bounds__(256) k_combine(const float *__restrict_
       acc.x = fmaf(g, v.x, acc.x), acc.y = fmaf(g, v.y, acc.y), acc.z = fmaf(g, v.z, acc.z), acc.w = fmaf(g, v.w, acc.w);
     }
     ((float4 *)(out + (uint64_t)t * E))[i] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Expert parallel: the rows that cross GPUs. A wire row is one quantised activation row packed: K codes, its scales,
+// q8_K's sums, padded to 16 bytes.
+__host__ __device__ constexpr uint32_t wire_row_bytes(bool q8k, uint32_t K) { return (K + (q8k ? K / 64 + K / 8 : K / 8) + 15) & ~15u; }
+
+// wire[r] = the quantised row of the token assignment row r reads (row_src[r]); ids_sorted[r] = its expert. One warp
+// per row.
+static __global__ void __launch_bounds__(256) k_gather_wire(const ActView act, uint32_t K, bool q8k, const uint32_t *__restrict__ row_src,
+                                                           const uint32_t *__restrict__ inv, const int32_t *__restrict__ ids, uint32_t A,
+                                                           uint8_t *__restrict__ wire, int32_t *__restrict__ ids_sorted) {
+  const uint32_t lane = threadIdx.x % 32;
+  const uint64_t r = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
+  if (r >= A) return;
+  const uint32_t wb = wire_row_bytes(q8k, K), t = row_src[r], dbytes = q8k ? K / 64 : K / 8;
+  uint8_t *dst = wire + r * wb;
+  const int4 *q = (const int4 *)(act.q + (uint64_t)t * act.q_stride);
+  for (uint32_t i = lane; i < K / 16; i += 32) ((int4 *)dst)[i] = q[i];
+  const uint32_t *d = (const uint32_t *)((const uint8_t *)act.d + (uint64_t)t * act.d_stride);
+  for (uint32_t i = lane; i < dbytes / 4; i += 32) ((uint32_t *)(dst + K))[i] = d[i];
+  if (q8k) {
+    const uint32_t *b = (const uint32_t *)((const uint8_t *)act.bs + (uint64_t)t * act.bs_stride);
+    for (uint32_t i = lane; i < K / 32; i += 32) ((uint32_t *)(dst + K + dbytes))[i] = b[i];
+  }
+  // The ids in expert order: assignment a sits at row inv[a]. Here r also counts the assignments.
+  if (lane == 0) ids_sorted[inv[r]] = ids[r];
+}
+
+// The f16 operand of the tensor-core kernels from wire rows: code * scale, as the quantisers write it. One warp per
+// 256 values.
+static __global__ void __launch_bounds__(256) k_wire_to_f16(const uint8_t *__restrict__ wire, uint32_t K, bool q8k, uint64_t nblk256,
+                                                           __half *__restrict__ out) {
+  const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
+  if (blk >= nblk256) return;
+  const uint32_t lane = threadIdx.x % 32, per_row = K / 256, wb = wire_row_bytes(q8k, K);
+  const uint64_t row = blk / per_row;
+  const uint32_t b = (uint32_t)(blk % per_row);
+  const uint8_t *src = wire + row * wb;
+  const char4 lo = ((const char4 *)(src + 256 * b))[2 * lane], hi = ((const char4 *)(src + 256 * b))[2 * lane + 1];
+  const float d = q8k ? ((const float *)(src + K))[b] : ((const float *)(src + K))[8 * b + lane / 4];
+  const __half2 h0 = __floats2half2_rn(d * (float)lo.x, d * (float)lo.y), h1 = __floats2half2_rn(d * (float)lo.z, d * (float)lo.w);
+  const __half2 h2 = __floats2half2_rn(d * (float)hi.x, d * (float)hi.y), h3 = __floats2half2_rn(d * (float)hi.z, d * (float)hi.w);
+  uint4 o;
+  o.x = *(const uint32_t *)&h0, o.y = *(const uint32_t *)&h1, o.z = *(const uint32_t *)&h2, o.w = *(const uint32_t *)&h3;
+  ((uint4 *)(out + row * K + 256 * b))[lane] = o;
+}
+
+// out[r] = y[inv[r]]: the experts' rows back in the order they arrived, as f32 or f16. One CTA per row.
+template <class O>
+static __global__ void __launch_bounds__(256) k_unpermute(const float *__restrict__ y, const uint32_t *__restrict__ inv, uint32_t E,
+                                                         O *__restrict__ out) {
+  const uint64_t r = blockIdx.x;
+  const float4 *src = (const float4 *)(y + (uint64_t)inv[r] * E);
+  for (uint32_t i = threadIdx.x; i < E / 4; i += 256) {
+    const float4 v = src[i];
+    if constexpr (sizeof(O) == 4) {
+      ((float4 *)(out + r * E))[i] = v;
+    } else {
+      const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+      uint2 o;
+      o.x = *(const uint32_t *)&a, o.y = *(const uint32_t *)&b;
+      ((uint2 *)(out + r * E))[i] = o;
+    }
   }
 }
 

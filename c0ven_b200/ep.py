@@ -1,0 +1,150 @@
+"""Expert parallel over the GPUs of one node: one process per GPU, each holding a contiguous range of the experts, the
+router and the shared expert replicated, the rows sharded. A step routes its own rows, sends each assignment's
+quantised activation row to the GPU that owns its expert (all-to-all), runs its experts on the rows it received, sends
+the results back (all-to-all) and combines them with its own shared expert. The reference has no expert parallelism
+(both its cards hold the same experts: docs/DESIGN.md:294-297); its two cards exchange partial sums instead
+(core/models/qwen4exp/model.cpp:1404-1418).
+
+The collectives are torch.distributed's (NCCL over NVLink on GPUs): per step one all-gather of the ranks' per-expert row
+counts (from which every rank knows what it sends, what it receives and which expert each received row is for, so no
+ids travel), one all-to-all of rows out and one of results back; one wait on the host, for the split sizes. The
+stages between them are the C ABI's moe_layer_*_device calls, behind a small backend object so that the exchange logic
+also runs on CPU ranks (gloo) in the tests, with a CPU stand-in for the stages.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def owner_ranges(n_experts: int, world: int):
+    """Experts [first, first + count) of every rank: equal contiguous ranges."""
+    if n_experts % world:
+        raise ValueError("the experts must divide evenly over the ranks")
+    per = n_experts // world
+    return [(r * per, per) for r in range(world)]
+
+
+def split_sizes(cnt_all: np.ndarray, rank: int):
+    """From every rank's rows per expert, cnt_all [world][n_experts]: the rows this rank sends to each rank and receives
+    from each rank."""
+    world, ne = cnt_all.shape
+    per = ne // world
+    by_owner = cnt_all.reshape(world, world, per).sum(-1)  # [source][owner]
+    return [int(v) for v in by_owner[rank]], [int(v) for v in by_owner[:, rank]]
+
+
+def received_ids(cnt_all: np.ndarray, rank: int) -> np.ndarray:
+    """The expert of every row this rank receives: source by source, each source's rows in expert order."""
+    world, ne = cnt_all.shape
+    per = ne // world
+    mine = cnt_all[:, rank * per:(rank + 1) * per].astype(np.int64)  # [source][local expert]
+    return np.repeat(np.tile(np.arange(rank * per, (rank + 1) * per, dtype=np.int32), world), mine.reshape(-1))
+
+
+class GpuStages:
+    """The stages on a GPU, through the C ABI."""
+
+    def __init__(self, layer: dict, rank: int, world: int, max_tokens: int, device: int, max_expert_rows: int = 0,
+                 y_f16: bool = True, profile: bool = False, tensor_min_rows: int = 0):
+        from .layer import MoELayer
+
+        first, count = owner_ranges(layer["n_experts"], world)[rank]
+        self.device = torch.device("cuda", device)
+        self.y_dtype = torch.float16 if y_f16 else torch.float32
+        self.n_embd, self.n_used, self.n_experts = layer["n_embd"], layer["n_used"], layer["n_experts"]
+        self.moe = MoELayer(layer, max_tokens=max_tokens, device=device, expert_first=first, expert_count=count,
+                            max_expert_rows=max_expert_rows or max_tokens * layer["n_used"] * world, profile=profile,
+                            tensor_min_rows=tensor_min_rows)
+        self.stream = torch.cuda.ExternalStream(self.moe.stream, device=self.device)
+        self.wire = self.moe.wire_row_bytes
+        self._bufs = {}
+
+    def route(self, x: torch.Tensor) -> torch.Tensor:
+        """Routes and packs x's rows; returns the rows per expert, an int32 tensor [n_experts] on the device."""
+        self.T = x.shape[0]
+        self.moe.route_device(x.data_ptr(), self.T)
+        cnt = self.empty((self.n_experts,), torch.int32, "cnt")
+        self.moe.counts_device(cnt.data_ptr())
+        return cnt
+
+    def gather(self) -> torch.Tensor:
+        rows = self.empty((self.T * self.n_used, self.wire), torch.uint8, "rows")
+        ids = self.empty((self.T * self.n_used,), torch.int32, "ids")
+        self.moe.gather_rows_device(rows.data_ptr(), ids.data_ptr())
+        return rows
+
+    def experts(self, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        R = rows.shape[0]
+        y = self.empty((R, self.n_embd), self.y_dtype, "y_in")
+        if R:
+            self.moe.experts_device(rows.data_ptr(), ids.data_ptr(), R, y.data_ptr(), self.y_dtype == torch.float16)
+        return y
+
+    def shared(self):
+        self.moe.shared_device()
+
+    def combine(self, y: torch.Tensor, out: torch.Tensor):
+        self.moe.combine_device(y.data_ptr(), y.dtype == torch.float16, out.data_ptr())
+
+    def empty(self, shape, dtype, name=None):
+        """A device tensor; with a name, a view of a buffer kept and grown between steps."""
+        if name is None:
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        n = int(np.prod(shape)) if len(shape) else 1
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            buf = torch.empty(max(n, 1) + max(n, 1) // 4, dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n].view(shape)
+
+    def to_device(self, a: np.ndarray) -> torch.Tensor:
+        return torch.from_numpy(a).to(self.device, non_blocking=True)
+
+    def sync(self):
+        self.moe.sync()
+
+    def close(self):
+        self._bufs.clear()
+        self.moe.close()
+
+
+class ExpertParallelMoE:
+    """One MoE layer over the process group's ranks. forward() takes this rank's rows and returns their outputs."""
+
+    def __init__(self, stages, group=None):
+        self.st, self.group = stages, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.sent_rows = self.received_rows = 0
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        st, W = self.st, self.world
+        with torch.cuda.stream(st.stream) if hasattr(st, "stream") else _null():
+            cnt = st.route(x)
+            cnt_all = st.empty((W * cnt.numel(),), cnt.dtype, "cnt_all")
+            dist.all_gather_into_tensor(cnt_all, cnt, group=self.group)
+            counts = cnt_all.cpu().numpy().reshape(W, -1)      # the step's one wait on the host
+            send, recv = split_sizes(counts, self.rank)
+            rows = st.gather()                                 # [A][wire] in expert order = destination order
+            R = sum(recv)
+            rows_in = st.empty((R, rows.shape[1]), rows.dtype, "rows_in")
+            dist.all_to_all_single(rows_in, rows, recv, send, group=self.group)
+            ids_in = st.to_device(received_ids(counts, self.rank))
+            y_in = st.experts(rows_in, ids_in)                 # [R][E] in arrival order
+            st.shared()                                        # the shared expert needs no other GPU
+            y = st.empty((rows.shape[0], y_in.shape[1]), y_in.dtype, "y")
+            dist.all_to_all_single(y, y_in, send, recv, group=self.group)
+            if out is None:
+                out = st.empty(tuple(x.shape), torch.float32)
+            st.combine(y, out)
+        self.sent_rows, self.received_rows = sum(send) - send[self.rank], R - recv[self.rank]
+        return out
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

@@ -30,7 +30,8 @@ class MoELayer:
     """
 
     def __init__(self, layer: dict, max_tokens: int = 4352, device: int = 0, profile: bool = False,
-                 expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0):
+                 expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0,
+                 max_expert_rows: int = 0):
         self._h = None
         L = _lib.lib()
         self.n_embd, self.n_ff = layer["n_embd"], layer["n_ff"]
@@ -41,7 +42,7 @@ class MoELayer:
         cfg = _lib.Config(self.n_embd, self.n_ff, self.n_experts, self.n_used, layer["gate_type"], layer["down_type"],
                           layer["shexp_gate_type"] if has_shared else 0, layer["shexp_down_type"] if has_shared else 0,
                           expert_first, count, max_tokens, device, float(layer.get("swiglu_limit", 0.0)),
-                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, 0)
+                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, max_expert_rows)
         sl = slice(expert_first, expert_first + count)
         keep = [np.ascontiguousarray(layer["router"], dtype=np.float32),
                 np.ascontiguousarray(layer["shexp_gate_inp"], dtype=np.float32) if has_shared else None,
@@ -101,6 +102,34 @@ class MoELayer:
         n = C.c_uint32(0)
         self._check(_lib.lib().moe_layer_read_route(self._h, _ptr(ids), _ptr(w), _ptr(inv), _ptr(tiles), cap, C.byref(n)))
         return ids, w, inv, tiles[:n.value].copy()
+
+    # Expert parallel, stage by stage (device addresses; queued on `stream`, the layer's own when None).
+    def route_device(self, x_ptr: int, T: int, stream=None):
+        self._check(_lib.lib().moe_layer_route_device(self._h, x_ptr, T, stream))
+
+    def read_counts(self, stream=None) -> np.ndarray:
+        cnt = np.empty(self.n_experts, dtype=np.uint32)
+        self._check(_lib.lib().moe_layer_read_counts(self._h, _ptr(cnt), stream))
+        return cnt
+
+    def counts_device(self, cnt_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_counts_device(self._h, cnt_ptr, stream))
+
+    @property
+    def wire_row_bytes(self) -> int:
+        return _lib.lib().moe_layer_wire_row_bytes(self._h)
+
+    def gather_rows_device(self, rows_ptr: int, ids_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_gather_rows_device(self._h, rows_ptr, ids_ptr, stream))
+
+    def experts_device(self, rows_ptr: int, ids_ptr: int, R: int, y_ptr: int, y_f16: bool, stream=None):
+        self._check(_lib.lib().moe_layer_experts_device(self._h, rows_ptr, ids_ptr, R, y_ptr, int(y_f16), stream))
+
+    def shared_device(self, stream=None):
+        self._check(_lib.lib().moe_layer_shared_device(self._h, stream))
+
+    def combine_device(self, y_ptr: int, y_f16: bool, out_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_combine_device(self._h, y_ptr, int(y_f16), out_ptr, stream))
 
     def stats(self) -> dict:
         s = _lib.Stats()

@@ -61,7 +61,7 @@ typedef struct {
   uint32_t flags;             /* MOE_FLAG_* */
   uint32_t tensor_min_rows;   /* an expert with at least this many rows in a call goes to the tensor-core kernels, one
                                  with fewer to the integer-dot kernels; default 16 */
-  uint32_t reserved;
+  uint32_t max_expert_rows;   /* expert parallel: rows moe_layer_experts_device may receive; default max_tokens * n_used */
 } moe_layer_config;
 
 #define MOE_FLAG_PROFILE 1u     /* time every stage of a call with events (moe_layer_stage_ms) */
@@ -118,6 +118,30 @@ MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, f
 /* The same on DEVICE buffers, queued on the layer's stream (or on stream, a cudaStream_t, when not null); returns
  * without waiting. */
 MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, uint32_t T, float *out_dev, void *stream);
+
+/* Expert parallel: a layer created with fewer than n_experts experts runs stage by stage, and the caller moves rows
+ * between GPUs in between (one process per GPU, an all-to-all for the rows out and one for the results back). The
+ * reference has no expert parallelism (both its cards hold the same experts, docs/DESIGN.md:294-297); these calls are
+ * this library's own. All pointers are DEVICE pointers; every call queues on stream (null: the layer's) and returns.
+ *   route:   quantises x, routes its T rows over all n_experts and sorts the T * n_used assignments by expert.
+ *   counts:  copies the rows each expert got (n_experts words) to the host, and waits, or to a device buffer, queued:
+ *            what the all-to-all's split sizes are made of.
+ *   gather:  rows_dev[r] = the quantised activation row (moe_layer_wire_row_bytes bytes) of assignment row r in expert
+ *            order, ids_dev[r] = its expert. Experts are owned in contiguous ranges, so this is destination order.
+ *   experts: R rows received (any order) with their expert ids, all among this GPU's experts; y_dev[r] = that expert's
+ *            FFN on row r, [R][n_embd] in the order received, f32 or (y_f16 != 0) f16.
+ *   shared:  the shared expert on the routed rows (may run on another stream than the experts).
+ *   combine: y_dev holds the results for this GPU's own assignments in expert order, as gather sent them;
+ *            out[t] = sum over k of w[t][k] * y[inv[t n_used + k]] + gate[t] * shared[t]. */
+MOE_API moe_status moe_layer_route_device(moe_layer *l, const float *x_dev, uint32_t T, void *stream);
+MOE_API moe_status moe_layer_read_counts(moe_layer *l, uint32_t *cnt_host, void *stream);
+MOE_API moe_status moe_layer_counts_device(moe_layer *l, uint32_t *cnt_dev, void *stream);
+MOE_API uint32_t moe_layer_wire_row_bytes(const moe_layer *l);
+MOE_API moe_status moe_layer_gather_rows_device(moe_layer *l, void *rows_dev, int32_t *ids_dev, void *stream);
+MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, const int32_t *ids_dev, uint32_t R, void *y_dev,
+                                            uint32_t y_f16, void *stream);
+MOE_API moe_status moe_layer_shared_device(moe_layer *l, void *stream);
+MOE_API moe_status moe_layer_combine_device(moe_layer *l, const void *y_dev, uint32_t y_f16, float *out_dev, void *stream);
 
 /* Waits for the layer's stream. MOE_TIMEOUT after timeout_ms (0: 60 s), never an unbounded wait. */
 MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms);

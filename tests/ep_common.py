@@ -1,0 +1,61 @@
+"""Shared by the expert-parallel tests: a CPU stand-in for the GPU stages, built on the oracle, so that the exchange
+logic of c0ven_b200.ep runs on gloo ranks without a GPU. Test infrastructure only."""
+import numpy as np
+import torch
+
+from c0ven_b200 import ep
+from oracle import oracle as O
+
+
+class OracleStages:
+    """The stages of c0ven_b200.ep.GpuStages on the CPU: a wire row is the f32 activation row itself."""
+
+    def __init__(self, layer, rank, world):
+        self.L, self.rank, self.world = layer, rank, world
+        self.first, self.count = ep.owner_ranges(layer["n_experts"], world)[rank]
+        self.K, self.E, self.F = layer["n_used"], layer["n_embd"], layer["n_ff"]
+
+    def route(self, x):
+        self.x = x.numpy()
+        L = self.L
+        rl = O.router_logits(self.x, L["router"], L["shexp_gate_inp"], L.get("router_bias"))
+        self.ids, self.w, self.gs = O.router_topk(rl, self.K)
+        cnt, base, self.inv, _ = O.pack(self.ids, L["n_experts"])
+        return torch.from_numpy(cnt.astype(np.int32))
+
+    def gather(self):
+        A = self.ids.size
+        order = np.empty(A, dtype=np.int64)
+        order[self.inv] = np.arange(A)
+        rows = self.x[order // self.K]
+        return torch.from_numpy(np.ascontiguousarray(rows).view(np.uint8).reshape(A, -1))
+
+    def experts(self, rows, ids):
+        L, R = self.L, rows.shape[0]
+        x = rows.numpy().view(np.float32).reshape(R, self.E)
+        ids = ids.numpy()
+        assert np.all((ids >= self.first) & (ids < self.first + self.count))
+        jobs = [(L["gate_exps"][e], L["up_exps"][e], L["down_exps"][e], r, 1.0) for r, e in enumerate(ids)]
+        y = O.compute_many(L["gate_type"], L["down_type"], self.E, self.F, jobs, x) if R else np.zeros((0, self.E), np.float32)
+        return torch.from_numpy(y)
+
+    def shared(self):
+        L = self.L
+        T = self.x.shape[0]
+        jobs = [(L["gate_shexp"], L["up_shexp"], L["down_shexp"], t, 1.0) for t in range(T)]
+        self.s = O.compute_many(L["shexp_gate_type"], L["shexp_down_type"], self.E, self.F, jobs, self.x)
+
+    def combine(self, y, out):
+        y = y.numpy()
+        T = self.x.shape[0]
+        o = np.zeros((T, self.E), dtype=np.float32)
+        for k in range(self.K):  # rank order, as the oracle's compute_many sums a token's jobs
+            o += self.w[:, k:k + 1] * y[self.inv.reshape(T, self.K)[:, k]]
+        o += self.gs[:, None] * self.s
+        out.copy_(torch.from_numpy(o))
+
+    def empty(self, shape, dtype, name=None):
+        return torch.empty(shape, dtype=dtype)
+
+    def to_device(self, a):
+        return torch.from_numpy(a)

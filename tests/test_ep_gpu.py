@@ -1,0 +1,78 @@
+"""Expert parallel on two B200s (NCCL): each rank holds half the experts; a rank's outputs must equal, bit for bit,
+what one GPU holding every expert gives for the same rows when the results travel as f32 and every expert takes the
+same kind of kernel on both (tensor_min_rows 1), and stay within the layer's bar when they travel as f16. Needs two GPUs; skipped otherwise."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+
+    from c0ven_b200 import MoELayer, ep, synth
+    from oracle import oracle as O
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    res = []
+    try:
+        for t, T in ((synth.Q4_K, (300, 41)), (synth.IQ3_S, (7, 1))):
+            layer = synth.make_layer(n_embd=512, n_ff=256, n_experts=32, n_used=4, gate_type=t, zipf_s=1.1, seed=50 + t)
+            x = synth.make_input(T[rank], 512, seed=20 + rank)
+            single = MoELayer(layer, max_tokens=512, device=rank, tensor_min_rows=1)
+            want = single.forward(x)
+            ids1 = single.route(T[rank])[0]
+            single.close()
+            ref = O.moe_forward(layer, x)[0]
+            for f16 in (False, True):
+                st = ep.GpuStages(layer, rank, world, max_tokens=512, device=rank, y_f16=f16, tensor_min_rows=1)
+                moe = ep.ExpertParallelMoE(st)
+                xd = torch.from_numpy(x).cuda()
+                for _ in range(2):
+                    out = moe.forward(xd)
+                st.sync()
+                got = out.cpu().numpy()
+                rel = float(np.abs(got - ref).max() / np.abs(ref).max())
+                res.append((t, f16, bool(np.array_equal(got, want)), rel, moe.sent_rows))
+                st.close()
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_match_one():
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+        assert p.exitcode == 0
+    for rank, res in sorted(q.get(timeout=5) for _ in range(2)):
+        for t, f16, same_bits, rel, sent in res:
+            assert rel <= 1e-2, (rank, t, f16, rel)
+            if not f16:
+                assert same_bits, (rank, t)
+            assert sent > 0
