@@ -239,14 +239,19 @@ def run_gpu(args, w):
     e2e_s = float(t.item())
 
     def teardown():
-        # Tensors the collectives touched are freed before the layer's stream goes, and the group before the process.
+        # Everything the layer's stream touched is freed and handed back to the driver while that stream still exists;
+        # then the group goes, then the layer.
         nonlocal x_dev, out_dev, flush
         torch.cuda.synchronize()
         del x_dev, out_dev, flush
         if world > 1:
-            stages.close()
+            stages._bufs.clear()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        if world > 1:
             dist.barrier()
             dist.destroy_process_group()
+            stages.close()
         else:
             gpu.close()
 
@@ -308,6 +313,11 @@ def main():
         run_reference(args, w)
     else:
         run_gpu(args, w)
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            # Under torchrun, leave without the interpreter's teardown: the order in which it would drop the collectives'
+            # streams and the allocator's blocks is not ours to set.
+            sys.stdout.flush()
+            os._exit(0)
 
 
 if __name__ == "__main__":

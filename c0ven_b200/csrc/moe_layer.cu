@@ -121,7 +121,7 @@ struct moe_layer {
   DeviceBuffer<uint32_t> grid;
   uint64_t gate_slice = 0, down_slice = 0;
   // A call's buffers.
-  DeviceBuffer<float> x, out, rl, w, gs, h, y, s;
+  DeviceBuffer<float> x, out, rl, pieces, gate_parts, w, gs, h, y, s;
   DeviceBuffer<int32_t> ids, ids_local;
   DeviceBuffer<uint32_t> error;
   DeviceBuffer<__half> wire_h;  // rows from other GPUs, dequantised for the tensor-core kernels
@@ -224,7 +224,9 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   }
 
   l->x.alloc((size_t)T * E), l->out.alloc((size_t)T * E);
-  l->rl.alloc((size_t)T * l->N), l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T), l->error.alloc(1);
+  l->rl.alloc((size_t)std::min<uint32_t>(T, 64) * l->N), l->gate_parts.alloc((size_t)T * (E / 256));
+  if (T > 64) l->pieces.alloc((size_t)kRouterPieces * T * NE);
+  l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T), l->error.alloc(1);
   l->pack.alloc(A, NE, kChunkTokens * K);
   if (ep) {
     l->pack_local.alloc(R, l->local, kLocalChunk);
@@ -246,15 +248,17 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   CUDA_OK(cudaStreamSynchronize(st));
 }
 
-void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, const ActBuffers &dst, cudaStream_t st) {
+// gate: with the rows' product with this vector wanted too (the shared expert's gate logit), its parts go to gate_parts.
+void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, const ActBuffers &dst, cudaStream_t st,
+                   const float *gate = nullptr, float *gate_parts = nullptr) {
   const uint64_t nblk = rows * (Kv / 256);
   if (nblk == 0) return;
   const ActView v = dst.view();
   const unsigned grid = (unsigned)((nblk + 7) / 8);
   if (dst.q8k)
-    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get());
+    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get(), gate, Kv / 256, gate_parts);
   else
-    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get());
+    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get(), gate, Kv / 256, gate_parts);
   launched(l, cudaGetLastError(), "quantize");
 }
 
@@ -274,11 +278,12 @@ uint32_t tensor_min_for(const moe_layer *l, uint64_t R) {
 void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   const uint32_t E = l->E, NE = l->NE, K = l->K, N = l->N;
   const uint64_t A = (uint64_t)T * K;
+  const bool by_pieces = T > 64;
   mark(l, ST_QUANT, st);
-  quantize_rows(l, x, T, E, l->xq_routed, st);
+  quantize_rows(l, x, T, E, l->xq_routed, st, by_pieces ? l->router.get() + (size_t)NE * E : nullptr, l->gate_parts.get());
   if (l->has_shared && !l->shared_x_same) quantize_rows(l, x, T, E, l->xq_shared, st);
   mark(l, ST_ROUTER, st);
-  if (T <= 64) {
+  if (!by_pieces) {
     const size_t smem = (size_t)8 * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float);
     if (!l->rows_attr_set) {
       CUDA_OK(cudaFuncSetAttribute(k_router_logits_rows<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -286,11 +291,12 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
     }
     k_router_logits_rows<8><<<dim3((N + 15) / 16, (T + 7) / 8), 128, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
   } else {
-    k_router_logits_tiles<<<dim3((N + 63) / 64, (T + 127) / 128), 256, 0, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+    k_router_pieces<<<dim3((NE + 127) / 128, (T + 127) / 128, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
   }
   launched(l, cudaGetLastError(), "router logits");
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
-  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->pack.chunk_hist.get());
+  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), by_pieces ? l->pieces.get() : nullptr, l->bias.get(), l->gate_parts.get(),
+                                                      E / 256, T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->pack.chunk_hist.get());
   launched(l, cudaGetLastError(), "router top-k");
   mark(l, ST_PACK, st);
   // On one GPU the pack also lists the groups and big tiles of the experts' kernels; expert parallel, it only sorts.

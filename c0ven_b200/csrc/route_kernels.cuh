@@ -27,12 +27,26 @@ constexpr uint32_t kRouterPieces = 8;   // pieces a router product is summed in
 
 // q8_0: per 32 values d = max|x| / 127, q = round(x * (1 / d)), 0 when d is 0; d kept as the f16 the CPU stores
 // (docs/spec/QUANT_FORMATS.md:463-465, :525-526).
+// With gate set (a vector of `per_row` * 256 floats), a block of 256 values also leaves its part of the row's product
+// with the vector in gate_parts[block]: the shared expert's gate logit, summed by the top-k kernel.
+__device__ __forceinline__ void gate_part(const float4 &a, const float4 &b, const float *gate, uint32_t per_row, uint64_t blk,
+                                          uint32_t lane, float *gate_parts) {
+  const float4 *g = (const float4 *)(gate + (blk % per_row) * 256);
+  const float4 ga = g[2 * lane], gb = g[2 * lane + 1];
+  float s = a.x * ga.x + a.y * ga.y + a.z * ga.z + a.w * ga.w + b.x * gb.x + b.y * gb.y + b.z * gb.z + b.w * gb.w;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) gate_parts[blk] = s;
+}
+
 static __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
-                                                   float *__restrict__ d, __half *__restrict__ deq) {
+                                                   float *__restrict__ d, __half *__restrict__ deq, const float *__restrict__ gate,
+                                                   uint32_t per_row, float *__restrict__ gate_parts) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
   const float4 a = ((const float4 *)(x + blk * 256))[2 * lane], b = ((const float4 *)(x + blk * 256))[2 * lane + 1];
+  if (gate) gate_part(a, b, gate, per_row, blk, lane, gate_parts);
   float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
                      fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -59,11 +73,13 @@ static __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restri
 // q8_K: per 256 values iscale = -127 / max with max the value of largest magnitude (the first of equals),
 // q = min(127, nearest-even(iscale * x)), d = 1 / iscale, and the sums of each 16 codes (QUANT_FORMATS.md:528-535).
 static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
-                                                   float *__restrict__ d, int16_t *__restrict__ bs, __half *__restrict__ deq) {
+                                                   float *__restrict__ d, int16_t *__restrict__ bs, __half *__restrict__ deq,
+                                                   const float *__restrict__ gate, uint32_t per_row, float *__restrict__ gate_parts) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
   const float4 a = ((const float4 *)(x + blk * 256))[2 * lane], b = ((const float4 *)(x + blk * 256))[2 * lane + 1];
+  if (gate) gate_part(a, b, gate, per_row, blk, lane, gate_parts);
   const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
   float amax = 0.0f, mx = 0.0f;
   uint32_t at = 8 * lane;
@@ -157,77 +173,76 @@ static __global__ void __launch_bounds__(128) k_router_logits_rows(const float *
   }
 }
 
-// Many rows: a 128 x 64 tile of (rows, experts) per CTA of 256 threads, 8 x 4 outputs a thread, 16 values of the
-// hidden size a step; the tile's partial sums fold into the totals at every piece's end.
-static __global__ void __launch_bounds__(256, 2) k_router_logits_tiles(const float *__restrict__ x, uint32_t T, uint32_t E,
-                                                            const float *__restrict__ W, uint32_t N,
-                                                            const float *__restrict__ bias, uint32_t NE,
-                                                            float *__restrict__ rl) {
-  constexpr int BM = 128, BN = 64, BK = 16;
-  __shared__ __align__(16) float As[2][BK][BM + 4], Bs[2][BK][BN + 4];
+// Many rows: the product piece by piece. A CTA takes a 128 x 128 tile of (rows, experts) and one of the kRouterPieces
+// pieces of the hidden size, 8 x 8 outputs a thread, 16 values of the piece a step, each output one chain of fused
+// multiply-adds in index order; it leaves the piece's partial sums in P[piece][row][expert]. The top-k kernel adds a
+// row's pieces in order. Splitting by piece gives eight times the CTAs, which keeps every SM busy at a few thousand
+// rows, and frees the registers the running totals would take. The shared expert's gate logit does not come from
+// here: the activation quantiser sums it (k_quant_*'s gate argument).
+static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__restrict__ x, uint32_t T, uint32_t E,
+                                                                const float *__restrict__ W, uint32_t NE, float *__restrict__ P) {
+  constexpr int BM = 128, BN = 128, BK = 16, LD = BM + 4;
+  __shared__ __align__(16) float As[2][BK][LD], Bs[2][BK][LD];
   const uint32_t tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
-  const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, piece = E / kRouterPieces;
-  float p[8][4], tot[8][4];
+  const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, piece = E / kRouterPieces, kbeg = blockIdx.z * piece;
+  float acc[8][8];
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) p[i][j] = 0.0f, tot[i][j] = 0.0f;
-  // A thread's loads: two float4 of x (row am, values 4 * aq .. and 4 * (aq + 2) ..), one of W (row bn; values 4 * bq ..).
-  // A warp's lanes hold consecutive rows, so its transposed stores fill consecutive banks.
-  const uint32_t am = tid % 128, aq = tid / 128, bn = tid % 64, bq = tid / 64;
-  float4 ra0, ra1, rb;
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+  // A thread's loads per step: two float4 of x and two of W, rows lr and the quarter lq of the step's 16 values and the
+  // one two on. A warp's lanes hold consecutive rows, so the transposed stores fill consecutive banks.
+  const uint32_t lr = tid % 128, lq = tid / 128;
+  float4 ra[2], rb[2];
   auto fetch = [&](uint32_t k0) {
-    const uint32_t r = m0 + am, e = n0 + bn;
-    ra0 = r < T ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * aq)) : make_float4(0, 0, 0, 0);
-    ra1 = r < T ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * (aq + 2))) : make_float4(0, 0, 0, 0);
-    rb = e < N ? __ldg((const float4 *)(W + (uint64_t)e * E + k0 + 4 * bq)) : make_float4(0, 0, 0, 0);
+    const uint32_t r = m0 + lr, e = n0 + lr;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      ra[i] = r < T ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
+      rb[i] = e < NE ? __ldg((const float4 *)(W + (uint64_t)e * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
+    }
   };
   auto stash = [&](int buf) {
-    As[buf][4 * aq + 0][am] = ra0.x, As[buf][4 * aq + 1][am] = ra0.y, As[buf][4 * aq + 2][am] = ra0.z, As[buf][4 * aq + 3][am] = ra0.w;
-    As[buf][4 * aq + 8][am] = ra1.x, As[buf][4 * aq + 9][am] = ra1.y, As[buf][4 * aq + 10][am] = ra1.z, As[buf][4 * aq + 11][am] = ra1.w;
-    Bs[buf][4 * bq + 0][bn] = rb.x, Bs[buf][4 * bq + 1][bn] = rb.y, Bs[buf][4 * bq + 2][bn] = rb.z, Bs[buf][4 * bq + 3][bn] = rb.w;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const uint32_t k = 4 * (lq + 2 * i);
+      As[buf][k + 0][lr] = ra[i].x, As[buf][k + 1][lr] = ra[i].y, As[buf][k + 2][lr] = ra[i].z, As[buf][k + 3][lr] = ra[i].w;
+      Bs[buf][k + 0][lr] = rb[i].x, Bs[buf][k + 1][lr] = rb[i].y, Bs[buf][k + 2][lr] = rb[i].z, Bs[buf][k + 3][lr] = rb[i].w;
+    }
   };
-  fetch(0);
+  fetch(kbeg);
   stash(0);
   __syncthreads();
-  const uint32_t steps = E / BK;
+  const uint32_t steps = piece / BK;
   for (uint32_t s = 0; s < steps; s++) {
     const int buf = s & 1;
-    if (s + 1 < steps) fetch((s + 1) * BK);
+    if (s + 1 < steps) fetch(kbeg + (s + 1) * BK);
 #pragma unroll
     for (int k = 0; k < BK; k++) {
-      const float4 a0 = *(const float4 *)&As[buf][k][ty * 8], a1 = *(const float4 *)&As[buf][k][ty * 8 + 4];
-      const float4 b = *(const float4 *)&Bs[buf][k][tx * 4];
-      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[4] = {b.x, b.y, b.z, b.w};
+      const float4 a0 = *(const float4 *)&As[buf][k][ty * 4], a1 = *(const float4 *)&As[buf][k][64 + ty * 4];
+      const float4 b0 = *(const float4 *)&Bs[buf][k][tx * 4], b1 = *(const float4 *)&Bs[buf][k][64 + tx * 4];
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
       for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) p[i][j] = fmaf(av[i], bv[j], p[i][j]);
+        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
     if (s + 1 < steps) stash(buf ^ 1);
     __syncthreads();
-    if (((s + 1) * BK) % piece == 0) {
-      const bool first = (s + 1) * BK == piece;
-#pragma unroll
-      for (int i = 0; i < 8; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          tot[i][j] = first ? p[i][j] : __fadd_rn(tot[i][j], p[i][j]);
-          p[i][j] = 0.0f;
-        }
-    }
   }
+  float *out = P + (uint64_t)blockIdx.z * T * NE;
 #pragma unroll
   for (int i = 0; i < 8; i++) {
-    const uint32_t t = m0 + ty * 8 + i;
+    const uint32_t t = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
     if (t >= T) continue;
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const uint32_t e = n0 + tx * 4 + j;
-      if (e >= N) continue;
-      float v = tot[i][j];
-      if (bias && e < NE) v = __fadd_rn(v, bias[e]);
-      rl[(uint64_t)t * N + e] = v;
+    for (int h = 0; h < 2; h++) {
+      const uint32_t e = n0 + 64 * h + tx * 4;
+      if (e + 3 < NE)
+        *(float4 *)(out + (uint64_t)t * NE + e) = make_float4(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3]);
+      else
+        for (int j = 0; j < 4; j++)
+          if (e + j < NE) out[(uint64_t)t * NE + e + j] = acc[i][4 * h + j];
     }
   }
 }
@@ -247,7 +262,11 @@ __device__ __forceinline__ float key_value(uint32_t key) {
 
 constexpr int kMaxPerLane = 16;  // experts a lane holds at most: 512 / 32
 
-static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, uint32_t T, uint32_t NE,
+// The logits come as rows rl[t][NE + 1] (the gate's logit last), or, with pieces set, as the partial sums
+// pieces[p][t][e] of k_router_pieces, added here in order with the bias, and the gate's logit as gate_parts[t][nparts].
+static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const float *__restrict__ pieces,
+                                                                  const float *__restrict__ bias, const float *__restrict__ gate_parts,
+                                                                  uint32_t nparts, uint32_t T, uint32_t NE,
                                                                   uint32_t K, int32_t *__restrict__ ids,
                                                                   float *__restrict__ w, float *__restrict__ gs,
                                                                   uint32_t *__restrict__ chunk_hist) {
@@ -256,14 +275,22 @@ static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const 
   __syncthreads();
   const uint32_t lane = threadIdx.x % 32, t = blockIdx.x * kChunkTokens + threadIdx.x / 32, per = NE / 32;
   if (t < T) {
-    const float *v = rl + (uint64_t)t * (NE + 1);
     uint32_t key[kMaxPerLane];
     float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; j++) {
       key[j] = 0;
       if ((uint32_t)j < per) {
-        const float f = v[lane + 32 * j];
+        const uint32_t e = lane + 32 * j;
+        float f;
+        if (pieces) {
+          f = pieces[(uint64_t)t * NE + e];
+#pragma unroll
+          for (uint32_t p = 1; p < kRouterPieces; p++) f = __fadd_rn(f, pieces[((uint64_t)p * T + t) * NE + e]);
+          if (bias) f = __fadd_rn(f, bias[e]);
+        } else {
+          f = rl[(uint64_t)t * (NE + 1) + e];
+        }
         key[j] = order_key(f);
         mx = fmaxf(mx, f);
       }
@@ -309,7 +336,16 @@ static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const 
       w[(uint64_t)t * K + lane] = pk / fmaxf(tot, 6.1035e-5f);
       atomicAdd(&hist[my_id], 1u);
     }
-    if (lane == 0) gs[t] = 1.0f / (1.0f + expf(-v[NE]));
+    if (lane == 0) {
+      float g;
+      if (pieces) {
+        g = 0.0f;
+        for (uint32_t p = 0; p < nparts; p++) g += gate_parts[(uint64_t)t * nparts + p];
+      } else {
+        g = rl[(uint64_t)t * (NE + 1) + NE];
+      }
+      gs[t] = 1.0f / (1.0f + expf(-g));
+    }
   }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];

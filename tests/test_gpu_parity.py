@@ -163,7 +163,7 @@ def test_full_shape_ragged_batch(t):
     gpu = MoELayer(layer, max_tokens=160, no_tensor=True)
     check(layer, gpu, synth.make_input(149, 2048, seed=9), INT_PATH_REL)
     gpu.close()
-    gpu = MoELayer(layer, max_tokens=700)   # the hot experts on the tensor cores, the tail on the integer dots
+    gpu = MoELayer(layer, max_tokens=700, tensor_min_rows=16)   # the hot experts on the tensor cores, the tail on the integer dots
     check(layer, gpu, synth.make_input(620, 2048, seed=10))
     st = gpu.stats()
     assert 0 < st["last_tensor_rows"] < 620 * 11
