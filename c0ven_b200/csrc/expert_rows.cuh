@@ -116,9 +116,9 @@ struct Unit<QT_Q4_K> {
     Raw x;
     x.q = ldg_stream16(s + (uint64_t)r * (K / 2) + 16u * u);
     const uint64_t blk = (uint64_t)r * (K / 256) + u / 8;
-    const uint32_t *sc = (const uint32_t *)(s + 128 * nblk + 12 * blk);
-    x.s0 = __ldg(sc), x.s1 = __ldg(sc + 1), x.s2 = __ldg(sc + 2);
-    x.dm = __ldg((const __half2 *)(s + 140 * nblk + 4 * blk));
+    const uint4 hd = __ldg((const uint4 *)(s + 128 * nblk + 16 * blk));  // d, dmin, then the 12 bytes of scales
+    x.dm = *(const __half2 *)&hd.x;
+    x.s0 = hd.y, x.s1 = hd.z, x.s2 = hd.w;
     return x;
   }
   __device__ static __forceinline__ uint32_t byte_of(const Raw &x, int i) {

@@ -1,5 +1,6 @@
-// The experts' products for many rows per expert: a grouped GEMM on the 5th-generation tensor cores. A CTA takes 128
-// weight rows of one expert and up to 256 of the rows routed to it. Its worker warps decode the quantised blocks to
+// The experts' products for many rows per expert: a grouped GEMM on the 5th-generation tensor cores. A work item is 128
+// weight rows of one expert and up to 256 of the rows routed to it; persistent CTAs, one per SM, take items in turn.
+// The worker warps decode the quantised blocks to
 // f16 straight into shared memory in the tensor core's K-major core-matrix layout and gather the rows' activations
 // beside them; one thread issues tcgen05.mma with the weights as the M side and the rows as the N side (so a short
 // tile costs a short instruction), accumulating f32 in tensor memory; the workers read the accumulators back with
@@ -18,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdio>
 
 #include "expert_rows.cuh"
 #include "formats.h"
@@ -31,7 +33,9 @@ struct BigTile {
 constexpr uint32_t kTileM = 128;   // weight rows a CTA takes
 constexpr uint32_t kTileN = 256;   // activation rows at most
 constexpr uint32_t kTileK = 64;    // values of the contraction a stage holds
-constexpr uint32_t kTileWorkers = 256;
+constexpr uint32_t kTileDecoders = 512;  // threads that decode weights: 16 warps, enough of them to hide their loads' latency
+constexpr uint32_t kTileCopiers = 128;   // threads that copy the rows' activations
+constexpr uint32_t kTileThreads = kTileDecoders + kTileCopiers + 32;
 
 struct ExpertTilesArgs {
   const uint8_t *w0, *w1;   // slot 0's slice of (gate, up) or (down, unused), runs layout
@@ -69,21 +73,31 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One bounded hardware wait: the warp sleeps until the phase completes or the hint (in ns) runs out.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Waits for the barrier's phase `parity` to complete, for about a second at most. False when it gave up or another
-// thread of the CTA already had.
+// thread of the CTA already had. The wait suspends the warp rather than spinning, so it takes no issue slots from the
+// warps that decode.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort, uint32_t *error) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
-  for (uint32_t spins = 0;; spins++) {
-    if (mbar_test(bar, parity)) return true;
+  for (;;) {
+    if (mbar_try(bar, parity, 20000)) return true;
     if (*abort) return false;
-    if ((spins & 63) == 63) {
-      __nanosleep(64);
-      if (clock64() - t0 > 2000000000ll) {
-        *abort = 1;
-        atomicExch(error, 1u);
-        return false;
-      }
+    if (clock64() - t0 > 2000000000ll) {
+      *abort = 1;
+      atomicExch(error, 1u);
+      return false;
     }
   }
 }
@@ -154,155 +168,173 @@ __device__ __forceinline__ uint4 ldg16(const void *p) {
   return v;
 }
 
+
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Small integers as f16 without an int-to-float conversion: 0x6400 | v is 1024 + v for v < 1024.
+__device__ __forceinline__ __half2 small_h2(uint32_t v) { return __hsub2(as_h2(0x64006400u | v | (v << 16)), as_h2(0x64006400u)); }
+
 // ---------------------------------------------------------------------------------------------------------------
-// Decoders: a stage is 64 values of every one of the tile's 128 weight rows. Decoder<QT>::kUnits units cover it; unit
-// i is fetched into registers (Raw) and then written as f16 into the operand tile.
+// Decoders. A stage is 64 values of every one of the tile's 128 weight rows; a thread takes one half of a row's stage,
+// 32 values: it fetches the half's quants and scales into registers (Raw), a stage ahead, and later writes them as f16
+// into the operand tile, chunks 4 h .. 4 h + 3 of row m. All arithmetic is in f16 pairs; integers reach f16 through
+// the exponent trick above, never through a conversion instruction.
 template <int QT>
 struct Decoder;
 
-// Q8_0: w = d * q. Unit: 16 codes of a row. 4 units a row.
+// Q8_0: w = d * q. A half is one block.
 template <>
 struct Decoder<QT_Q8_0> {
-  static constexpr uint32_t kUnits = kTileM * 4;
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
   struct Raw {
-    uint4 q;
+    uint4 q0, q1;
     __half d;
   };
-  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r0, uint32_t k0, uint32_t i) {
-    const uint32_t m = (i & 7) | ((i >> 5) << 3), u = (i >> 3) & 3, r = r0 + m;
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + (uint64_t)r * K + k0 + 32 * h;
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
     Raw x;
-    x.q = ldg16(s + (uint64_t)r * K + k0 + 16 * u);
-    x.d = __ldg((const __half *)(s + 32 * nblk) + (uint64_t)r * (K / 32) + k0 / 32 + u / 2);
+    const uint8_t *q = s + (uint64_t)r * K + k0 + 32 * h;
+    x.q0 = ldg16(q), x.q1 = ldg16(q + 16);
+    x.d = __ldg((const __half *)(s + 32 * nblk) + (uint64_t)r * (K / 32) + k0 / 32 + h);
     return x;
   }
-  __device__ static __forceinline__ void store(const Raw &x, uint8_t *tile, uint32_t i, const uint32_t *) {
-    const uint32_t m = (i & 7) | ((i >> 5) << 3), u = (i >> 3) & 3;
-    const __half2 d2 = __half2half2(x.d), off = __float2half2_rn(1152.0f);
-    const uint32_t w[4] = {x.q.x ^ 0x80808080u, x.q.y ^ 0x80808080u, x.q.z ^ 0x80808080u, x.q.w ^ 0x80808080u};
-    uint32_t h[8];
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *) {
+    const __half2 d2 = __half2half2(x.d), off = as_h2(0x64806480u);  // 1152 = 1024 + 128
+    const uint32_t w[8] = {x.q0.x, x.q0.y, x.q0.z, x.q0.w, x.q1.x, x.q1.y, x.q1.z, x.q1.w};
+    uint32_t o[16];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      h[2 * j] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(w[j], 0x4140)), off), d2));
-      h[2 * j + 1] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(w[j], 0x4342)), off), d2));
+    for (int j = 0; j < 8; j++) {
+      const uint32_t u = w[j] ^ 0x80808080u;  // int8 + 128
+      o[2 * j] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(u, 0x4140)), off), d2));
+      o[2 * j + 1] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(u, 0x4342)), off), d2));
     }
-    store_chunk(tile, m, 2 * u, make_uint4(h[0], h[1], h[2], h[3]));
-    store_chunk(tile, m, 2 * u + 1, make_uint4(h[4], h[5], h[6], h[7]));
+#pragma unroll
+    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
   }
 };
 
-// Q4_K: w = d * sc * q - dmin * m. Unit: 16 bytes of qs, the low nibbles 16 values of sub-block 2c, the high nibbles
-// 16 of sub-block 2c + 1, 32 values further on. 2 units a row.
+// Q4_K: w = d * sc * q - dmin * m. A stage is 32 bytes of qs; its first half is their low nibbles (sub-block 2c), its
+// second their high nibbles (sub-block 2c + 1). The two threads of a row's stage load 16 of the 32 bytes each and hand
+// each other theirs by a shuffle, so no byte is loaded twice. The block's d, dmin and scales are one 16-byte piece,
+// loaded once for its four stages.
 template <>
 struct Decoder<QT_Q4_K> {
-  static constexpr uint32_t kUnits = kTileM * 2;
+  struct Hdr {
+    uint4 v;  // d, dmin; then the 12 bytes of packed scales and minimums
+  };
   struct Raw {
     uint4 q;
-    uint32_t s0, s1, s2;
-    __half2 dm;
   };
-  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r0, uint32_t k0, uint32_t i) {
-    const uint32_t m = (i & 7) | ((i >> 4) << 3), hf = (i >> 3) & 1, r = r0 + m;
-    Raw x;
-    x.q = ldg16(s + (uint64_t)r * (K / 2) + (k0 / 64) * 32 + 16 * hf);
-    const uint64_t blk = (uint64_t)r * (K / 256) + k0 / 256;
-    const uint32_t *sc = (const uint32_t *)(s + 128 * nblk + 12 * blk);
-    x.s0 = __ldg(sc), x.s1 = __ldg(sc + 1), x.s2 = __ldg(sc + 2);
-    x.dm = __ldg((const __half2 *)(s + 140 * nblk + 4 * blk));
-    return x;
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0) {
+    return Hdr{__ldg((const uint4 *)(s + 128 * nblk + 16 * ((uint64_t)r * (K / 256) + k0 / 256)))};
   }
-  __device__ static __forceinline__ uint32_t byte_of(const Raw &x, int i) {
-    const uint32_t w = i < 4 ? x.s0 : i < 8 ? x.s1 : x.s2;
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + (uint64_t)r * (K / 2) + (k0 / 64) * 32 + 16 * h;
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return Raw{ldg16(quants_at(s, nblk, K, r, k0, h))};
+  }
+  __device__ static __forceinline__ uint32_t byte_of(const Hdr &x, uint32_t i) {
+    const uint32_t w = i < 4 ? x.v.y : i < 8 ? x.v.z : x.v.w;
     return (w >> (8 * (i & 3))) & 0xFF;
   }
-  __device__ static __forceinline__ void scale_min(const Raw &x, int j, int &sc, int &mn) {
+  __device__ static __forceinline__ void store(const Hdr &hd, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t k0, const uint32_t *) {
+    // The partner (the other half of the same row: lane ^ 8) holds the other 16 bytes.
+    uint4 o4;
+    o4.x = __shfl_xor_sync(0xffffffffu, x.q.x, 8), o4.y = __shfl_xor_sync(0xffffffffu, x.q.y, 8);
+    o4.z = __shfl_xor_sync(0xffffffffu, x.q.z, 8), o4.w = __shfl_xor_sync(0xffffffffu, x.q.w, 8);
+    const uint4 q0 = h ? o4 : x.q, q1 = h ? x.q : o4;
+    const uint32_t j = 2 * ((k0 % 256) / 64) + h;  // the sub-block; its 6-bit scale and minimum (QUANT_FORMATS.md:386-392)
+    uint32_t sc, mn;
     if (j < 4) {
-      sc = byte_of(x, j) & 63;
-      mn = byte_of(x, j + 4) & 63;
+      sc = byte_of(hd, j) & 63, mn = byte_of(hd, j + 4) & 63;
     } else {
-      sc = (byte_of(x, j + 4) & 0xF) | ((byte_of(x, j - 4) >> 6) << 4);
-      mn = (byte_of(x, j + 4) >> 4) | ((byte_of(x, j) >> 6) << 4);
+      sc = (byte_of(hd, j + 4) & 0xF) | ((byte_of(hd, j - 4) >> 6) << 4);
+      mn = (byte_of(hd, j + 4) >> 4) | ((byte_of(hd, j) >> 6) << 4);
     }
-  }
-  __device__ static __forceinline__ void store(const Raw &x, uint8_t *tile, uint32_t i, const uint32_t *, uint32_t k0) {
-    const uint32_t m = (i & 7) | ((i >> 4) << 3), hf = (i >> 3) & 1, c = (k0 % 256) / 64;
-    int sc_lo, m_lo, sc_hi, m_hi;
-    scale_min(x, 2 * c, sc_lo, m_lo);
-    scale_min(x, 2 * c + 1, sc_hi, m_hi);
-    const float dmin = __high2float(x.dm);
-    const __half2 d2 = __half2half2(__low2half(x.dm));
     // (1024 + q) * sc - 1024 * sc = q * sc, exact in f16; then * d - dmin * m, rounded once.
-    const __half2 scl = __float2half2_rn((float)sc_lo), sch = __float2half2_rn((float)sc_hi);
-    const __half2 bl = __float2half2_rn(-1024.0f * sc_lo), bh = __float2half2_rn(-1024.0f * sc_hi);
-    const __half2 ml = __float2half2_rn(-dmin * m_lo), mh = __float2half2_rn(-dmin * m_hi);
-    const uint32_t w[4] = {x.q.x, x.q.y, x.q.z, x.q.w};
-    uint32_t lo[8], hi[8];
+    const __half2 dm = as_h2(hd.v.x);
+    const __half2 sc2 = small_h2(sc), b2 = __hmul2(sc2, as_h2(0xE400E400u));  // -1024 * sc
+    const __half2 d2 = __half2half2(__low2half(dm)), m2 = __hneg2(__hmul2(__half2half2(__high2half(dm)), small_h2(mn)));
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t sh = 4 * h;
+    uint32_t o[16];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const uint32_t l = w[j] & 0x0F0F0F0Fu, h = (w[j] >> 4) & 0x0F0F0F0Fu;
-      lo[2 * j] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(l, 0x4140)), scl, bl), d2, ml));
-      lo[2 * j + 1] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(l, 0x4342)), scl, bl), d2, ml));
-      hi[2 * j] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(h, 0x4140)), sch, bh), d2, mh));
-      hi[2 * j + 1] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(h, 0x4342)), sch, bh), d2, mh));
+    for (int i = 0; i < 8; i++) {
+      const uint32_t t = (w[i] >> sh) & 0x0F0F0F0Fu;
+      o[2 * i] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(t, 0x4140)), sc2, b2), d2, m2));
+      o[2 * i + 1] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(t, 0x4342)), sc2, b2), d2, m2));
     }
-    store_chunk(tile, m, 2 * hf, make_uint4(lo[0], lo[1], lo[2], lo[3]));
-    store_chunk(tile, m, 2 * hf + 1, make_uint4(lo[4], lo[5], lo[6], lo[7]));
-    store_chunk(tile, m, 4 + 2 * hf, make_uint4(hi[0], hi[1], hi[2], hi[3]));
-    store_chunk(tile, m, 4 + 2 * hf + 1, make_uint4(hi[4], hi[5], hi[6], hi[7]));
+#pragma unroll
+    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
   }
 };
 
-// Q6_K: w = d * scales[v / 16] * (q - 32). A stage is half of a block's half: its 64 values take one nibble of 64
-// bytes of ql and two bits of 32 bytes of qh. Unit: 16 bytes of ql, 16 values. 4 units a row.
+// Q6_K: w = d * scales[v / 16] * (q - 32). A stage is a quarter of a block: one nibble of 64 bytes of ql and two bits
+// of 32 bytes of qh; a half is 32 bytes of ql with all 32 of qh, two groups of 16 with a scale each.
 template <>
 struct Decoder<QT_Q6_K> {
-  static constexpr uint32_t kUnits = kTileM * 4;
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
   struct Raw {
-    uint4 ql, qh;
-    int sc;
+    uint4 l0, l1, h0, h1;
+    int sc0, sc1;
     __half d;
   };
-  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r0, uint32_t k0, uint32_t i) {
-    const uint32_t m = (i & 7) | ((i >> 5) << 3), u = (i >> 3) & 3, r = r0 + m;
-    const uint32_t v0 = k0 % 256, h = v0 / 128;  // the stage starts at value v0 of its block: 0, 64, 128 or 192
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + 128 * ((uint64_t)r * (K / 256) + k0 / 256) + 64 * ((k0 % 256) / 128) + 32 * h;
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    const uint32_t v0 = k0 % 256, hh = v0 / 128;  // the stage starts at value v0 of its block: 0, 64, 128 or 192
     const uint64_t blk = (uint64_t)r * (K / 256) + k0 / 256;
     Raw x;
-    x.ql = ldg16(s + 128 * blk + 64 * h + 16 * u);
-    x.qh = ldg16(s + 128 * nblk + 64 * blk + 32 * h + 16 * (u & 1));
-    x.sc = __ldg((const int8_t *)(s + 192 * nblk + 16 * blk) + v0 / 16 + u);
+    const uint8_t *ql = s + 128 * blk + 64 * hh + 32 * h, *qh = s + 128 * nblk + 64 * blk + 32 * hh;
+    x.l0 = ldg16(ql), x.l1 = ldg16(ql + 16), x.h0 = ldg16(qh), x.h1 = ldg16(qh + 16);
+    const int8_t *sc = (const int8_t *)(s + 192 * nblk + 16 * blk) + v0 / 16 + 2 * h;
+    x.sc0 = __ldg(sc), x.sc1 = __ldg(sc + 1);
     x.d = __ldg((const __half *)(s + 208 * nblk) + blk);
     return x;
   }
-  __device__ static __forceinline__ void store(const Raw &x, uint8_t *tile, uint32_t i, const uint32_t *, uint32_t k0) {
-    const uint32_t m = (i & 7) | ((i >> 5) << 3), u = (i >> 3) & 3;
-    const bool high = (k0 % 128) >= 64;  // values 64..127 of the half: the high nibbles, qh's bits 4..7
-    const uint32_t sh = (high ? 4 : 0) + (u >= 2 ? 2 : 0);
-    const __half2 dsc = __float2half2_rn(__half2float(x.d) * (float)x.sc), off = __float2half2_rn(1056.0f);
-    const uint32_t l[4] = {x.ql.x, x.ql.y, x.ql.z, x.ql.w}, hb[4] = {x.qh.x, x.qh.y, x.qh.z, x.qh.w};
-    uint32_t o[8];
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t k0, const uint32_t *) {
+    const bool high = (k0 % 128) >= 64;  // values 64 .. 127 of the block's half: the high nibbles, qh's bits 4 .. 7
+    const uint32_t sh = (high ? 4 : 0) + (h ? 2 : 0), nsh = high ? 4 : 0;
+    const __half2 d2 = __half2half2(x.d), off = as_h2(0x64206420u), o128 = as_h2(0x64806480u);  // 1056 = 1024 + 32; 1152
+    const __half2 ds0 = __hmul2(d2, __hsub2(as_h2(0x64006400u | (uint32_t)(x.sc0 + 128) * 0x10001u), o128));
+    const __half2 ds1 = __hmul2(d2, __hsub2(as_h2(0x64006400u | (uint32_t)(x.sc1 + 128) * 0x10001u), o128));
+    const uint32_t l[8] = {x.l0.x, x.l0.y, x.l0.z, x.l0.w, x.l1.x, x.l1.y, x.l1.z, x.l1.w};
+    const uint32_t b[8] = {x.h0.x, x.h0.y, x.h0.z, x.h0.w, x.h1.x, x.h1.y, x.h1.z, x.h1.w};
+    uint32_t o[16];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const uint32_t q = ((high ? l[j] >> 4 : l[j]) & 0x0F0F0F0Fu) | (((hb[j] >> sh) & 0x03030303u) << 4);
-      o[2 * j] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(q, 0x4140)), off), dsc));
-      o[2 * j + 1] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(q, 0x4342)), off), dsc));
+    for (int i = 0; i < 8; i++) {
+      const uint32_t q = ((l[i] >> nsh) & 0x0F0F0F0Fu) | (((b[i] >> sh) & 0x03030303u) << 4);
+      const __half2 ds = i < 4 ? ds0 : ds1;
+      o[2 * i] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(q, 0x4140)), off), ds));
+      o[2 * i + 1] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(q, 0x4342)), off), ds));
     }
-    store_chunk(tile, m, 2 * u, make_uint4(o[0], o[1], o[2], o[3]));
-    store_chunk(tile, m, 2 * u + 1, make_uint4(o[4], o[5], o[6], o[7]));
+#pragma unroll
+    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
   }
 };
 
-// IQ3_S: w = d * (1 + 2 s) * grid[index][i] * sign. A stage is two sub-blocks of 32. Unit: 8 bytes of qs, one
-// sub-block. 2 units a row.
+// IQ3_S: w = d * (1 + 2 s) * grid[index][i] * sign. A half is one sub-block of 32: 8 bytes of qs, a byte of qh, 4 of
+// signs, a nibble of scale. The codebook is in shared memory.
 template <>
 struct Decoder<QT_IQ3_S> {
-  static constexpr uint32_t kUnits = kTileM * 2;
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
   struct Raw {
     uint2 qs;
     uint32_t sg, qh, sc;
     __half d;
   };
-  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r0, uint32_t k0, uint32_t i) {
-    const uint32_t m = (i & 7) | ((i >> 4) << 3), sbi = (i >> 3) & 1, r = r0 + m;
-    const uint32_t sb = (k0 % 256) / 32 + sbi;  // the sub-block within its block
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + 64 * ((uint64_t)r * (K / 256) + k0 / 256) + 8 * ((k0 % 256) / 32 + h);
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    const uint32_t sb = (k0 % 256) / 32 + h;  // the sub-block within its block
     const uint64_t blk = (uint64_t)r * (K / 256) + k0 / 256;
     Raw x;
     x.qs = __ldg((const uint2 *)(s + 64 * blk + 8 * sb));
@@ -312,9 +344,8 @@ struct Decoder<QT_IQ3_S> {
     x.d = __ldg((const __half *)(s + 108 * nblk) + blk);
     return x;
   }
-  __device__ static __forceinline__ void store(const Raw &x, uint8_t *tile, uint32_t i, const uint32_t *grid, uint32_t) {
-    const uint32_t m = (i & 7) | ((i >> 4) << 3), sbi = (i >> 3) & 1;
-    const __half2 ls = __float2half2_rn((float)(2 * x.sc + 1)), d2 = __half2half2(x.d), off = __float2half2_rn(1024.0f);
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *grid) {
+    const __half2 ls = small_h2(2 * x.sc + 1), d2 = __half2half2(x.d), off = as_h2(0x64006400u);
     uint32_t o[16];
 #pragma unroll
     for (int k = 0; k < 8; k++) {
@@ -327,19 +358,12 @@ struct Decoder<QT_IQ3_S> {
       o[2 * k + 1] = as_u32(__hmul2(__hmul2(__hsub2(as_h2(bias_h2(g, 0x4342)), off), ls), d2)) ^ s23;
     }
 #pragma unroll
-    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * sbi + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
+    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
   }
 };
 
-template <int QT>
-__device__ __forceinline__ void decode_store(const typename Decoder<QT>::Raw &x, uint8_t *tile, uint32_t i, const uint32_t *grid, uint32_t k0) {
-  if constexpr (QT == QT_Q8_0)
-    Decoder<QT>::store(x, tile, i, grid);
-  else
-    Decoder<QT>::store(x, tile, i, grid, k0);
-}
-
 }  // namespace tc
+
 
 // Shared memory of a CTA: the stages (NMAT weight tiles of 16 KB and a row tile of 32 KB each), then the barriers.
 template <int NMAT>
@@ -347,158 +371,211 @@ struct TileSmem {
   static constexpr uint32_t kStages = NMAT == 2 ? 3 : 4;
   static constexpr uint32_t kWBytes = kTileM * kTileK * 2, kXBytes = kTileN * kTileK * 2;
   static constexpr uint32_t kStageBytes = NMAT * kWBytes + kXBytes;
-  static constexpr uint32_t kBarriers = kStages * kStageBytes;  // full[kStages], empty[kStages], acc, then tmem address, abort
+  static constexpr uint32_t kBarriers = kStages * kStageBytes;  // full[kStages], empty[kStages], acc full, acc empty; tmem address; abort
   static constexpr uint32_t kGrid = kBarriers + 128;            // IQ3_S's codebook, 2 KB
-  static constexpr uint32_t kRowIdx = kGrid + 2048;             // the tile's activation rows, kTileN words
-  static constexpr uint32_t kBytes = kRowIdx + 4 * kTileN + 1024;  // and room to align the base to 1024
+  static constexpr uint32_t kBytes = kGrid + 2048 + 1024;       // and room to align the base to 1024
 };
 
-// NMAT 2: out = swiglu(gate x, up x); NMAT 1: out = down h. Launch: grid (R / 128, tiles at most), 288 threads
-// (8 worker warps, then the warp that owns tensor memory and issues the MMAs), dynamic shared memory TileSmem::kBytes.
+// SwiGLU with the fast exponential and division: the tensor-core path's results already differ from the CPU path's
+// in the last bits of f16 products, so full-precision expf buys nothing here.
+__device__ __forceinline__ float swiglu_fast(float g, float u, float limit) {
+  if (limit > 0.0f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+// The tile a work item belongs to.
+struct ItemTile {
+  uint32_t slot, start, count;
+};
+__device__ __forceinline__ ItemTile item_tile(const ExpertTilesArgs &a, uint32_t ti) {
+  if (a.tiles) {
+    const BigTile t = a.tiles[ti];
+    return ItemTile{t.slot, t.start, t.count};
+  }
+  const uint32_t start = ti * kTileN;
+  return ItemTile{0, start, min(kTileN, a.dense_rows - start)};
+}
+
+// NMAT 2: out = swiglu(gate x, up x); NMAT 1: out = down h. Persistent: the grid is one CTA per SM (fewer when there is
+// less work), and CTA b takes the work items b, b + gridDim.x, ...; item i is weight-row tile i % (R / 128) of big tile
+// i / (R / 128), so neighbouring CTAs share a tile's activations in L2. Three roles: 16 decode warps (quants to f16
+// weights in shared memory, and the epilogue), 4 copy warps (the rows' activations, asynchronous 16-byte copies), and
+// the warp that owns tensor memory and whose first lane issues the MMAs. A warp arrives on a barrier once, by one
+// lane: hundreds of arrivals per stage on one barrier word would serialise in shared memory and set the stage's pace.
+// Dynamic shared memory TileSmem::kBytes.
 template <int QT, int NMAT>
-__global__ void __launch_bounds__(288, 1) k_expert_tiles(const ExpertTilesArgs a, const uint32_t *__restrict__ grid_global) {
+__global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTilesArgs a, const uint32_t *__restrict__ grid_global) {
   using namespace tc;
   using SM = TileSmem<NMAT>;
   using Dec = Decoder<QT>;
-  constexpr uint32_t S = SM::kStages;
+  using Raw = typename Dec::Raw;
+  constexpr uint32_t S = SM::kStages, kCols = NMAT == 2 ? 512 : 256;
+  constexpr uint32_t kDW = kTileDecoders / 32, kCW = kTileCopiers / 32;  // decode warps, copy warps
+  constexpr uint32_t kHalves = NMAT * kTileM * 2;        // (matrix, row, half) units to decode per stage: a thread takes one
+  constexpr uint32_t CPT = kTileN * 8 / kTileCopiers;    // activation pieces a copy thread takes per stage at most
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
-  uint32_t slot, start, count;
-  if (a.tiles) {
-    if (blockIdx.y >= *a.ntiles) return;
-    const BigTile t = a.tiles[blockIdx.y];
-    slot = t.slot, start = t.start, count = t.count;
-  } else {
-    start = blockIdx.y * kTileN;
-    if (start >= a.dense_rows) return;
-    slot = 0, count = min(kTileN, a.dense_rows - start);
-  }
-  const uint32_t K = a.K, KT = K / kTileK, r0 = blockIdx.x * kTileM;
-  const uint32_t N = (count + 15) & ~15u;  // the MMA's N: the rows, rounded up to 16
+  const uint32_t K = a.K, KT = K / kTileK, RT = a.R / kTileM;
+  const uint32_t ntiles = a.tiles ? *a.ntiles : (a.dense_rows + kTileN - 1) / kTileN;
+  const uint32_t nitems = ntiles * RT;
+  if (blockIdx.x >= nitems) return;
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   uint64_t *bars = (uint64_t *)(smem + SM::kBarriers);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](uint32_t s) { return bar0 + 8 * s; };
   auto empty_bar = [&](uint32_t s) { return bar0 + 8 * (S + s); };
-  const uint32_t acc_bar = bar0 + 8 * (2 * S);
-  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 1);
+  const uint32_t acc_full = bar0 + 8 * (2 * S), acc_empty = bar0 + 8 * (2 * S + 1);
+  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 2);
   volatile uint32_t *abort = tmem_slot + 1;
   uint32_t *grid = (uint32_t *)(smem + SM::kGrid);
-  uint32_t *rowidx = (uint32_t *)(smem + SM::kRowIdx);
-  constexpr uint32_t kCols = NMAT == 2 ? 512 : 256;
 
-  // A stage is full when every worker has stored its decoded weights (one arrival) and its copies of the rows'
-  // activations have landed (one more, made by the copy unit).
+  // A stage is full when every decode warp has stored its weights (one arrival a warp) and every copy thread's copies
+  // have landed (one arrival a thread, made by the copy unit). The accumulators are empty again when every decode warp
+  // has read its part of them.
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), 2 * kTileWorkers), mbar_init(empty_bar(s), 1);
-    mbar_init(acc_bar, 1);
+    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW + kTileCopiers), mbar_init(empty_bar(s), 1);
+    mbar_init(acc_full, 1), mbar_init(acc_empty, kDW);
     *abort = 0;
     fence_barrier_init();
   }
   if constexpr (QT == QT_IQ3_S)
     for (uint32_t i = tid; i < 512; i += blockDim.x) grid[i] = grid_global[i];
-  for (uint32_t n = tid; n < kTileN; n += blockDim.x)
-    rowidx[n] = n < count ? (a.act_row ? a.act_row[start + n] : start + n) : 0xFFFFFFFFu;
-  if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kCols);
+  if (warp == kDW + kCW) tmem_alloc(smem_u32(tmem_slot), kCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
 
-  if (warp < 8) {
-    // Workers: decode this stage's weights and gather its rows' activations into the operand tiles.
+  if (warp < kDW) {
+    // Decode warps. This thread's unit: half h of row m of matrix tid / 256 (threads past the units decode nothing): 8
+    // consecutive threads take the 8 rows of a core matrix, so a quarter-warp's 16-byte stores fill 128 contiguous bytes.
     const uint64_t nblk = (uint64_t)a.R * (K / block_values(QT));
-    const uint8_t *w0 = a.w0 + (uint64_t)slot * a.slice_bytes;
-    const uint8_t *w1 = NMAT == 2 ? a.w1 + (uint64_t)slot * a.slice_bytes : nullptr;
-    constexpr uint32_t UPT = Dec::kUnits / kTileWorkers;  // weight units a thread takes per matrix and stage
-    using Raw = typename Dec::Raw;
-    const uint32_t nchunks = N * 8;  // 16-byte pieces of the rows' activations in a stage
-    bool ok = true;
-    Raw raw[2][NMAT][UPT];  // this stage's quants and the next one's, fetched a stage ahead
-    auto fetch = [&](Raw (&r)[NMAT][UPT], uint32_t k0) {
-#pragma unroll
-      for (uint32_t j = 0; j < UPT; j++) {
-        r[0][j] = Dec::fetch(w0, nblk, K, r0, k0, tid + j * kTileWorkers);
-        if constexpr (NMAT == 2) r[1][j] = Dec::fetch(w1, nblk, K, r0, k0, tid + j * kTileWorkers);
+    const bool decodes = tid < kHalves;
+    const uint32_t mat = tid / 256, u = tid % 256, m = (u & 7) | ((u >> 4) << 3), h = (u >> 3) & 1;
+    uint32_t li = 0;
+    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+      const ItemTile t = item_tile(a, item / RT);
+      const uint32_t r0 = (item % RT) * kTileM, N = (t.count + 15) & ~15u;
+      const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
+      // Quants come from HBM the first time an expert is touched; a request for the L2 goes out kAhead stages before
+      // the load into registers, which itself goes a stage before the decode.
+      constexpr uint32_t kAhead = 6;
+      Raw raw[2];
+      typename Dec::Hdr hdr, hdr_next;  // the block's scales: fetched with its first stage's quants, used from that stage on
+      auto fetch = [&](Raw &r, uint32_t k0) {
+        if (decodes) {
+          r = Dec::fetch(wm, nblk, K, r0 + m, k0, h);
+          if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0);
+          if (k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, h));
+        }
+      };
+      auto stage_step = [&](Raw &r, uint32_t it) {
+        const uint32_t g = li * KT + it, s = g % S, use = g / S, k0 = it * kTileK;
+        if (use > 0) ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error);
+        if (!ok) return;
+        tc_fence_after();
+        if (k0 % 256 == 0) hdr = hdr_next;
+        if (decodes) Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
+      };
+      if (decodes)
+        for (uint32_t p = 1; p < kAhead && p < KT; p++) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, h));
+      fetch(raw[0], 0);
+      for (uint32_t it = 0; it < KT && ok; it += 2) {
+        if (it + 1 < KT) fetch(raw[1], (it + 1) * kTileK);
+        stage_step(raw[0], it);
+        if (!ok || it + 1 >= KT) break;
+        if (it + 2 < KT) fetch(raw[0], (it + 2) * kTileK);
+        stage_step(raw[1], it + 1);
       }
-    };
-    auto stage_step = [&](Raw (&r)[NMAT][UPT], uint32_t it) {
-      const uint32_t s = it % S, k0 = it * kTileK;
-      uint8_t *stage = smem + s * SM::kStageBytes;
-      if (it >= S) ok = mbar_wait(empty_bar(s), ((it / S) - 1) & 1, abort, a.error);
-      if (!ok) return;
-      tc_fence_after();
-      // The rows' activations: 16-byte asynchronous copies by token index, straight into the operand layout. Piece c
-      // is (row n, chunk kc); 8 consecutive threads take the 8 rows of a core matrix. Rows past count are never read
-      // back (their columns of the result are dropped), so they are left as they are.
-      const uint32_t xt = smem_u32(stage + NMAT * SM::kWBytes);
-      for (uint32_t c = tid; c < nchunks; c += kTileWorkers) {
-        const uint32_t n = (c & 7) | ((c >> 6) << 3), kc = (c >> 3) & 7, row = rowidx[n];
-        if (row != 0xFFFFFFFFu) copy_async16(xt + (n >> 3) * kSbo + kc * kLbo + (n & 7) * 16, a.act + (uint64_t)row * K + k0 + 8 * kc);
-      }
-      mbar_arrive_after_copies(full_bar(s));
+      // Epilogue: warp w reads TMEM lanes 32 (w % 4) .., its row of the weights; the warps of a quarter share the columns.
+      if (ok) ok = mbar_wait(acc_full, li & 1, abort, a.error);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t q = warp % 4, r = r0 + 32 * q + lane;
+        for (uint32_t c = warp / 4; c < N / 16; c += kDW / 4) {
+          uint32_t gv[16], uv[16];
+          tmem_ld16(tmem_base + ((32 * q) << 16) + 16 * c, gv);
+          if constexpr (NMAT == 2) tmem_ld16(tmem_base + ((32 * q) << 16) + kTileN + 16 * c, uv);
+          tmem_ld_wait();
 #pragma unroll
-      for (uint32_t j = 0; j < UPT; j++) {
-        decode_store<QT>(r[0][j], stage, tid + j * kTileWorkers, grid, k0);
-        if constexpr (NMAT == 2) decode_store<QT>(r[1][j], stage + SM::kWBytes, tid + j * kTileWorkers, grid, k0);
-      }
-      fence_async_smem();
-      mbar_arrive(full_bar(s));
-    };
-    fetch(raw[0], 0);
-    for (uint32_t it = 0; it < KT && ok; it += 2) {
-      if (it + 1 < KT) fetch(raw[1], (it + 1) * kTileK);
-      stage_step(raw[0], it);
-      if (!ok || it + 1 >= KT) break;
-      if (it + 2 < KT) fetch(raw[0], (it + 2) * kTileK);
-      stage_step(raw[1], it + 1);
-    }
-    // Epilogue: warp w reads TMEM lanes 32 (w % 4) .., its row of the weights; warps w and w + 4 share the columns.
-    if (ok) ok = mbar_wait(acc_bar, 0, abort, a.error);
-    if (ok) {
-      tc_fence_after();
-      const uint32_t q = warp % 4, r = r0 + 32 * q + lane;
-      for (uint32_t c = warp / 4; c < N / 16; c += 2) {
-        uint32_t g[16], u[16];
-        tmem_ld16(tmem_base + ((32 * q) << 16) + 16 * c, g);
-        if constexpr (NMAT == 2) tmem_ld16(tmem_base + ((32 * q) << 16) + kTileN + 16 * c, u);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; j++) {
-          const uint32_t n = 16 * c + j;
-          if (n < count && r < a.R) {
-            float v = __uint_as_float(g[j]);
-            if constexpr (NMAT == 2) v = swiglu(v, __uint_as_float(u[j]), a.limit);
-            a.out[(uint64_t)(start + n) * a.out_stride + r] = v;
+          for (int j = 0; j < 16; j++) {
+            const uint32_t n = 16 * c + j;
+            if (n < t.count) {
+              float v = __uint_as_float(gv[j]);
+              if constexpr (NMAT == 2) v = swiglu_fast(v, __uint_as_float(uv[j]), a.limit);
+              a.out[(uint64_t)(t.start + n) * a.out_stride + r] = v;
+            }
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);
+      }
+    }
+  }
+  else if (warp < kDW + kCW) {
+    // Copy warps: the rows' activations, 16-byte asynchronous copies by token index straight into the operand layout.
+    // Thread ct takes chunk kc of rows n0 + 16 j, j < CPT, at dst0 + 2048 j in a stage's row tile; 8 consecutive
+    // threads take the 8 rows of a core matrix. Rows past count are never read back (their columns of the result are
+    // dropped), so they are left as they are.
+    const uint32_t ct = tid - kTileDecoders, kc = (ct >> 3) & 7, n0 = (ct & 7) | ((ct >> 6) << 3);
+    const uint32_t dst0 = NMAT * SM::kWBytes + (ct >> 6) * kSbo + kc * kLbo + (ct & 7) * 16;
+    uint32_t li = 0;
+    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+      const ItemTile t = item_tile(a, item / RT);
+      const __half *src[CPT];
+#pragma unroll
+      for (int j = 0; j < (int)CPT; j++) {
+        const uint32_t n = n0 + 16 * j;
+        src[j] = n < t.count ? a.act + (uint64_t)(a.act_row ? a.act_row[t.start + n] : t.start + n) * K + 8 * kc : nullptr;
+      }
+      for (uint32_t it = 0; it < KT && ok; it++) {
+        const uint32_t g = li * KT + it, s = g % S, use = g / S, k0 = it * kTileK;
+        if (use > 0) ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error);
+        if (!ok) break;
+        const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + dst0;
+#pragma unroll
+        for (int j = 0; j < (int)CPT; j++)
+          if (src[j]) copy_async16(xt + 2048 * j, src[j] + k0);
+        mbar_arrive_after_copies(full_bar(s));
       }
     }
   } else if (lane == 0) {
     // The MMA thread: per stage, four K steps of 16 for each matrix; the commit frees the stage when they are done.
-    const uint32_t idesc = instr_desc(N);
-    bool ok = true;
-    for (uint32_t it = 0; it < KT && ok; it++) {
-      const uint32_t s = it % S;
-      ok = mbar_wait(full_bar(s), (it / S) & 1, abort, a.error);
-      if (!ok) break;
-      fence_async_smem();  // the copies' writes, like the workers' stores, must be visible to the tensor core's reads
-      tc_fence_after();
-      const uint32_t stage = smem_u32(smem + s * SM::kStageBytes), xt = stage + NMAT * SM::kWBytes;
+    uint32_t li = 0;
+    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+      const ItemTile t = item_tile(a, item / RT);
+      const uint32_t idesc = instr_desc((t.count + 15) & ~15u);
+      if (li > 0) ok = mbar_wait(acc_empty, (li - 1) & 1, abort, a.error);
+      for (uint32_t it = 0; it < KT && ok; it++) {
+        const uint32_t g = li * KT + it, s = g % S;
+        ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error);
+        if (!ok) break;
+        fence_async_smem();  // the copies' writes, like the decoders' stores, must be visible to the tensor core's reads
+        tc_fence_after();
+        const uint32_t stage = smem_u32(smem + s * SM::kStageBytes), xt = stage + NMAT * SM::kWBytes;
 #pragma unroll
-      for (uint32_t k = 0; k < kTileK / 16; k++) {
-        const uint64_t db = smem_desc(xt + 2 * k * kLbo);
-        mma_f16(tmem_base, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
-        if constexpr (NMAT == 2) mma_f16(tmem_base + kTileN, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
+        for (uint32_t k = 0; k < kTileK / 16; k++) {
+          const uint64_t db = smem_desc(xt + 2 * k * kLbo);
+          mma_f16(tmem_base, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
+          if constexpr (NMAT == 2) mma_f16(tmem_base + kTileN, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
+        }
+        mma_commit(empty_bar(s));
       }
-      mma_commit(empty_bar(s));
+      if (ok) mma_commit(acc_full);
     }
-    if (ok) mma_commit(acc_bar);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kDW + kCW) {
     __syncwarp();
     tc_fence_after();
     tmem_free(tmem_base, kCols);

@@ -2,6 +2,8 @@
 // EXPERT_TILES_QT set.
 #pragma once
 
+#include <algorithm>
+
 #include "expert_tiles.cuh"
 
 namespace moe {
@@ -13,7 +15,11 @@ cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, uint32_t max_tiles, co
   const size_t smem = TileSmem<NMAT>::kBytes;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kernel<<<dim3(a.R / kTileM, max_tiles), 288, smem, st>>>(a, grid_global);
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  const uint64_t items = (uint64_t)max_tiles * (a.R / kTileM);
+  kernel<<<(unsigned)std::min<uint64_t>(items, (uint64_t)sms), kTileThreads, smem, st>>>(a, grid_global);
   return cudaGetLastError();
 }
 

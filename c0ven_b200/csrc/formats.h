@@ -1,6 +1,7 @@
 // The GGUF block formats the layer reads and the "runs" layout the GPU holds them in: a slice of n blocks is one run
 // per field, the quants first and the f16 scales last, field f of block k at run_offset(f, n) + k * field_size(f).
-// The formats and the run order are the reference's (shared/quant.h:36-176; docs/spec/QUANT_FORMATS.md, "Wide loads");
+// The formats and the run order are the reference's (shared/quant.h:36-176; docs/spec/QUANT_FORMATS.md, "Wide loads"),
+// but for Q4_K, whose d, dmin and packed scales stay together as the block's first 16 bytes, so one 128-bit load brings them;
 // the layout is a permutation of the file's bytes, so an expert costs the bytes it has in the file.
 #pragma once
 
@@ -29,12 +30,12 @@ FMT_HD constexpr uint64_t row_bytes(uint32_t t, uint64_t n) { return n / block_v
 struct Field {
   uint32_t offset, size;
 };
-FMT_HD constexpr uint32_t nfields(uint32_t t) { return t == QT_Q8_0 ? 2u : t == QT_Q4_K ? 3u : t == QT_Q6_K ? 4u : t == QT_IQ3_S ? 5u : 0u; }
+FMT_HD constexpr uint32_t nfields(uint32_t t) { return t == QT_Q8_0 ? 2u : t == QT_Q4_K ? 2u : t == QT_Q6_K ? 4u : t == QT_IQ3_S ? 5u : 0u; }
 // Field f of type t, in run order.
 FMT_HD constexpr Field field(uint32_t t, uint32_t f) {
   switch (t) {
     case QT_Q8_0: return f == 0 ? Field{2, 32} : Field{0, 2};                                                  // qs, d
-    case QT_Q4_K: return f == 0 ? Field{16, 128} : f == 1 ? Field{4, 12} : Field{0, 4};                         // qs, scales, d+dmin
+    case QT_Q4_K: return f == 0 ? Field{16, 128} : Field{0, 16};  // qs; then d, dmin and the scales as one 16-byte piece, one load
     case QT_Q6_K: return f == 0 ? Field{0, 128} : f == 1 ? Field{128, 64} : f == 2 ? Field{192, 16} : Field{208, 2};  // ql, qh, scales, d
     case QT_IQ3_S:
       return f == 0 ? Field{2, 64} : f == 1 ? Field{74, 32} : f == 2 ? Field{66, 8} : f == 3 ? Field{106, 4} : Field{0, 2};  // qs, signs, qh, scales, d

@@ -41,14 +41,19 @@ def test_struct_layouts_match_the_library():
 
 
 @pytest.mark.parametrize("t", [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S])
-def test_host_repack_is_the_oracles_permutation(t):
+def test_host_repack_is_a_permutation_in_run_order(t):
     rng = np.random.default_rng(t)
     n = 256
     blocks = synth.random_blocks(t, n, rng)
     runs = np.empty_like(blocks)
     L = _lib.lib()
     assert L.moe_to_runs(t, blocks.ctypes.data, n, runs.ctypes.data) == _lib.MOE_OK
-    assert np.array_equal(runs.reshape(-1), O.to_runs(t, blocks).reshape(-1))
+    assert np.array_equal(np.sort(runs.reshape(-1)), np.sort(blocks.reshape(-1)))
+    if t != synth.Q4_K:  # Q4_K keeps d, dmin and the scales as one 16-byte piece; the others are the reference's runs
+        assert np.array_equal(runs.reshape(-1), O.to_runs(t, blocks).reshape(-1))
+    else:
+        assert np.array_equal(runs.reshape(-1)[:n * 128].reshape(n, 128), blocks[:, 16:])
+        assert np.array_equal(runs.reshape(-1)[n * 128:].reshape(n, 16), blocks[:, :16])
     back = np.empty_like(blocks)
     assert L.moe_from_runs(t, runs.ctypes.data, n, back.ctypes.data) == _lib.MOE_OK
     assert np.array_equal(back, blocks)
