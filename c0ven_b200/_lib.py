@@ -13,7 +13,7 @@ FLAG_PROFILE, FLAG_NO_TENSOR = 1, 2
 STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", "copies")
 
 SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_layer_forward_device", "moe_layer_sync",
-           "moe_layer_read_route", "moe_layer_read_stats", "moe_layer_stage_ms", "moe_layer_stream", "moe_last_error",
+           "moe_layer_read_route", "moe_layer_read_stats", "moe_layer_stage_ms", "moe_layer_set_profiling", "moe_layer_stream", "moe_last_error",
            "moe_abi_layout", "moe_to_runs", "moe_from_runs",
            "moe_route_rows_static", "moe_route_rows_static_error", "moe_layer_route_device", "moe_layer_read_counts", "moe_layer_counts_device",
            "moe_layer_wire_row_bytes", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
@@ -74,6 +74,7 @@ def lib():
         L.moe_layer_read_route.argtypes = [vp, vp, vp, vp, vp, u32, C.POINTER(u32)]
         L.moe_layer_read_stats.argtypes = [vp, C.POINTER(Stats)]
         L.moe_layer_stage_ms.argtypes = [vp, vp]
+        L.moe_layer_set_profiling.argtypes = [vp, u32]
         L.moe_layer_stream.argtypes = [vp]
         L.moe_layer_stream.restype = vp
         L.moe_last_error.argtypes = [vp]

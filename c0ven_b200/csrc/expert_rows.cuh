@@ -92,9 +92,10 @@ struct Unit<QT_Q8_0> {
     return x;
   }
   template <int M>
-  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc) {
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc, uint32_t n) {
 #pragma unroll
     for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
       const uint8_t *a = acts + t * stride;
       const int s = dot4x4(x.q, *(const int4 *)(a + 16u * u));
       acc[t] = fmaf(x.d * ((const float *)(a + K))[u / 2], (float)s, acc[t]);
@@ -136,7 +137,7 @@ struct Unit<QT_Q4_K> {
     }
   }
   template <int M>
-  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc) {
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc, uint32_t n) {
     const uint32_t b = u / 8, j = u % 8, p = j / 2, hf = j & 1;
     int sc_lo, m_lo, sc_hi, m_hi;
     scale_min(x, 2 * p, sc_lo, m_lo);
@@ -148,6 +149,7 @@ struct Unit<QT_Q4_K> {
     const uint32_t dsz = act_d_bytes(true, K);
 #pragma unroll
     for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
       const uint8_t *a = acts + t * stride;
       const uint8_t *av = a + 256 * b + 64 * p + 16 * hf;
       const int s_lo = dot4x4(lo, *(const int4 *)av), s_hi = dot4x4(hi, *(const int4 *)(av + 32));
@@ -181,7 +183,7 @@ struct Unit<QT_Q6_K> {
     return x;
   }
   template <int M>
-  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc) {
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc, uint32_t n) {
     const uint32_t b = u / 8, j = u % 8, h = j / 4, jj = j % 4, sh = jj < 2 ? 0 : 2;
     const uint32_t g16 = 8 * h + 2 * (jj >> 1) + (jj & 1);  // the low nibbles' group of 16; the high ones' is 4 on
     uint4 lo, hi;
@@ -196,6 +198,7 @@ struct Unit<QT_Q6_K> {
     const uint32_t dsz = act_d_bytes(true, K);
 #pragma unroll
     for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
       const uint8_t *a = acts + t * stride;
       const uint8_t *av = a + 256 * b + 16 * g16;
       const int s_lo = dot4x4(lo, *(const int4 *)av), s_hi = dot4x4(hi, *(const int4 *)(av + 64));
@@ -231,7 +234,7 @@ struct Unit<QT_IQ3_S> {
   }
   template <int M>
   __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc,
-                                             const uint32_t *grid) {
+                                             uint32_t n, const uint32_t *grid) {
     const uint32_t b = u / 4, c = u % 4;
     int g[16];
 #pragma unroll
@@ -245,6 +248,7 @@ struct Unit<QT_IQ3_S> {
     const int sc0 = 2 * (int)(x.sc & 0xF) + 1, sc1 = 2 * (int)((x.sc >> 4) & 0xF) + 1;
 #pragma unroll
     for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
       const uint8_t *a = acts + t * stride;
       const int4 *av = (const int4 *)(a + 256 * b + 64 * c);
       const int4 a0 = av[0], a1 = av[1], a2 = av[2], a3 = av[3];
@@ -263,11 +267,18 @@ struct Unit<QT_IQ3_S> {
 
 template <int QT, int M>
 __device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride,
-                                         float *acc, const uint32_t *grid) {
+                                         float *acc, uint32_t n, const uint32_t *grid) {
   if constexpr (QT == QT_IQ3_S)
-    Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, grid);
+    Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n, grid);
   else
-    Unit<QT>::template dot<M>(x, K, u, acts, stride, acc);
+    Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n);
+}
+
+// Passes of a warp whose loads are issued together: about 16 loads of 16 bytes a lane, fewer when many activation rows
+// already fill the registers with accumulators.
+__host__ __device__ constexpr int rows_batch(int nmat, int nu, int m) {
+  const int want = 16 / (nmat * nu) > 0 ? 16 / (nmat * nu) : 1, cap = m >= 4 ? 4 : 8;
+  return want < cap ? want : cap;
 }
 
 // NMAT 2: h[row][r] = swiglu(gate_r . x, up_r . x); NMAT 1: y[row][r] = down_r . h. One CTA of 8 warps per (row tile,
@@ -289,6 +300,36 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
     slot = 0, n = min((uint32_t)M, a.dense_rows - start);
   }
   const uint32_t K = a.K, stride = act_row_stride(q8k, K), dsz = act_d_bytes(q8k, K);
+  const uint32_t upr = K / Unit<QT>::kValues;  // units per weight row
+  const uint64_t nblk = (uint64_t)a.R * (K / block_values(QT));
+  const uint8_t *w0 = a.w0 + (uint64_t)slot * a.slice_bytes;
+  const uint8_t *w1 = NMAT == 2 ? a.w1 + (uint64_t)slot * a.slice_bytes : nullptr;
+  const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, li = lane % G, sub = lane / G;
+  constexpr uint32_t RPP = 32 / G;  // weight rows a warp takes per pass
+  constexpr int NU = UPL > 0 ? UPL : 1;
+  constexpr int RB = rows_batch(NMAT, NU, M);  // passes whose loads go out together
+  using Raw = typename Unit<QT>::Raw;
+  const uint32_t rows_per_warp = UPL > 0 ? RPP * RB : a.rows_per_cta / 8;
+  const uint32_t r_begin = blockIdx.x * (8 * rows_per_warp) + warp * rows_per_warp;
+
+  // With the row length known at compile time, every load of the warp's rows goes out first, before the activations
+  // are staged: the weights come from HBM and their latency is the kernel's, so as many bytes as the registers hold
+  // are put in flight at once.
+  Raw raw[RB][NMAT][NU];
+  if constexpr (UPL > 0) {
+#pragma unroll
+    for (int b = 0; b < RB; b++) {
+      const uint32_t r = r_begin + b * RPP + sub;
+      if (r < a.R) {
+#pragma unroll
+        for (int j = 0; j < NU; j++) {
+          raw[b][0][j] = Unit<QT>::fetch(w0, nblk, K, r, li + G * j, nullptr);
+          if constexpr (NMAT == 2) raw[b][1][j] = Unit<QT>::fetch(w1, nblk, K, r, li + G * j, nullptr);
+        }
+      }
+    }
+  }
+
   uint32_t *grid = (uint32_t *)(smem + M * stride);
   if constexpr (QT == QT_IQ3_S)
     for (uint32_t i = threadIdx.x; i < 512; i += 256) grid[i] = grid_global[i];
@@ -313,48 +354,7 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   }
   __syncthreads();
 
-  const uint32_t upr = K / Unit<QT>::kValues;  // units per weight row
-  const uint64_t nblk = (uint64_t)a.R * (K / block_values(QT));
-  const uint8_t *w0 = a.w0 + (uint64_t)slot * a.slice_bytes;
-  const uint8_t *w1 = NMAT == 2 ? a.w1 + (uint64_t)slot * a.slice_bytes : nullptr;
-  const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, li = lane % G, sub = lane / G;
-  constexpr uint32_t RPP = 32 / G;  // weight rows a warp takes per pass
-  const uint32_t rows_per_warp = a.rows_per_cta / 8;
-  const uint32_t r_begin = blockIdx.x * a.rows_per_cta + warp * rows_per_warp;
-  constexpr int NU = UPL > 0 ? UPL : 1;
-  using Raw = typename Unit<QT>::Raw;
-
-  for (uint32_t rr = 0; rr < rows_per_warp; rr += RPP) {
-    const uint32_t r = r_begin + rr + sub;
-    float acc[NMAT][M];
-#pragma unroll
-    for (int m = 0; m < NMAT; m++)
-#pragma unroll
-      for (int t = 0; t < M; t++) acc[m][t] = 0.0f;
-    if (r < a.R) {
-      if constexpr (UPL > 0) {
-        Raw raw[NMAT][NU];
-#pragma unroll
-        for (int j = 0; j < NU; j++) {
-          raw[0][j] = Unit<QT>::fetch(w0, nblk, K, r, li + G * j, grid);
-          if constexpr (NMAT == 2) raw[1][j] = Unit<QT>::fetch(w1, nblk, K, r, li + G * j, grid);
-        }
-#pragma unroll
-        for (int j = 0; j < NU; j++) {
-          unit_dot<QT, M>(raw[0][j], K, li + G * j, smem, stride, acc[0], grid);
-          if constexpr (NMAT == 2) unit_dot<QT, M>(raw[1][j], K, li + G * j, smem, stride, acc[1], grid);
-        }
-      } else {
-        for (uint32_t u = li; u < upr; u += G) {
-          const Raw x0 = Unit<QT>::fetch(w0, nblk, K, r, u, grid);
-          unit_dot<QT, M>(x0, K, u, smem, stride, acc[0], grid);
-          if constexpr (NMAT == 2) {
-            const Raw x1 = Unit<QT>::fetch(w1, nblk, K, r, u, grid);
-            unit_dot<QT, M>(x1, K, u, smem, stride, acc[1], grid);
-          }
-        }
-      }
-    }
+  auto finish = [&](float (&acc)[NMAT][M], uint32_t r) {
 #pragma unroll
     for (int m = 0; m < NMAT; m++)
 #pragma unroll
@@ -369,6 +369,46 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
           if constexpr (NMAT == 2) v = swiglu(acc[0][t], acc[1][t], a.limit);
           a.out[(uint64_t)(start + t) * a.out_stride + r] = v;
         }
+    }
+  };
+
+  if constexpr (UPL > 0) {
+#pragma unroll
+    for (int b = 0; b < RB; b++) {
+      const uint32_t r = r_begin + b * RPP + sub;
+      float acc[NMAT][M];
+#pragma unroll
+      for (int m = 0; m < NMAT; m++)
+#pragma unroll
+        for (int t = 0; t < M; t++) acc[m][t] = 0.0f;
+      if (r < a.R) {
+#pragma unroll
+        for (int j = 0; j < NU; j++) {
+          unit_dot<QT, M>(raw[b][0][j], K, li + G * j, smem, stride, acc[0], n, grid);
+          if constexpr (NMAT == 2) unit_dot<QT, M>(raw[b][1][j], K, li + G * j, smem, stride, acc[1], n, grid);
+        }
+      }
+      finish(acc, r);
+    }
+  } else {
+    for (uint32_t rr = 0; rr < rows_per_warp; rr += RPP) {
+      const uint32_t r = r_begin + rr + sub;
+      float acc[NMAT][M];
+#pragma unroll
+      for (int m = 0; m < NMAT; m++)
+#pragma unroll
+        for (int t = 0; t < M; t++) acc[m][t] = 0.0f;
+      if (r < a.R) {
+        for (uint32_t u = li; u < upr; u += G) {
+          const Raw x0 = Unit<QT>::fetch(w0, nblk, K, r, u, nullptr);
+          unit_dot<QT, M>(x0, K, u, smem, stride, acc[0], n, grid);
+          if constexpr (NMAT == 2) {
+            const Raw x1 = Unit<QT>::fetch(w1, nblk, K, r, u, nullptr);
+            unit_dot<QT, M>(x1, K, u, smem, stride, acc[1], n, grid);
+          }
+        }
+      }
+      finish(acc, r);
     }
   }
 }

@@ -9,8 +9,12 @@ namespace moe {
 template <int QT, int NMAT, int M, int G, int UPL>
 static cudaError_t launch_one(ExpertRowsArgs a, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st) {
   constexpr bool q8k = act_is_q8k(QT);
-  const uint32_t rpp = 32 / G;
-  if (a.rows_per_cta < 8 * rpp) a.rows_per_cta = 8 * rpp;
+  // With the row length known at compile time a CTA's eight warps take one batch of passes each; else the caller's count.
+  constexpr uint32_t rpp = 32 / G;
+  if (UPL > 0)
+    a.rows_per_cta = 8 * rpp * rows_batch(NMAT, UPL, M);
+  else if (a.rows_per_cta < 8 * rpp)
+    a.rows_per_cta = 8 * rpp;
   const size_t smem = (size_t)M * act_row_stride(q8k, a.K) + (QT == QT_IQ3_S ? 2048 : 0);
   auto kernel = k_expert_rows<QT, NMAT, M, G, UPL>;
   if (smem > 48 * 1024) {

@@ -114,7 +114,21 @@ struct moe_layer {
   uint32_t E = 0, F = 0, NE = 0, K = 0, N = 0, local = 0, Tmax = 0;
   uint64_t Rmax = 0;  // expert rows a call may bring: max_tokens * n_used, or max_expert_rows
   bool has_shared = false, profile = false, can_tensor = false;
-  std::unique_ptr<Stream> stream;
+  std::unique_ptr<Stream> stream, aux;  // aux: the shared expert runs beside the routed ones
+  std::unique_ptr<Event> fork_ev, join_ev;
+  // Steps of few rows are bound by launches, not work: the whole call is recorded once per (rows, buffers, stream)
+  // as a CUDA graph and replayed (the reference records its per-width step lists once too: core/ze/ze.h:155-189).
+  struct StepGraph {
+    uint32_t T;
+    const float *x;
+    float *out;
+    cudaStream_t st;
+    cudaGraphExec_t exec;
+    uint64_t kernels;
+    uint32_t seen;
+  };
+  std::vector<StepGraph> graphs;
+  bool graphs_ok = true;
   // Weights.
   DeviceBuffer<float> router, bias;
   DeviceBuffer<uint8_t> wg, wu, wd, sg, su, sd;
@@ -190,6 +204,8 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->profile = c.flags & MOE_FLAG_PROFILE;
   l->can_tensor = !(c.flags & MOE_FLAG_NO_TENSOR) && c.n_embd % kTileK == 0 && c.n_ff % kTileM == 0;
   l->stream = std::make_unique<Stream>();
+  l->aux = std::make_unique<Stream>();
+  l->fork_ev = std::make_unique<Event>(), l->join_ev = std::make_unique<Event>();
   cudaStream_t st = l->stream->get();
   const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, T = l->Tmax;
   const uint64_t A = (uint64_t)T * K;
@@ -284,12 +300,21 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   if (l->has_shared && !l->shared_x_same) quantize_rows(l, x, T, E, l->xq_shared, st);
   mark(l, ST_ROUTER, st);
   if (!by_pieces) {
-    const size_t smem = (size_t)8 * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float);
+    // Steps of up to 2 rows stage only those (8 KB a row); longer ones 8 rows a pass.
+    const uint32_t tm = T <= 2 ? T : 8;
+    const size_t smem = (size_t)tm * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float);
     if (!l->rows_attr_set) {
-      CUDA_OK(cudaFuncSetAttribute(k_router_logits_rows<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      const int most = (int)((size_t)8 * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float));
+      CUDA_OK(cudaFuncSetAttribute(k_router_logits_rows<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
       l->rows_attr_set = true;
     }
-    k_router_logits_rows<8><<<dim3((N + 15) / 16, (T + 7) / 8), 128, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+    const dim3 grid((N + 3) / 4, (T + tm - 1) / tm);
+    if (tm == 1)
+      k_router_logits_rows<1><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+    else if (tm == 2)
+      k_router_logits_rows<2><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+    else
+      k_router_logits_rows<8><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
   } else {
     k_router_pieces<<<dim3((NE + 127) / 128, (T + 127) / 128, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
   }
@@ -407,11 +432,74 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   if (l->local != l->NE) throw BadArgument("this call needs every expert on the GPU; an expert-parallel layer goes stage by stage");
   const uint64_t A = (uint64_t)T * l->K;
   stage_route(l, x, T, st);
+  // The shared expert needs only the quantised rows: it runs on a second stream beside the routed experts and joins
+  // before the combine. With per-stage timing on, it runs in line instead, so that its stage can be timed.
+  const bool beside = l->has_shared && !l->profile;
+  if (beside) {
+    l->fork_ev->record(st);
+    CUDA_OK(cudaStreamWaitEvent(l->aux->get(), l->fork_ev->get(), 0));
+    stage_shared(l, T, l->aux->get());
+    l->join_ev->record(l->aux->get());
+  }
   const ActSource src{l->xq_routed.view(), l->xq_routed.h.get(), l->pack.row_src.get()};
   stage_experts(l, src, l->pack, A, l->last_tensor_min, l->y.get(), st);
-  stage_shared(l, T, st);
+  if (beside)
+    CUDA_OK(cudaStreamWaitEvent(st, l->join_ev->get(), 0));
+  else
+    stage_shared(l, T, st);
   stage_combine<float>(l, l->y.get(), T, out, st);
   l->stats.calls++, l->stats.rows += T, l->stats.assignments += A;
+}
+
+constexpr uint32_t kGraphMaxRows = 64;
+
+// forward_device, replayed from a graph when the step is small and has been seen before with the same buffers.
+void forward_step(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {
+  if (l->profile || !l->graphs_ok || T > kGraphMaxRows || l->local != l->NE) return forward_device(l, x, T, out, st);
+  moe_layer::StepGraph *g = nullptr;
+  for (auto &c : l->graphs)
+    if (c.T == T && c.x == x && c.out == out && c.st == st) g = &c;
+  if (g && g->exec) {
+    CUDA_OK(cudaGraphLaunch(g->exec, st));
+    l->stats.kernels += g->kernels, l->stats.calls++, l->stats.rows += T, l->stats.assignments += (uint64_t)T * l->K;
+    l->last_T = T, l->last_pack = &l->pack, l->last_tensor_min = tensor_min_for(l, (uint64_t)T * l->K);
+    return;
+  }
+  if (!g) {  // first sight: run it plainly (this also sets the kernels' attributes); record it the next time
+    if (l->graphs.size() >= 16) {
+      if (l->graphs.front().exec) cudaGraphExecDestroy(l->graphs.front().exec);
+      l->graphs.erase(l->graphs.begin());
+    }
+    l->graphs.push_back(moe_layer::StepGraph{T, x, out, st, nullptr, 0, 1});
+    return forward_device(l, x, T, out, st);
+  }
+  const moe_layer_stats before = l->stats;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+  if (e == cudaSuccess) {
+    try {
+      forward_device(l, x, T, out, st);
+    } catch (...) {
+      cudaStreamEndCapture(st, &graph);
+      if (graph) cudaGraphDestroy(graph);
+      l->graphs_ok = false;
+      l->stats = before;
+      cudaGetLastError();
+      return forward_device(l, x, T, out, st);
+    }
+    e = cudaStreamEndCapture(st, &graph);
+  }
+  if (e == cudaSuccess && graph) e = cudaGraphInstantiate(&g->exec, graph, 0);
+  if (graph) cudaGraphDestroy(graph);
+  if (e != cudaSuccess || !g->exec) {  // recording is an optimisation: without it the call still runs
+    cudaGetLastError();
+    g->exec = nullptr, l->graphs_ok = false, l->stats = before;
+    return forward_device(l, x, T, out, st);
+  }
+  g->kernels = l->stats.kernels - before.kernels;
+  l->stats = before;
+  CUDA_OK(cudaGraphLaunch(g->exec, st));
+  l->stats.kernels += g->kernels, l->stats.calls++, l->stats.rows += T, l->stats.assignments += (uint64_t)T * l->K;
 }
 
 // After the stream has drained: a kernel whose wait ran out left the error word set.
@@ -470,6 +558,9 @@ MOE_API void moe_layer_destroy(moe_layer *l) {
   if (!l) return;
   cudaSetDevice(l->cfg.device);
   if (l->stream) cudaStreamSynchronize(l->stream->get());
+  if (l->aux) cudaStreamSynchronize(l->aux->get());
+  for (auto &g : l->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
   delete l;
 }
 
@@ -481,7 +572,7 @@ MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, f
     cudaStream_t st = l->stream->get();
     const size_t bytes = (size_t)T * l->E * sizeof(float);
     CUDA_OK(cudaMemcpyAsync(l->x.get(), x, bytes, cudaMemcpyHostToDevice, st));
-    forward_device(l, l->x.get(), T, l->out.get(), st);
+    forward_step(l, l->x.get(), T, l->out.get(), st);
     CUDA_OK(cudaMemcpyAsync(out, l->out.get(), bytes, cudaMemcpyDeviceToHost, st));
     if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
     l->stats.h2d_bytes += bytes, l->stats.d2h_bytes += bytes;
@@ -496,7 +587,7 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
   return guarded(l, [&] {
     if (!x_dev || !out_dev || T == 0 || T > l->Tmax) throw BadArgument("x and out are required, and 1 <= T <= max_tokens");
     cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
-    forward_device(l, x_dev, T, out_dev, st);
+    forward_step(l, x_dev, T, out_dev, st);
     if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
   });
 }
@@ -666,6 +757,15 @@ MOE_API moe_status moe_layer_stage_ms(moe_layer *l, float *ms) {
     if (!l->profile || !l->ev_valid) throw BadArgument("the layer was not created with MOE_FLAG_PROFILE, or no call has run");
     CUDA_OK(cudaEventSynchronize(l->ev[MOE_STAGES]->get()));
     for (int i = 0; i < MOE_STAGES; i++) ms[i] = Event::ms(*l->ev[i], *l->ev[i + 1]);
+  });
+}
+
+MOE_API moe_status moe_layer_set_profiling(moe_layer *l, uint32_t on) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    l->stream->wait(0);
+    l->profile = on != 0, l->ev_valid = false;
   });
 }
 

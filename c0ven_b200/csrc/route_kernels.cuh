@@ -125,39 +125,49 @@ static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restri
 // order, the pieces then added in order, and an expert's bias last. Both kernels and the CPU oracle keep this one
 // order, so that the logits, and with them the chosen experts, agree bit for bit whatever the row count.
 
-// Few rows (up to 8 per CTA pass): 4 weight rows per warp, 8 lanes a row, lane s taking piece s.
+// Few rows (up to TM per CTA pass): a CTA is one warp and takes 4 weight rows, 8 lanes a row, lane s taking piece s, so
+// that a step of one row still spreads the router's 4 MB over 129 CTAs; 8 loads of 16 bytes in flight per lane (a piece is a multiple of 32 values).
 template <int TM>
-static __global__ void __launch_bounds__(128) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
-                                                           const float *__restrict__ W, uint32_t N,
-                                                           const float *__restrict__ bias, uint32_t NE,
-                                                           float *__restrict__ rl) {
+static __global__ void __launch_bounds__(32) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
+                                                          const float *__restrict__ W, uint32_t N,
+                                                          const float *__restrict__ bias, uint32_t NE,
+                                                          float *__restrict__ rl) {
   extern __shared__ __align__(16) float xs[];  // TM rows, each piece padded by 4 floats to spread the banks
   const uint32_t piece = E / kRouterPieces, pstride = piece + 4, rstride = kRouterPieces * pstride;
   const uint32_t t0 = blockIdx.y * TM, tn = min((uint32_t)TM, T - t0);
-  for (uint32_t i = threadIdx.x; i < TM * (E / 4); i += 128) {
+  const uint32_t lane = threadIdx.x, s = lane % 8, row = blockIdx.x * 4 + lane / 8;
+  // The first weights are on their way while the rows are staged.
+  const float4 *w = (const float4 *)(W + (uint64_t)min(row, N - 1) * E + s * piece);
+  float4 wq[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) wq[i] = __ldg(w + i);
+  for (uint32_t i = lane; i < TM * (E / 4); i += 32) {
     const uint32_t t = i / (E / 4), k4 = i % (E / 4), k = 4 * k4;
     const float4 v = t < tn ? ((const float4 *)(x + (uint64_t)(t0 + t) * E))[k4] : make_float4(0, 0, 0, 0);
     *(float4 *)(xs + t * rstride + (k / piece) * pstride + k % piece) = v;
   }
-  __syncthreads();
-  const uint32_t lane = threadIdx.x % 32, s = lane % 8;
-  const uint32_t row = (blockIdx.x * 4 + threadIdx.x / 32) * 4 + lane / 8;
+  __syncwarp();
   float p[TM];
 #pragma unroll
   for (int t = 0; t < TM; t++) p[t] = 0.0f;
-  if (row < N) {
-    const float4 *w = (const float4 *)(W + (uint64_t)row * E + s * piece);
-    const float *xp = xs + s * pstride;
-#pragma unroll 8
-    for (uint32_t i = 0; i < piece / 4; i++) {
-      const float4 wv = __ldg(w + i);
+  const float *xp = xs + s * pstride;
+  for (uint32_t i0 = 0; i0 < piece / 4; i0 += 8) {
+    float4 cur[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) cur[i] = wq[i];
+    if (i0 + 8 < piece / 4) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) wq[i] = __ldg(w + i0 + 8 + i);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
 #pragma unroll
       for (int t = 0; t < TM; t++) {
-        const float4 xv = *(const float4 *)(xp + t * rstride + 4 * i);
-        p[t] = fmaf(xv.x, wv.x, p[t]);
-        p[t] = fmaf(xv.y, wv.y, p[t]);
-        p[t] = fmaf(xv.z, wv.z, p[t]);
-        p[t] = fmaf(xv.w, wv.w, p[t]);
+        const float4 xv = *(const float4 *)(xp + t * rstride + 4 * (i0 + i));
+        p[t] = fmaf(xv.x, cur[i].x, p[t]);
+        p[t] = fmaf(xv.y, cur[i].y, p[t]);
+        p[t] = fmaf(xv.z, cur[i].z, p[t]);
+        p[t] = fmaf(xv.w, cur[i].w, p[t]);
       }
     }
   }

@@ -82,7 +82,7 @@ MOE_API moe_status moe_route_rows_static(const float *x_dev, uint32_t T, uint32_
   // Both regions are written in full for the rows of this call before they are read (every logit of rows < T; every
   // expert's count of every chunk), so the last call's contents need no clearing.
   const size_t smem = (size_t)8 * kRouterPieces * (n_embd / kRouterPieces + 4) * sizeof(float);
-  k_router_logits_rows<8><<<dim3((N + 15) / 16, (T + 7) / 8), 128, smem, st>>>(x_dev, T, n_embd, router_dev, N, bias_dev, n_experts, rl);
+  k_router_logits_rows<8><<<dim3((N + 3) / 4, (T + 7) / 8), 32, smem, st>>>(x_dev, T, n_embd, router_dev, N, bias_dev, n_experts, rl);
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
   k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(rl, nullptr, nullptr, nullptr, 0, T, n_experts, n_used, ids_dev, w_dev, gate_dev, hist);
   e = cudaGetLastError();

@@ -136,6 +136,9 @@ class MoELayer:
         self._check(_lib.lib().moe_layer_read_stats(self._h, C.byref(s)))
         return {n: getattr(s, n) for n, _ in _lib.Stats._fields_}
 
+    def set_profiling(self, on: bool):
+        self._check(_lib.lib().moe_layer_set_profiling(self._h, int(on)))
+
     def stage_ms(self) -> dict:
         ms = np.zeros(len(_lib.STAGES), dtype=np.float32)
         self._check(_lib.lib().moe_layer_stage_ms(self._h, _ptr(ms)))

@@ -155,6 +155,9 @@ MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, ui
 MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out);
 /* With MOE_FLAG_PROFILE: the last call's time in each stage, milliseconds, MOE_STAGES floats. Waits for the stream. */
 MOE_API moe_status moe_layer_stage_ms(moe_layer *l, float *ms);
+/* Turns the per-stage timing of MOE_FLAG_PROFILE on or off after create. While it is on, the stages run one after
+ * another on one stream and small steps are not replayed from recorded graphs, so a call is slower than without. */
+MOE_API moe_status moe_layer_set_profiling(moe_layer *l, uint32_t on);
 /* The layer's cudaStream_t. */
 MOE_API void *moe_layer_stream(moe_layer *l);
 
