@@ -95,8 +95,16 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(sm))
 
 
-def algorithmic(w: dict, T: int, experts_hit: int) -> dict:
-    """Bytes and flops the layer needs for T rows that hit `experts_hit` distinct experts."""
+_STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", "copies")
+
+# DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), by
+# (workload, stage); the summaries under profiles/ say which capture. None: not captured.
+TRAFFIC = {("ragged3521_q4_k_zipf", "gate_up"): 135.6e6}
+
+
+def algorithmic(w: dict, T: int, experts_hit: int, world: int = 1) -> dict:
+    """Bytes and flops one GPU's part of the layer needs for its T rows, with `experts_hit` distinct experts hit there.
+    Expert parallel, the rows a GPU's experts compute are taken as its share, T * K, of all the rows."""
     gt, dt = w["gate_type"], w.get("down_type") or w["gate_type"]
     sgt, sdt = w.get("shexp_gate_type") or gt, w.get("shexp_down_type") or dt
     routed, shared = synth.expert_bytes(gt, dt, E, F), synth.expert_bytes(sgt, sdt, E, F)
@@ -122,7 +130,7 @@ def run_reference(args, w):
         return
     from oracle import oracle
 
-    T_full = w["tokens"]
+    T_full = args.tokens or w["tokens"]
     T = min(T_full, args.cpu_tokens)
     layer, x = build_layer(w), synth.make_input(T_full, E, seed=1)[:T]
     threads = oracle.threads()
@@ -144,7 +152,7 @@ def run_reference(args, w):
 def run_gpu(args, w):
     import torch
 
-    from c0ven_b200 import MoELayer
+    from c0ven_b200 import MoELayer, ep
 
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -154,39 +162,66 @@ def run_gpu(args, w):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    T = w["tokens"]
-    layer = build_layer(w)
+    T_total, nlayers = args.tokens or w["tokens"], w.get("layers", 1)
+    scaling = w.get("scaling", "weak")
+    # Weak scaling: every rank brings the workload's rows. Strong: the workload's rows are shared out.
+    T = T_total if world == 1 or scaling == "weak" else max(1, T_total // world)
+    base = build_layer(w)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
     x_host = torch.from_numpy(synth.make_input(T, E, seed=1 + rank)).pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
-    if world == 1:
-        gpu = MoELayer(layer, max_tokens=T, device=local, profile=False, tensor_min_rows=args.tensor_min)
-        x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
 
-        def step():
-            gpu.forward_device(x_dev.data_ptr(), T, out_dev.data_ptr())
+    # The layers of a stack share their experts' bytes on the host (each layer still has its own copy in HBM, so the
+    # traffic is a stack's) and differ in their routers.
+    layers, moes, main_sp = [], [], None
+    for i in range(nlayers):
+        lw = base if i == 0 else dict(base, router=(np.random.default_rng(100 + i).standard_normal((NE, E)) * 0.02).astype(np.float32))
+        if world == 1:
+            m = MoELayer(lw, max_tokens=T, device=local, profile=False, tensor_min_rows=args.tensor_min)
+            layers.append(m), moes.append(None)
+            main_sp = main_sp or m.stream
+        else:
+            st = ep.GpuStages(lw, rank, world, max_tokens=T, device=local, y_f16=True, profile=False,
+                              tensor_min_rows=args.tensor_min, stream_ptr=main_sp)
+            layers.append(st.moe), moes.append(ep.ExpertParallelMoE(st))
+            main_sp = main_sp or st.moe.stream
+    stream = torch.cuda.ExternalStream(main_sp, device=local)
+    x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
+    res, xn = torch.empty_like(x_dev), torch.empty_like(x_dev)
 
-        def step_host():
-            gpu.forward(x_host.numpy(), out_host.numpy())
-    else:
-        # Expert parallel: every rank holds 512 / N experts and brings its own T rows (weak scaling).
-        from c0ven_b200 import ep
+    def run_layer(i, xin, xout):
+        if world == 1:
+            layers[i].forward_device(xin.data_ptr(), T, xout.data_ptr(), main_sp)
+        else:
+            moes[i].forward(xin, xout)
 
-        stages = ep.GpuStages(layer, rank, world, max_tokens=T, device=local, y_f16=True, profile=False,
-                              tensor_min_rows=args.tensor_min)
-        moe, gpu = ep.ExpertParallelMoE(stages), stages.moe
-        x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
+    def step():
+        """One pass over the batch; queued on the main stream. A stack is x <- x + moe_l(rmsnorm(x)) for every layer:
+        attention replaced by the identity, the norm there only to keep 48 random layers' values bounded."""
+        with torch.cuda.stream(stream):
+            if nlayers == 1:
+                run_layer(0, x_dev, out_dev)
+                return
+            res.copy_(x_dev)
+            for i in range(nlayers):
+                torch.mul(res, torch.rsqrt(res.square().mean(-1, keepdim=True) + 1e-6), out=xn)
+                run_layer(i, xn, out_dev)
+                res.add_(out_dev)
 
-        def step():
-            moe.forward(x_dev, out_dev)
+    def step_host():
+        """The same from pinned host rows to pinned host rows."""
+        if world == 1 and nlayers == 1:
+            layers[0].forward(x_host.numpy(), out_host.numpy())  # the C ABI's host-buffer call
+            return
+        with torch.cuda.stream(stream):
+            x_dev.copy_(x_host, non_blocking=True)
+        step()
+        with torch.cuda.stream(stream):
+            out_host.copy_(res if nlayers > 1 else out_dev, non_blocking=True)
+        stream.synchronize()
 
-        def step_host():
-            with torch.cuda.stream(stages.stream):
-                xd = x_host.to("cuda", non_blocking=True)
-                od = moe.forward(xd)
-                out_host.copy_(od, non_blocking=True)
-            gpu.sync()
-    stream = torch.cuda.ExternalStream(gpu.stream, device=local)
+    def sync():
+        stream.synchronize()
 
     def barrier():
         torch.cuda.synchronize()
@@ -194,13 +229,15 @@ def run_gpu(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def kernels():
+        return sum(m.stats()["kernels"] for m in layers)
+
     # Timed steps run as a caller would run them: no per-stage timing, the shared expert beside the routed ones, small
     # steps replayed from their recorded graph. The stages are timed afterwards, in a few more steps with the timing on.
-    gpu.set_profiling(False)
     for _ in range(args.warmup):
         step()
-    gpu.sync()
-    k0 = gpu.stats()["kernels"]
+    sync()
+    k0 = kernels()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
@@ -208,36 +245,37 @@ def run_gpu(args, w):
         for i in range(args.steps):
             flush.fill_(i & 0xFF)  # L2 flush between timed iterations, outside the timed interval
             torch.cuda.synchronize()
-            with torch.cuda.stream(stream):
-                starts[i].record(stream)
-                step()
-                ends[i].record(stream)
-            gpu.sync()
+            starts[i].record(stream)
+            step()
+            ends[i].record(stream)
+            sync()
         barrier()
-    launches = gpu.stats()["kernels"] - k0
-    gpu.set_profiling(True)
-    step()
-    gpu.sync()
-    nprof = max(3, min(args.steps, 10))
-    stage = {k: 0.0 for k in gpu.stage_ms()}
-    for i in range(nprof):
-        flush.fill_(i & 0xFF)
-        torch.cuda.synchronize()
-        step()
-        gpu.sync()
-        for k, v in gpu.stage_ms().items():
-            stage[k] += v / nprof
-    gpu.set_profiling(False)
+    launches = kernels() - k0
     ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / args.steps
     t = torch.tensor([ms], device="cuda")
     if dist:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    st = gpu.stats()
 
-    # End to end: host buffers (pinned) in, host buffers out, the copies inside the timed region. One GPU: the C ABI's
-    # moe_layer_forward; expert parallel: the same stages with the copies on the layer's stream.
-    xh = x_host.numpy()
+    for m in layers:
+        m.set_profiling(True)
+    step()
+    sync()
+    nprof = max(3, min(args.steps, 10))
+    stage = {k: 0.0 for k in _STAGES}
+    for i in range(nprof):
+        flush.fill_(i & 0xFF)
+        torch.cuda.synchronize()
+        step()
+        sync()
+        for m in layers:
+            for k, v in m.stage_ms().items():
+                stage[k] += v / nprof
+    for m in layers:
+        m.set_profiling(False)
+    stats = [m.stats() for m in layers]
+
+    # End to end: pinned host rows in, pinned host rows out, the copies inside the timed region.
     for _ in range(2):
         step_host()
     barrier()
@@ -252,54 +290,54 @@ def run_gpu(args, w):
     e2e_s = float(t.item())
 
     def teardown():
-        # Everything the layer's stream touched is freed and handed back to the driver while that stream still exists;
-        # then the group goes, then the layer.
-        nonlocal x_dev, out_dev, flush
+        # Every rank waits for the others, then the process ends here, without the interpreter's teardown: the order in
+        # which that would drop the layers' streams, the collectives' and the allocator's blocks used on them is not
+        # ours to set, and a block freed after its stream has gone aborts the process.
         torch.cuda.synchronize()
-        del x_dev, out_dev, flush
-        if world > 1:
-            stages._bufs.clear()
-        torch.cuda.synchronize()
-        torch.cuda.empty_cache()
         if world > 1:
             dist.barrier()
-            dist.destroy_process_group()
-            stages.close()
-        else:
-            gpu.close()
+        sys.stdout.flush()
+        os._exit(0)
 
     if rank != 0:
         teardown()
         return
     peaks = measured_peaks()
-    alg = algorithmic(w, T, st["last_experts_hit"])
+    hit = sum(s["last_experts_hit"] for s in stats)
+    tensor_rows = sum(s["last_tensor_rows"] for s in stats)
+    algs = [algorithmic(w, T, s["last_experts_hit"], world) for s in stats]
+    alg = {k: sum(a[k] for a in algs) for k in algs[0]}
     dom = max(("gate_up", "down"), key=lambda k: stage[k])
     dom_ms = stage[dom]
-    tensor_path = st["last_tensor_rows"] > 0
-    if tensor_path:
+    if tensor_rows > 0:
         achieved = alg["flops_" + dom] / (dom_ms * 1e-3) / 1e12
         roof = dict(bound="tensor", achieved=achieved, peak=peaks["bf16_tflops"], unit="TFLOP/s", frac=achieved / peaks["bf16_tflops"])
     else:
         achieved = alg["bytes_" + dom] / (dom_ms * 1e-3) / 1e9
         roof = dict(bound="hbm", achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s", frac=achieved / peaks["hbm_gbs"])
-    roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=None)
+    roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=TRAFFIC.get((w["name"], dom)))
     cpu = None
-    if world == 1 and not args.no_cpu:
+    if world == 1 and not args.no_cpu and nlayers == 1:
         from oracle import oracle
 
         Tc = min(T, args.cpu_tokens)
         threads = oracle.threads()
-        cpu_step(layer, xh[:Tc], threads)
-        dt = statistics.median([cpu_step(layer, xh[:Tc], threads) for _ in range(3)])
+        xh = x_host.numpy()
+        cpu_step(base, xh[:Tc], threads)
+        dt = statistics.median([cpu_step(base, xh[:Tc], threads) for _ in range(3)])
         cpu = dict(value=Tc / dt, unit=UNIT, cores=threads, kind="port", sample=f"first {Tc} of {T} rows, median of 3 passes")
+    if world == 1:
+        par = "1 GPU"
+    else:
+        par = (f"expert parallel x{world}: {NE // world} experts and {T} rows per GPU ({scaling} scaling), "
+               "all-to-all of q8 rows out and f16 results back")
     line = dict(metric=METRIC, value=world * T / (ms * 1e-3), unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
-                ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
-                dtype="bf16" if tensor_path else "i8", data="synthetic",
-                config=dict(workload=w["name"], rows=T, runs=w.get("runs"), hidden=E, ffn=F, experts=NE, top_k=K,
-                            weights=synth.TYPE_NAMES[w["gate_type"]], zipf_s=w.get("zipf_s", 0.0),
-                            experts_hit=st["last_experts_hit"], tiles=st["last_tiles"],
-                            parallelism="1 GPU" if world == 1 else f"expert parallel x{world}: {NE // world} experts and {T} rows per GPU, "
-                            "all-to-all of q8 rows out and f16 results back", l2="flushed between timed steps"),
+                ms_per_step=ms, higher_is_better=True, scaling=scaling, vs_baseline=None,
+                dtype="f16" if tensor_rows > 0 else "i8", data="synthetic",
+                config=dict(workload=w["name"], rows=world * T, rows_per_gpu=T, layers=nlayers, runs=w.get("runs"), hidden=E, ffn=F,
+                            experts=NE, top_k=K, weights=synth.TYPE_NAMES[w["gate_type"]], zipf_s=w.get("zipf_s", 0.0),
+                            experts_hit=hit, tiles=sum(s["last_tiles"] for s in stats), parallelism=par,
+                            l2="flushed between timed steps"),
                 roofline=roof, stage_ms=stage, layer_bytes=alg["bytes_layer"], layer_flops=alg["flops_layer"],
                 cpu_baseline=cpu, clocks=clocks.summary(),
                 e2e=dict(value=world * T / e2e_s, unit=UNIT, h2d_bytes_per_step=T * E * 4, d2h_bytes_per_step=T * E * 4,
@@ -315,22 +353,21 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="ragged3521_q4_k_zipf", choices=[k for k, v in synth.CONFIGS.items() if isinstance(v["tokens"], int)])
+    ap.add_argument("--workload", default="ragged3521_q4_k_zipf", choices=list(synth.CONFIGS))
     ap.add_argument("--cpu-tokens", type=int, default=3521, help="rows of the batch the CPU baseline takes per pass")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0, help="rows instead of the workload's (the sweep's points)")
     ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     w = workload(args.workload)
+    if not isinstance(w["tokens"], int) and not args.tokens:
+        args.tokens = w["tokens"][-2]  # a sweep's default point; --tokens picks another
     if args.impl == "reference":
         run_reference(args, w)
     else:
         run_gpu(args, w)
-        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
-            # Under torchrun, leave without the interpreter's teardown: the order in which it would drop the collectives'
-            # streams and the allocator's blocks is not ours to set.
-            sys.stdout.flush()
-            os._exit(0)
+
 
 
 if __name__ == "__main__":

@@ -42,6 +42,7 @@ struct ExpertRowsArgs {
   const MoeGroup *groups;   // null: dense_rows rows of slot 0, taken M at a time
   const uint32_t *ngroups;
   uint32_t dense_rows;
+  uint32_t n_min, n_max;    // of the groups, only those with n_min <= n <= n_max rows are this launch's (0, 0: all)
   float *out;  // out[expert-order row][r]
   uint32_t out_stride;
   float limit;  // SwiGLU limit, 0: off
@@ -294,6 +295,7 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
     if (blockIdx.y >= *a.ngroups) return;
     const MoeGroup g = a.groups[blockIdx.y];
     slot = g.slot, start = g.start, n = g.n;
+    if (a.n_max && (n < a.n_min || n > a.n_max)) return;
   } else {
     start = blockIdx.y * M;
     if (start >= a.dense_rows) return;

@@ -336,6 +336,21 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   l->last_T = T, l->last_pack = &l->pack;
 }
 
+// The integer-dot kernel over a pack's groups. Most groups of a short step hold one or two rows; the kernel for eight
+// rows keeps eight rows' accumulators in registers whatever the group holds, which costs occupancy. So when groups can
+// hold more than two rows, the groups of one or two go to the two-row kernel and only the larger ones to the wide one;
+// each launch passes over the other's groups.
+void launch_rows_by_size(moe_layer *l, uint32_t qt, int nmat, ExpertRowsArgs a, int M, uint32_t max_groups, cudaStream_t st, const char *what) {
+  if (M <= 2) {
+    launched(l, launch_rows(qt, nmat, a, M, max_groups, l->grid.get(), st), what);
+    return;
+  }
+  a.n_min = 1, a.n_max = 2;
+  launched(l, launch_rows(qt, nmat, a, 2, max_groups, l->grid.get(), st), what);
+  a.n_min = 3, a.n_max = kGroupMax;
+  launched(l, launch_rows(qt, nmat, a, M, max_groups, l->grid.get(), st), what);
+}
+
 // The routed experts on the R rows a pack lists: gate/up and SwiGLU into h, h quantised, down into y (expert order).
 void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint32_t tm, float *y, cudaStream_t st) {
   const uint32_t E = l->E, F = l->F, nexp = pk.nexp;
@@ -361,7 +376,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.act = src.view, a.act_row = src.act_row;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
-    launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
+    launch_rows_by_size(l, c.gate_type, 2, a, M, max_groups, st, "experts gate/up");
   }
   quantize_rows(l, l->h.get(), R, F, l->hq_routed, st);
   mark(l, ST_DOWN, st);
@@ -379,7 +394,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.act = l->hq_routed.view(), a.act_row = nullptr;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = y, a.out_stride = E;
-    launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), st), "experts down");
+    launch_rows_by_size(l, c.down_type, 1, a, M, max_groups, st, "experts down");
   }
 }
 

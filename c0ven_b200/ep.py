@@ -47,7 +47,7 @@ class GpuStages:
     """The stages on a GPU, through the C ABI."""
 
     def __init__(self, layer: dict, rank: int, world: int, max_tokens: int, device: int, max_expert_rows: int = 0,
-                 y_f16: bool = True, profile: bool = False, tensor_min_rows: int = 0):
+                 y_f16: bool = True, profile: bool = False, tensor_min_rows: int = 0, stream_ptr: int | None = None):
         from .layer import MoELayer
 
         first, count = owner_ranges(layer["n_experts"], world)[rank]
@@ -57,36 +57,38 @@ class GpuStages:
         self.moe = MoELayer(layer, max_tokens=max_tokens, device=device, expert_first=first, expert_count=count,
                             max_expert_rows=max_expert_rows or max_tokens * layer["n_used"] * world, profile=profile,
                             tensor_min_rows=tensor_min_rows)
-        self.stream = torch.cuda.ExternalStream(self.moe.stream, device=self.device)
+        # The stream every stage is queued on: the layer's own, or the caller's (several layers of a stack share one).
+        self._sp = stream_ptr
+        self.stream = torch.cuda.ExternalStream(stream_ptr or self.moe.stream, device=self.device)
         self.wire = self.moe.wire_row_bytes
         self._bufs = {}
 
     def route(self, x: torch.Tensor) -> torch.Tensor:
         """Routes and packs x's rows; returns the rows per expert, an int32 tensor [n_experts] on the device."""
         self.T = x.shape[0]
-        self.moe.route_device(x.data_ptr(), self.T)
+        self.moe.route_device(x.data_ptr(), self.T, self._sp)
         cnt = self.empty((self.n_experts,), torch.int32, "cnt")
-        self.moe.counts_device(cnt.data_ptr())
+        self.moe.counts_device(cnt.data_ptr(), self._sp)
         return cnt
 
     def gather(self) -> torch.Tensor:
         rows = self.empty((self.T * self.n_used, self.wire), torch.uint8, "rows")
         ids = self.empty((self.T * self.n_used,), torch.int32, "ids")
-        self.moe.gather_rows_device(rows.data_ptr(), ids.data_ptr())
+        self.moe.gather_rows_device(rows.data_ptr(), ids.data_ptr(), self._sp)
         return rows
 
     def experts(self, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         R = rows.shape[0]
         y = self.empty((R, self.n_embd), self.y_dtype, "y_in")
         if R:
-            self.moe.experts_device(rows.data_ptr(), ids.data_ptr(), R, y.data_ptr(), self.y_dtype == torch.float16)
+            self.moe.experts_device(rows.data_ptr(), ids.data_ptr(), R, y.data_ptr(), self.y_dtype == torch.float16, self._sp)
         return y
 
     def shared(self):
-        self.moe.shared_device()
+        self.moe.shared_device(self._sp)
 
     def combine(self, y: torch.Tensor, out: torch.Tensor):
-        self.moe.combine_device(y.data_ptr(), y.dtype == torch.float16, out.data_ptr())
+        self.moe.combine_device(y.data_ptr(), y.dtype == torch.float16, out.data_ptr(), self._sp)
 
     def empty(self, shape, dtype, name=None):
         """A device tensor; with a name, a view of a buffer kept and grown between steps."""

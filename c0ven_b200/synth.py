@@ -87,8 +87,8 @@ def make_input(T: int, n_embd: int, seed=1) -> np.ndarray:
 CONFIGS = {
     "decode1_q8_0": dict(tokens=1, runs=[1], gate_type=Q8_0, zipf_s=0.0),
     "ragged3521_q4_k_zipf": dict(tokens=3521, runs=[1, 8, 512, 3000], gate_type=Q4_K, zipf_s=1.1),
-    "stack48_verify32_iq3_s": dict(tokens=32, runs=[8, 8, 8, 8], gate_type=IQ3_S, zipf_s=0.0, layers=48),
-    "prefill32768_q4_k": dict(tokens=32768, runs=[32768], gate_type=Q4_K, zipf_s=0.0),
+    "stack48_verify32_iq3_s": dict(tokens=32, runs=[8, 8, 8, 8], gate_type=IQ3_S, zipf_s=0.0, layers=48, scaling="strong"),
+    "prefill32768_q4_k": dict(tokens=32768, runs=[32768], gate_type=Q4_K, zipf_s=0.0, scaling="strong"),
     "sweep_q4k_q6k_q8_0": dict(tokens=[1, 4, 32, 256, 2048, 8192], gate_type=Q4_K, down_type=Q6_K,
                                shexp_gate_type=Q8_0, shexp_down_type=Q8_0, zipf_s=1.1),
 }
