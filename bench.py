@@ -162,7 +162,7 @@ def run_gpu(args, w):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    T_total, nlayers = args.tokens or w["tokens"], w.get("layers", 1)
+    T_total, nlayers = args.tokens or w["tokens"], args.layers or w.get("layers", 1)
     scaling = w.get("scaling", "weak")
     # Weak scaling: every rank brings the workload's rows. Strong: the workload's rows are shared out.
     T = T_total if world == 1 or scaling == "weak" else max(1, T_total // world)
@@ -356,6 +356,7 @@ def main():
     ap.add_argument("--workload", default="ragged3521_q4_k_zipf", choices=list(synth.CONFIGS))
     ap.add_argument("--cpu-tokens", type=int, default=3521, help="rows of the batch the CPU baseline takes per pass")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="layers instead of the workload's")
     ap.add_argument("--tokens", type=int, default=0, help="rows instead of the workload's (the sweep's points)")
     ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
     args = ap.parse_args()

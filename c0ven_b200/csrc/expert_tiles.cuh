@@ -1,8 +1,8 @@
 // The experts' products for many rows per expert: a grouped GEMM on the 5th-generation tensor cores. A work item is 128
 // weight rows of one expert and up to 256 of the rows routed to it; persistent CTAs, one per SM, take items in turn.
-// The worker warps decode the quantised blocks to
-// f16 straight into shared memory in the tensor core's K-major core-matrix layout and gather the rows' activations
-// beside them; one thread issues tcgen05.mma with the weights as the M side and the rows as the N side (so a short
+// Decode warps turn the quantised blocks into f16 straight into shared memory in the tensor core's K-major
+// core-matrix layout; one thread brings the rows' activations beside them with bulk-tensor (TMA) copies, 64 rows a
+// copy, in the 128-byte-swizzled K-major layout; one thread issues tcgen05.mma with the weights as the M side and the rows as the N side (so a short
 // tile costs a short instruction), accumulating f32 in tensor memory; the workers read the accumulators back with
 // tcgen05.ld, apply SwiGLU and store. This replaces the reference's moe_gate_up_t / moe_down_t
 // (kernels/quant/qgemm.cl:88-239), whose tiles are 64 rows on Xe2's DPAS.
@@ -15,6 +15,7 @@
 // other waits return at once, and the CTA still frees its tensor memory before it exits.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -34,15 +35,14 @@ constexpr uint32_t kTileM = 128;   // weight rows a CTA takes
 constexpr uint32_t kTileN = 256;   // activation rows at most
 constexpr uint32_t kTileK = 64;    // values of the contraction a stage holds
 constexpr uint32_t kTileDecoders = 512;  // threads that decode weights: 16 warps, enough of them to hide their loads' latency
-constexpr uint32_t kTileCopiers = 128;   // threads that copy the rows' activations
-constexpr uint32_t kTileThreads = kTileDecoders + kTileCopiers + 32;
+constexpr uint32_t kTileThreads = kTileDecoders + 64;  // and the warp whose first lane issues the copies, and the MMA warp
+constexpr uint32_t kTileBoxRows = 64;    // rows one bulk-tensor copy brings (the tensor map's box: 64 values x 64 rows)
 
 struct ExpertTilesArgs {
   const uint8_t *w0, *w1;   // slot 0's slice of (gate, up) or (down, unused), runs layout
   uint64_t slice_bytes;
   uint32_t K, R;            // values per weight row; weight rows
-  const __half *act;        // activation rows, f16 [rows][K]
-  const uint32_t *act_row;  // expert-order row -> activation row; null: the same row
+                            // the activation rows, f16 [rows][K] in the order of the tiles, come through the tensor map
   const BigTile *tiles;     // null: dense_rows rows of slot 0 in tiles of kTileN
   const uint32_t *ntiles;
   uint32_t dense_rows;
@@ -101,13 +101,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
-// The arrival happens when every cp.async this thread issued before it has landed; it counts as one of the barrier's
-// expected arrivals.
-__device__ __forceinline__ void mbar_arrive_after_copies(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+// One arrival that also tells the barrier to expect `bytes` of bulk copies before its phase completes.
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void copy_async16(uint32_t dst_smem, const void *src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+// Box (x .. x + 63 values, y .. y + 63 rows) of the map's tensor into shared memory at dst (1024-byte aligned); the
+// bytes are counted on the barrier as they land. x * 2 bytes is a multiple of 16, as every bulk-tensor copy needs.
+__device__ __forceinline__ void tma_load_rows(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar)
+               : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -149,6 +152,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 constexpr uint32_t kLbo = 128, kSbo = 1024;
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(kLbo >> 4) << 16) | ((uint64_t)(kSbo >> 4) << 32) | (1ull << 46);
+}
+// The rows' tile as the bulk-tensor copies lay it: a row is 128 contiguous bytes (64 values) whose 16-byte pieces are
+// swizzled by the row's low three bits; 8 rows 1024 bytes on. The next 16 values of the contraction: 32 bytes on.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // kind::f16 instruction descriptor: f32 accumulator, f16 A and B, both K-major, M 128, N n.
 __device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((kTileM >> 4) << 24); }
@@ -402,20 +410,20 @@ __device__ __forceinline__ ItemTile item_tile(const ExpertTilesArgs &a, uint32_t
 // NMAT 2: out = swiglu(gate x, up x); NMAT 1: out = down h. Persistent: the grid is one CTA per SM (fewer when there is
 // less work), and CTA b takes the work items b, b + gridDim.x, ...; item i is weight-row tile i % (R / 128) of big tile
 // i / (R / 128), so neighbouring CTAs share a tile's activations in L2. Three roles: 16 decode warps (quants to f16
-// weights in shared memory, and the epilogue), 4 copy warps (the rows' activations, asynchronous 16-byte copies), and
-// the warp that owns tensor memory and whose first lane issues the MMAs. A warp arrives on a barrier once, by one
+// weights in shared memory, and the epilogue), a warp whose first lane issues the bulk-tensor copies of the rows'
+// activations, and the warp that owns tensor memory and whose first lane issues the MMAs. A warp arrives on a barrier once, by one
 // lane: hundreds of arrivals per stage on one barrier word would serialise in shared memory and set the stage's pace.
 // Dynamic shared memory TileSmem::kBytes.
 template <int QT, int NMAT>
-__global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTilesArgs a, const uint32_t *__restrict__ grid_global) {
+__global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTilesArgs a, const __grid_constant__ CUtensorMap act_map,
+                                                                  const uint32_t *__restrict__ grid_global) {
   using namespace tc;
   using SM = TileSmem<NMAT>;
   using Dec = Decoder<QT>;
   using Raw = typename Dec::Raw;
   constexpr uint32_t S = SM::kStages, kCols = NMAT == 2 ? 512 : 256;
-  constexpr uint32_t kDW = kTileDecoders / 32, kCW = kTileCopiers / 32;  // decode warps, copy warps
+  constexpr uint32_t kDW = kTileDecoders / 32, kCW = 1;  // decode warps, the copy warp
   constexpr uint32_t kHalves = NMAT * kTileM * 2;        // (matrix, row, half) units to decode per stage: a thread takes one
-  constexpr uint32_t CPT = kTileN * 8 / kTileCopiers;    // activation pieces a copy thread takes per stage at most
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
@@ -433,11 +441,11 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   volatile uint32_t *abort = tmem_slot + 1;
   uint32_t *grid = (uint32_t *)(smem + SM::kGrid);
 
-  // A stage is full when every decode warp has stored its weights (one arrival a warp) and every copy thread's copies
-  // have landed (one arrival a thread, made by the copy unit). The accumulators are empty again when every decode warp
+  // A stage is full when every decode warp has stored its weights (one arrival a warp) and the rows' copies have landed
+  // (the copy thread's arrival states their bytes; the copy unit counts them off). The accumulators are empty again when every decode warp
   // has read its part of them.
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW + kTileCopiers), mbar_init(empty_bar(s), 1);
+    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW + 1), mbar_init(empty_bar(s), 1);
     mbar_init(acc_full, 1), mbar_init(acc_empty, kDW);
     *abort = 0;
     fence_barrier_init();
@@ -450,6 +458,14 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+#ifdef MOE_TILE_TIMING
+  // Cycles this thread spent in each kind of wait or work; CTA 0 prints one thread of each role at the end.
+  long long tw[4] = {0, 0, 0, 0};
+  const long long t_begin = clock64();
+#define TT(i, stmt) { const long long t_ = clock64(); stmt; tw[i] += clock64() - t_; }
+#else
+#define TT(i, stmt) { stmt; }
+#endif
 
   if (warp < kDW) {
     // Decode warps. This thread's unit: half h of row m of matrix tid / 256 (threads past the units decode nothing): 8
@@ -469,18 +485,25 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       typename Dec::Hdr hdr, hdr_next;  // the block's scales: fetched with its first stage's quants, used from that stage on
       auto fetch = [&](Raw &r, uint32_t k0) {
         if (decodes) {
+#ifdef MOE_TILE_FAKELOAD
+          r = Dec::fetch(wm, nblk, K, 0, 0, h);
+          if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, 0, 0);
+#else
           r = Dec::fetch(wm, nblk, K, r0 + m, k0, h);
           if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0);
           if (k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, h));
+#endif
         }
       };
       auto stage_step = [&](Raw &r, uint32_t it) {
         const uint32_t g = li * KT + it, s = g % S, use = g / S, k0 = it * kTileK;
-        if (use > 0) ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error);
+        if (use > 0) TT(0, ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error));
         if (!ok) return;
         tc_fence_after();
         if (k0 % 256 == 0) hdr = hdr_next;
-        if (decodes) Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid);
+#ifndef MOE_TILE_NODECODE
+        if (decodes) TT(1, Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid); fence_async_smem(); __syncwarp());
+#endif
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
@@ -496,7 +519,10 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         stage_step(raw[1], it + 1);
       }
       // Epilogue: warp w reads TMEM lanes 32 (w % 4) .., its row of the weights; the warps of a quarter share the columns.
-      if (ok) ok = mbar_wait(acc_full, li & 1, abort, a.error);
+      if (ok) TT(2, ok = mbar_wait(acc_full, li & 1, abort, a.error));
+#ifdef MOE_TILE_TIMING
+      const long long t_epi = clock64();
+#endif
       if (ok) {
         tc_fence_after();
         const uint32_t q = warp % 4, r = r0 + 32 * q + lane;
@@ -511,6 +537,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
             if (n < t.count) {
               float v = __uint_as_float(gv[j]);
               if constexpr (NMAT == 2) v = swiglu_fast(v, __uint_as_float(uv[j]), a.limit);
+#ifdef MOE_TILE_NOEPI
+              if (v == 1.2345e30f)
+#endif
               a.out[(uint64_t)(t.start + n) * a.out_stride + r] = v;
             }
           }
@@ -519,34 +548,42 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty);
       }
+#ifdef MOE_TILE_TIMING
+      tw[3] += clock64() - t_epi;
+#endif
     }
+#ifdef MOE_TILE_TIMING
+    if (blockIdx.x == 0 && tid == 0)
+      printf("decode warp: items %u total %lld | wait empty %lld, decode+store %lld, wait acc %lld, epilogue %lld\n", li, clock64() - t_begin, tw[0], tw[1], tw[2], tw[3]);
+#endif
   }
   else if (warp < kDW + kCW) {
-    // Copy warps: the rows' activations, 16-byte asynchronous copies by token index straight into the operand layout.
-    // Thread ct takes chunk kc of rows n0 + 16 j, j < CPT, at dst0 + 2048 j in a stage's row tile; 8 consecutive
-    // threads take the 8 rows of a core matrix. Rows past count are never read back (their columns of the result are
-    // dropped), so they are left as they are.
-    const uint32_t ct = tid - kTileDecoders, kc = (ct >> 3) & 7, n0 = (ct & 7) | ((ct >> 6) << 3);
-    const uint32_t dst0 = NMAT * SM::kWBytes + (ct >> 6) * kSbo + kc * kLbo + (ct & 7) * 16;
-    uint32_t li = 0;
-    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
-      const ItemTile t = item_tile(a, item / RT);
-      const __half *src[CPT];
-#pragma unroll
-      for (int j = 0; j < (int)CPT; j++) {
-        const uint32_t n = n0 + 16 * j;
-        src[j] = n < t.count ? a.act + (uint64_t)(a.act_row ? a.act_row[t.start + n] : t.start + n) * K + 8 * kc : nullptr;
+    // The copy thread: per stage, the 64 values of the tile's rows, 64 rows a copy, in the swizzled layout. A copy may
+    // run past the tile's rows into the next expert's, or past the tensor (zeros): those columns of the result are dropped.
+    if (lane == 0) {
+      uint32_t li = 0;
+      for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+        const ItemTile t = item_tile(a, item / RT);
+        const uint32_t nbox = (t.count + kTileBoxRows - 1) / kTileBoxRows;
+        for (uint32_t it = 0; it < KT && ok; it++) {
+          const uint32_t g = li * KT + it, s = g % S, use = g / S;
+          if (use > 0) TT(0, ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error));
+          if (!ok) break;
+          const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + NMAT * SM::kWBytes;
+          mbar_arrive_expect(full_bar(s), nbox * kTileBoxRows * kTileK * 2);
+          for (uint32_t i = 0; i < nbox; i++)
+            tma_load_rows(xt + i * kTileBoxRows * kTileK * 2, &act_map, it * kTileK, t.start + i * kTileBoxRows, full_bar(s));
+        }
       }
-      for (uint32_t it = 0; it < KT && ok; it++) {
-        const uint32_t g = li * KT + it, s = g % S, use = g / S, k0 = it * kTileK;
-        if (use > 0) ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error);
-        if (!ok) break;
-        const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + dst0;
-#pragma unroll
-        for (int j = 0; j < (int)CPT; j++)
-          if (src[j]) copy_async16(xt + 2048 * j, src[j] + k0);
-        mbar_arrive_after_copies(full_bar(s));
+      if (!ok) {
+        // Copies already issued may still be on their way: give them time to land before the CTA leaves.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000) {
+        }
       }
+#ifdef MOE_TILE_TIMING
+      if (blockIdx.x == 0) printf("copy thread: total %lld | wait empty %lld\n", clock64() - t_begin, tw[0]);
+#endif
     }
   } else if (lane == 0) {
     // The MMA thread: per stage, four K steps of 16 for each matrix; the commit frees the stage when they are done.
@@ -554,17 +591,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t idesc = instr_desc((t.count + 15) & ~15u);
-      if (li > 0) ok = mbar_wait(acc_empty, (li - 1) & 1, abort, a.error);
+      if (li > 0) TT(1, ok = mbar_wait(acc_empty, (li - 1) & 1, abort, a.error));
       for (uint32_t it = 0; it < KT && ok; it++) {
         const uint32_t g = li * KT + it, s = g % S;
-        ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error);
+        TT(0, ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error));
         if (!ok) break;
-        fence_async_smem();  // the copies' writes, like the decoders' stores, must be visible to the tensor core's reads
         tc_fence_after();
         const uint32_t stage = smem_u32(smem + s * SM::kStageBytes), xt = stage + NMAT * SM::kWBytes;
 #pragma unroll
         for (uint32_t k = 0; k < kTileK / 16; k++) {
-          const uint64_t db = smem_desc(xt + 2 * k * kLbo);
+          const uint64_t db = smem_desc_sw128(xt + 32 * k);
           mma_f16(tmem_base, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
           if constexpr (NMAT == 2) mma_f16(tmem_base + kTileN, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
         }
@@ -572,6 +608,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       }
       if (ok) mma_commit(acc_full);
     }
+#ifdef MOE_TILE_TIMING
+    if (blockIdx.x == 0) printf("mma thread: items %u total %lld | wait full %lld, wait accumulators free %lld\n", li, clock64() - t_begin, tw[0], tw[1]);
+#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -582,7 +621,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   }
 }
 
+// act_map: the activation rows, f16 [rows][a.K] in the order of the tiles (tensor_map.h).
 template <int QT, int NMAT>
-cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, uint32_t max_tiles, const uint32_t *grid_global, cudaStream_t st);
+cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, const CUtensorMap &act_map, uint32_t max_tiles, const uint32_t *grid_global, cudaStream_t st);
 
 }  // namespace moe

@@ -18,6 +18,7 @@
 #include "iq3s_grid.h"
 #include "moe_layer.h"
 #include "route_kernels.cuh"
+#include "tensor_map.h"
 
 namespace moe {
 
@@ -39,13 +40,11 @@ static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, i
 #undef ROWS_CASE
 }
 
-template <int QT, int NMAT>
-cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, uint32_t max_tiles, const uint32_t *grid_global, cudaStream_t st);
-
-static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a, uint32_t max_tiles, const uint32_t *grid, cudaStream_t st) {
+static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a, const CUtensorMap &map, uint32_t max_tiles, const uint32_t *grid,
+                                cudaStream_t st) {
 #define TILES_CASE(T)                                                                                  \
   case T:                                                                                              \
-    return nmat == 2 ? launch_expert_tiles<T, 2>(a, max_tiles, grid, st) : launch_expert_tiles<T, 1>(a, max_tiles, grid, st);
+    return nmat == 2 ? launch_expert_tiles<T, 2>(a, map, max_tiles, grid, st) : launch_expert_tiles<T, 1>(a, map, max_tiles, grid, st);
   switch (qt) {
     TILES_CASE(QT_Q8_0)
     TILES_CASE(QT_Q4_K)
@@ -62,6 +61,7 @@ struct ActBuffers {
   DeviceBuffer<float> d;
   DeviceBuffer<int16_t> bs;
   DeviceBuffer<__half> h;  // the codes dequantised, f16: the tensor-core kernels' operand
+  CUtensorMap h_map{};     // over h, for the tile kernels' copies
   bool q8k = false;
   uint32_t K = 0;
   void alloc(uint64_t rows, uint32_t Kv, bool k, bool with_f16) {
@@ -69,7 +69,11 @@ struct ActBuffers {
     q.alloc(rows * K);
     d.alloc(rows * (k ? K / 256 : K / 32));
     if (k) bs.alloc(rows * (K / 16));
-    if (with_f16) h.alloc(rows * K);
+    if (with_f16) {
+      const uint64_t hr = std::max<uint64_t>(rows, kMapBoxRows);  // a map's tensor is at least one box high
+      h.alloc(hr * K);
+      h_map = make_rows_map(h.get(), hr, K);
+    }
   }
   ActView view(uint64_t row0 = 0) const {
     const uint32_t dn = q8k ? K / 256 : K / 32;
@@ -139,6 +143,8 @@ struct moe_layer {
   DeviceBuffer<int32_t> ids, ids_local;
   DeviceBuffer<uint32_t> error;
   DeviceBuffer<__half> wire_h;  // rows from other GPUs, dequantised for the tensor-core kernels
+  DeviceBuffer<__half> xg;      // the routed experts' activation rows in expert order, f16: what their tile kernel copies from
+  CUtensorMap xg_map{};
   PackBuffers pack, pack_local;  // the step's own rows over every expert; the rows received, over this GPU's experts
   ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
   bool shared_x_same = true, rows_attr_set = false, shared_on_tensor = false;
@@ -250,6 +256,11 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
     if (l->can_tensor) l->wire_h.alloc(R * E);
   }
   l->h.alloc((R + T) * F), l->y.alloc(R * E);
+  if (l->can_tensor) {
+    const uint64_t rows = std::max<uint64_t>(R, kMapBoxRows);
+    l->xg.alloc(rows * E);
+    l->xg_map = make_rows_map(l->xg.get(), rows, E);
+  }
   l->xq_routed.alloc(T, E, act_is_q8k(c.gate_type), l->can_tensor);
   l->hq_routed.alloc(R, F, act_is_q8k(c.down_type), l->can_tensor);
   if (l->has_shared) {
@@ -281,6 +292,11 @@ void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, c
 // Rows a group's kernel takes at once, for groups that hold at most n rows.
 int group_rows(uint64_t n) { return n > 4 ? 8 : n > 2 ? 4 : (int)n; }
 
+// The most rows a group holds in a call of R expert rows over nexp experts. With no more rows than experts nearly every
+// expert has one or two: groups of two keep the kernel's accumulators few and its occupancy up, and the odd expert
+// with more rows is read again by its next group, out of L2. With more rows, groups of eight read an expert once.
+uint32_t group_cap(uint64_t R, uint32_t nexp) { return R <= nexp ? 2 : kGroupMax; }
+
 // Rows from which an expert goes to the tensor-core kernels in a call of R expert rows; 0: none does. With few rows in
 // all, the step is bound by reading each expert once and the integer-dot kernels do that best; with many, every
 // expert's rows fill tensor-core tiles better than groups of 8.
@@ -308,13 +324,14 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
       CUDA_OK(cudaFuncSetAttribute(k_router_logits_rows<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
       l->rows_attr_set = true;
     }
-    const dim3 grid((N + 3) / 4, (T + tm - 1) / tm);
+    const uint32_t warps = tm <= 2 ? 1 : 8;
+    const dim3 grid((N + 4 * warps - 1) / (4 * warps), (T + tm - 1) / tm);
     if (tm == 1)
       k_router_logits_rows<1><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
     else if (tm == 2)
       k_router_logits_rows<2><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
     else
-      k_router_logits_rows<8><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+      k_router_logits_rows<8><<<grid, 256, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
   } else {
     k_router_pieces<<<dim3((NE + 127) / 128, (T + 127) / 128, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
   }
@@ -327,7 +344,7 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   // On one GPU the pack also lists the groups and big tiles of the experts' kernels; expert parallel, it only sorts.
   const uint32_t tm = l->local == NE ? tensor_min_for(l, A) : 0;
   l->last_tensor_min = tm;
-  k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, l->pack.out());
+  k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, group_cap(A, NE), l->pack.out());
   launched(l, cudaGetLastError(), "pack scan");
   const uint32_t chunk_len = kChunkTokens * K;
   k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->pack.base.get(),
@@ -336,39 +353,28 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   l->last_T = T, l->last_pack = &l->pack;
 }
 
-// The integer-dot kernel over a pack's groups. Most groups of a short step hold one or two rows; the kernel for eight
-// rows keeps eight rows' accumulators in registers whatever the group holds, which costs occupancy. So when groups can
-// hold more than two rows, the groups of one or two go to the two-row kernel and only the larger ones to the wide one;
-// each launch passes over the other's groups.
-void launch_rows_by_size(moe_layer *l, uint32_t qt, int nmat, ExpertRowsArgs a, int M, uint32_t max_groups, cudaStream_t st, const char *what) {
-  if (M <= 2) {
-    launched(l, launch_rows(qt, nmat, a, M, max_groups, l->grid.get(), st), what);
-    return;
-  }
-  a.n_min = 1, a.n_max = 2;
-  launched(l, launch_rows(qt, nmat, a, 2, max_groups, l->grid.get(), st), what);
-  a.n_min = 3, a.n_max = kGroupMax;
-  launched(l, launch_rows(qt, nmat, a, M, max_groups, l->grid.get(), st), what);
-}
-
 // The routed experts on the R rows a pack lists: gate/up and SwiGLU into h, h quantised, down into y (expert order).
-void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint32_t tm, float *y, cudaStream_t st) {
+// most: the most rows one expert can have (a step's tokens; in an expert-parallel call, not known below R).
+void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint64_t most, uint32_t tm, float *y, cudaStream_t st) {
   const uint32_t E = l->E, F = l->F, nexp = pk.nexp;
   const moe_layer_config &c = l->cfg;
   // The most groups and big tiles the rows can make: an expert below tm rows has (tm - 2) / 8 + 1 groups at most, and one
   // at or above it a tile per 256 rows and one more.
-  const int M = group_rows(tm ? std::min<uint64_t>(R, tm - 1) : R);
+  const uint32_t gmax = group_cap(R, nexp);
+  const int M = group_rows(std::min<uint64_t>(std::min<uint64_t>(gmax, most), tm ? std::min<uint64_t>(R, tm - 1) : R));
   const uint32_t max_groups =
-      tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(R, (uint64_t)nexp * ((tm - 2) / kGroupMax + 1)) : 0) : (uint32_t)std::min<uint64_t>(R, R / kGroupMax + nexp);
+      tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(R, (uint64_t)nexp * ((tm - 2) / gmax + 1)) : 0) : (uint32_t)std::min<uint64_t>(R, R / gmax + nexp);
   const uint32_t max_big = tm && R >= tm ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm)) : 0;
   mark(l, ST_GATE_UP, st);
   if (max_big) {
     ExpertTilesArgs a{};
+    // The rows in expert order first: a tile's rows are then one box after another for the kernel's copies.
+    k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
+    launched(l, cudaGetLastError(), "rows to expert order");
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F;
-    a.act = src.h, a.act_row = src.act_row;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
-    launched(l, launch_tiles(c.gate_type, 2, a, max_big, l->grid.get(), st), "experts gate/up tiles");
+    launched(l, launch_tiles(c.gate_type, 2, a, l->xg_map, max_big, l->grid.get(), st), "experts gate/up tiles");
   }
   if (max_groups) {
     ExpertRowsArgs a{};
@@ -376,17 +382,16 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.act = src.view, a.act_row = src.act_row;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
-    launch_rows_by_size(l, c.gate_type, 2, a, M, max_groups, st, "experts gate/up");
+    launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
   }
   quantize_rows(l, l->h.get(), R, F, l->hq_routed, st);
   mark(l, ST_DOWN, st);
   if (max_big) {
     ExpertTilesArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;
-    a.act = l->hq_routed.h.get(), a.act_row = nullptr;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = y, a.out_stride = E, a.error = l->error.get();
-    launched(l, launch_tiles(c.down_type, 1, a, max_big, l->grid.get(), st), "experts down tiles");
+    launched(l, launch_tiles(c.down_type, 1, a, l->hq_routed.h_map, max_big, l->grid.get(), st), "experts down tiles");
   }
   if (max_groups) {
     ExpertRowsArgs a{};
@@ -394,7 +399,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.act = l->hq_routed.view(), a.act_row = nullptr;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = y, a.out_stride = E;
-    launch_rows_by_size(l, c.down_type, 1, a, M, max_groups, st, "experts down");
+    launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), st), "experts down");
   }
 }
 
@@ -409,14 +414,14 @@ void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
   if (l->can_tensor && T >= (l->cfg.tensor_min_rows ? l->cfg.tensor_min_rows : 16)) {
     const uint32_t dense_tiles = (T + kTileN - 1) / kTileN;
     ExpertTilesArgs a{};
-    a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.act = xs.h.get(), a.dense_rows = T;
+    a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.dense_rows = T;
     a.out = hs, a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
-    launched(l, launch_tiles(c.shexp_gate_type, 2, a, dense_tiles, l->grid.get(), st), "shared gate/up tiles");
+    launched(l, launch_tiles(c.shexp_gate_type, 2, a, xs.h_map, dense_tiles, l->grid.get(), st), "shared gate/up tiles");
     quantize_rows(l, hs, T, F, l->hq_shared, st);
     ExpertTilesArgs b{};
-    b.w0 = l->sd.get(), b.K = F, b.R = E, b.act = l->hq_shared.h.get(), b.dense_rows = T;
+    b.w0 = l->sd.get(), b.K = F, b.R = E, b.dense_rows = T;
     b.out = l->s.get(), b.out_stride = E, b.error = l->error.get();
-    launched(l, launch_tiles(c.shexp_down_type, 1, b, dense_tiles, l->grid.get(), st), "shared down tiles");
+    launched(l, launch_tiles(c.shexp_down_type, 1, b, l->hq_shared.h_map, dense_tiles, l->grid.get(), st), "shared down tiles");
     l->shared_on_tensor = true;
     return;
   }
@@ -457,7 +462,7 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
     l->join_ev->record(l->aux->get());
   }
   const ActSource src{l->xq_routed.view(), l->xq_routed.h.get(), l->pack.row_src.get()};
-  stage_experts(l, src, l->pack, A, l->last_tensor_min, l->y.get(), st);
+  stage_experts(l, src, l->pack, A, T, l->last_tensor_min, l->y.get(), st);
   if (beside)
     CUDA_OK(cudaStreamWaitEvent(st, l->join_ev->get(), 0));
   else
@@ -672,7 +677,7 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
     const uint32_t nchunks = (R + kLocalChunk - 1) / kLocalChunk;
     k_chunk_hist<<<nchunks, 256, 0, st>>>(ids_dev, R, kLocalChunk, nexp, l->cfg.expert_first, pk.chunk_hist.get());
     launched(l, cudaGetLastError(), "local counts");
-    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, pk.out());
+    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, group_cap(R, nexp), pk.out());
     launched(l, cudaGetLastError(), "local pack scan");
     k_pack_fill<<<nchunks, 512, kLocalChunk * sizeof(int32_t), st>>>(ids_dev, R, kLocalChunk, nexp, pk.base.get(), pk.chunk_off.get(), 1,
                                                                  pk.inv.get(), pk.row_src.get(), l->cfg.expert_first);
@@ -688,7 +693,7 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
       src.h = l->wire_h.get();
     }
     l->last_pack = &pk;
-    stage_experts(l, src, pk, R, tm, l->y.get(), st);
+    stage_experts(l, src, pk, R, R, tm, l->y.get(), st);
     if (y_f16)
       k_unpermute<__half><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (__half *)y_dev);
     else

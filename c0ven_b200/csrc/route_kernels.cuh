@@ -125,28 +125,29 @@ static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restri
 // order, the pieces then added in order, and an expert's bias last. Both kernels and the CPU oracle keep this one
 // order, so that the logits, and with them the chosen experts, agree bit for bit whatever the row count.
 
-// Few rows (up to TM per CTA pass): a CTA is one warp and takes 4 weight rows, 8 lanes a row, lane s taking piece s, so
-// that a step of one row still spreads the router's 4 MB over 129 CTAs; 8 loads of 16 bytes in flight per lane (a piece is a multiple of 32 values).
+// Few rows (up to TM per CTA pass): a warp takes 4 weight rows, 8 lanes a row, lane s taking piece s; 8 loads of 16 bytes
+// in flight per lane (a piece is a multiple of 32 values). A CTA is one warp when the step has one or two rows, so that
+// the router's 4 MB spread over 129 CTAs, and eight warps otherwise, so that the staged rows serve 32 weight rows.
 template <int TM>
-static __global__ void __launch_bounds__(32) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
+static __global__ void __launch_bounds__(256) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
                                                           const float *__restrict__ W, uint32_t N,
                                                           const float *__restrict__ bias, uint32_t NE,
                                                           float *__restrict__ rl) {
   extern __shared__ __align__(16) float xs[];  // TM rows, each piece padded by 4 floats to spread the banks
   const uint32_t piece = E / kRouterPieces, pstride = piece + 4, rstride = kRouterPieces * pstride;
   const uint32_t t0 = blockIdx.y * TM, tn = min((uint32_t)TM, T - t0);
-  const uint32_t lane = threadIdx.x, s = lane % 8, row = blockIdx.x * 4 + lane / 8;
+  const uint32_t lane = threadIdx.x % 32, s = lane % 8, row = (blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32) * 4 + lane / 8;
   // The first weights are on their way while the rows are staged.
   const float4 *w = (const float4 *)(W + (uint64_t)min(row, N - 1) * E + s * piece);
   float4 wq[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) wq[i] = __ldg(w + i);
-  for (uint32_t i = lane; i < TM * (E / 4); i += 32) {
+  for (uint32_t i = threadIdx.x; i < TM * (E / 4); i += blockDim.x) {
     const uint32_t t = i / (E / 4), k4 = i % (E / 4), k = 4 * k4;
     const float4 v = t < tn ? ((const float4 *)(x + (uint64_t)(t0 + t) * E))[k4] : make_float4(0, 0, 0, 0);
     *(float4 *)(xs + t * rstride + (k / piece) * pstride + k % piece) = v;
   }
-  __syncwarp();
+  __syncthreads();
   float p[TM];
 #pragma unroll
   for (int t = 0; t < TM; t++) p[t] = 0.0f;
@@ -377,6 +378,16 @@ static __global__ void __launch_bounds__(256) k_chunk_hist(const int32_t *__rest
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
 }
 
+// dst[r] = src[row_src[r]] for r < R: the rows' f16 activations put in expert order, 16 bytes a thread, so that the
+// tile kernels' bulk-tensor copies find a tile's rows one after another.
+static __global__ void __launch_bounds__(256) k_gather_f16(const __half *__restrict__ src, const uint32_t *__restrict__ row_src, uint64_t R,
+                                                   uint32_t K, __half *__restrict__ dst) {
+  const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x, per = K / 8, r = i / per;
+  if (r >= R) return;
+  const uint32_t c = (uint32_t)(i % per);
+  ((uint4 *)(dst + r * K))[c] = __ldg((const uint4 *)(src + (uint64_t)row_src[r] * K) + c);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Pack. Assignments a = t * K + k go into expert order by a stable counting sort: experts ascending, and inside an
 // expert's run ascending a. The reference's fill takes rows by atomic increments, so its order inside a run depends on
@@ -386,7 +397,7 @@ struct PackOut {
   uint32_t *cnt, *base;    // NE each
   uint32_t *chunk_off;     // [chunks][NE]: rows of the expert's run taken by earlier chunks
   MoeTile *tiles;          // expert order, <= 64 rows each (prompt.cl:719-723)
-  MoeGroup *groups;        // <= 8 rows each: the experts with fewer than tensor_min rows
+  MoeGroup *groups;        // <= group_max rows each: the experts with fewer than tensor_min rows
   BigTile *big;            // <= kTileN rows each: the others, for the tensor-core kernels
   uint32_t *counters;      // [0] tiles, [1] groups, [2] experts hit, [3] rows, [4] big tiles, [5] their rows
 };
@@ -395,9 +406,9 @@ struct PackOut {
 __host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { return tensor_min != 0 && n >= tensor_min; }
 
 // One CTA of 512 threads, thread e for expert e: sums the chunks' counts, scans them over the experts, writes tiles
-// and groups. first_expert: the id of slot 0.
+// and groups. first_expert: the id of slot 0. group_max: the most rows a group holds (<= kGroupMax).
 static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
-                                                  uint32_t first_expert, uint32_t tensor_min, PackOut o) {
+                                                  uint32_t first_expert, uint32_t tensor_min, uint32_t group_max, PackOut o) {
   __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512];
   const uint32_t e = threadIdx.x;
   uint32_t run = 0;
@@ -410,7 +421,7 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
     }
   }
   const bool tensor = n_is_tensor(run, tensor_min);
-  const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = tensor ? 0 : (n + kGroupMax - 1) / kGroupMax;
+  const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = tensor ? 0 : (n + group_max - 1) / group_max;
   const uint32_t nb = tensor ? (n + kTileN - 1) / kTileN : 0;
   s_rows[e] = n, s_tiles[e] = nt, s_groups[e] = ng, s_hit[e] = n > 0, s_big[e] = nb, s_bigrows[e] = tensor ? n : 0;
   __syncthreads();
@@ -430,7 +441,7 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
     for (uint32_t i = 0; i < nt; i++)
       o.tiles[tile0 + i] = MoeTile{first_expert + e, e, first + i * kTileRows, min(kTileRows, n - i * kTileRows)};
     for (uint32_t i = 0; i < ng; i++)
-      o.groups[group0 + i] = MoeGroup{e, first + i * kGroupMax, min((uint32_t)kGroupMax, n - i * kGroupMax)};
+      o.groups[group0 + i] = MoeGroup{e, first + i * group_max, min(group_max, n - i * group_max)};
     const uint32_t big0 = s_big[e] - nb;
     for (uint32_t i = 0; i < nb; i++) o.big[big0 + i] = BigTile{e, first + i * kTileN, min(kTileN, n - i * kTileN)};
   }
