@@ -224,10 +224,10 @@ struct Decoder<QT_Q8_0> {
   }
 };
 
-// Q4_K: w = d * sc * q - dmin * m. A stage is 32 bytes of qs; its first half is their low nibbles (sub-block 2c), its
-// second their high nibbles (sub-block 2c + 1). The two threads of a row's stage load 16 of the 32 bytes each and hand
-// each other theirs by a shuffle, so no byte is loaded twice. The block's d, dmin and scales are one 16-byte piece,
-// loaded once for its four stages.
+// Q4_K: w = d * sc * q - dmin * m. A stage is 32 bytes of qs: their low nibbles are its first 32 values (sub-block 2c),
+// their high nibbles its second 32 (sub-block 2c + 1). The two threads of a row's stage take 16 of the 32 bytes each,
+// both nibbles: values 16 h .. 16 h + 15 of each sub-block, chunks 2 h, 2 h + 1 and 4 + 2 h, 5 + 2 h of the stage. The
+// block's d, dmin and scales are one 16-byte piece, loaded once for its four stages.
 template <>
 struct Decoder<QT_Q4_K> {
   struct Hdr {
@@ -245,39 +245,42 @@ struct Decoder<QT_Q4_K> {
   __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
     return Raw{ldg16(quants_at(s, nblk, K, r, k0, h))};
   }
-  __device__ static __forceinline__ uint32_t byte_of(const Hdr &x, uint32_t i) {
-    const uint32_t w = i < 4 ? x.v.y : i < 8 ? x.v.z : x.v.w;
-    return (w >> (8 * (i & 3))) & 0xFF;
+  // The 6-bit scale and minimum of sub-blocks 2 c and 2 c + 1 (QUANT_FORMATS.md:386-392), each pair as two bytes of a word.
+  __device__ static __forceinline__ void scales_of(const Hdr &x, uint32_t c, uint32_t &sc, uint32_t &mn) {
+    // Bytes 2 c, 2 c + 1 of the three words of packed scales: words y (bytes 0-3), z (4-7), w (8-11).
+    const uint32_t lo = c & 1 ? 0x7732u : 0x7710u;  // byte_perm selector for bytes 2 (c & 1), 2 (c & 1) + 1, zero-extended
+    if (c < 2) {
+      sc = __byte_perm(x.v.y, 0, lo) & 0x3F3Fu, mn = __byte_perm(x.v.z, 0, lo) & 0x3F3Fu;
+    } else {
+      const uint32_t p = __byte_perm(x.v.w, 0, lo), a = __byte_perm(x.v.y, 0, lo), b = __byte_perm(x.v.z, 0, lo);
+      sc = (p & 0x0F0Fu) | ((a >> 2) & 0x3030u), mn = ((p >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
+    }
   }
   __device__ static __forceinline__ void store(const Hdr &hd, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t k0, const uint32_t *) {
-    // The partner (the other half of the same row: lane ^ 8) holds the other 16 bytes.
-    uint4 o4;
-    o4.x = __shfl_xor_sync(0xffffffffu, x.q.x, 8), o4.y = __shfl_xor_sync(0xffffffffu, x.q.y, 8);
-    o4.z = __shfl_xor_sync(0xffffffffu, x.q.z, 8), o4.w = __shfl_xor_sync(0xffffffffu, x.q.w, 8);
-    const uint4 q0 = h ? o4 : x.q, q1 = h ? x.q : o4;
-    const uint32_t j = 2 * ((k0 % 256) / 64) + h;  // the sub-block; its 6-bit scale and minimum (QUANT_FORMATS.md:386-392)
     uint32_t sc, mn;
-    if (j < 4) {
-      sc = byte_of(hd, j) & 63, mn = byte_of(hd, j + 4) & 63;
-    } else {
-      sc = (byte_of(hd, j + 4) & 0xF) | ((byte_of(hd, j - 4) >> 6) << 4);
-      mn = (byte_of(hd, j + 4) >> 4) | ((byte_of(hd, j) >> 6) << 4);
-    }
-    // (1024 + q) * sc - 1024 * sc = q * sc, exact in f16; then * d - dmin * m, rounded once.
+    scales_of(hd, (k0 % 256) / 64, sc, mn);
+    // A byte beside the exponent byte 0x64 is the f16 value 1024 + byte: 1024 + q for a low nibble, 1024 + 16 q for a
+    // high nibble left in place. q comes out exactly (v - 1024, or v / 16 - 64 in one fused step); then w = a * q + c
+    // with a = d * sc and c = -dmin * m, rounded once.
     const __half2 dm = as_h2(hd.v.x);
-    const __half2 sc2 = small_h2(sc), b2 = __hmul2(sc2, as_h2(0xE400E400u));  // -1024 * sc
-    const __half2 d2 = __half2half2(__low2half(dm)), m2 = __hneg2(__hmul2(__half2half2(__high2half(dm)), small_h2(mn)));
-    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const uint32_t sh = 4 * h;
-    uint32_t o[16];
+    const float d = __low2float(dm), dmin = __high2float(dm);
+    const __half2 A0 = __float2half2_rn(d * (float)(sc & 0xFF)), A1 = __float2half2_rn(d * (float)(sc >> 8));
+    const __half2 C0 = __float2half2_rn(-dmin * (float)(mn & 0xFF)), C1 = __float2half2_rn(-dmin * (float)(mn >> 8));
+    const __half2 k1024 = as_h2(0x64006400u), k16th = as_h2(0x2C002C00u), km64 = as_h2(0xD400D400u);  // 1024, 1/16, -64
+    const uint32_t w[4] = {x.q.x, x.q.y, x.q.z, x.q.w};
+    uint32_t lo[8], hi[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const uint32_t t = (w[i] >> sh) & 0x0F0F0F0Fu;
-      o[2 * i] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(t, 0x4140)), sc2, b2), d2, m2));
-      o[2 * i + 1] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(t, 0x4342)), sc2, b2), d2, m2));
+    for (int i = 0; i < 4; i++) {
+      const uint32_t l = w[i] & 0x0F0F0F0Fu, g = w[i] & 0xF0F0F0F0u;
+      lo[2 * i] = as_u32(__hfma2(__hsub2(as_h2(bias_h2(l, 0x4140)), k1024), A0, C0));
+      lo[2 * i + 1] = as_u32(__hfma2(__hsub2(as_h2(bias_h2(l, 0x4342)), k1024), A0, C0));
+      hi[2 * i] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(g, 0x4140)), k16th, km64), A1, C1));
+      hi[2 * i + 1] = as_u32(__hfma2(__hfma2(as_h2(bias_h2(g, 0x4342)), k16th, km64), A1, C1));
     }
-#pragma unroll
-    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
+    store_chunk(tile, m, 2 * h, make_uint4(lo[0], lo[1], lo[2], lo[3]));
+    store_chunk(tile, m, 2 * h + 1, make_uint4(lo[4], lo[5], lo[6], lo[7]));
+    store_chunk(tile, m, 4 + 2 * h, make_uint4(hi[0], hi[1], hi[2], hi[3]));
+    store_chunk(tile, m, 5 + 2 * h, make_uint4(hi[4], hi[5], hi[6], hi[7]));
   }
 };
 
@@ -460,7 +463,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   bool ok = true;
 #ifdef MOE_TILE_TIMING
   // Cycles this thread spent in each kind of wait or work; CTA 0 prints one thread of each role at the end.
-  long long tw[4] = {0, 0, 0, 0};
+  long long tw[6] = {0, 0, 0, 0, 0, 0};
   const long long t_begin = clock64();
 #define TT(i, stmt) { const long long t_ = clock64(); stmt; tw[i] += clock64() - t_; }
 #else
@@ -502,20 +505,18 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         tc_fence_after();
         if (k0 % 256 == 0) hdr = hdr_next;
 #ifndef MOE_TILE_NODECODE
-        if (decodes) TT(1, Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid); fence_async_smem(); __syncwarp());
+        if (decodes) TT(1, Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid));
 #endif
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(s));
+        TT(4, fence_async_smem(); __syncwarp(); if (lane == 0) mbar_arrive(full_bar(s)));
       };
       if (decodes)
         for (uint32_t p = 1; p < kAhead && p < KT; p++) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, h));
-      fetch(raw[0], 0);
+      TT(5, fetch(raw[0], 0));
       for (uint32_t it = 0; it < KT && ok; it += 2) {
-        if (it + 1 < KT) fetch(raw[1], (it + 1) * kTileK);
+        if (it + 1 < KT) TT(5, fetch(raw[1], (it + 1) * kTileK));
         stage_step(raw[0], it);
         if (!ok || it + 1 >= KT) break;
-        if (it + 2 < KT) fetch(raw[0], (it + 2) * kTileK);
+        if (it + 2 < KT) TT(5, fetch(raw[0], (it + 2) * kTileK));
         stage_step(raw[1], it + 1);
       }
       // Epilogue: warp w reads TMEM lanes 32 (w % 4) .., its row of the weights; the warps of a quarter share the columns.
@@ -554,7 +555,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     }
 #ifdef MOE_TILE_TIMING
     if (blockIdx.x == 0 && tid == 0)
-      printf("decode warp: items %u total %lld | wait empty %lld, decode+store %lld, wait acc %lld, epilogue %lld\n", li, clock64() - t_begin, tw[0], tw[1], tw[2], tw[3]);
+      printf("decode warp: items %u total %lld | wait empty %lld, decode+store %lld, fence+arrive %lld, fetch %lld, wait acc %lld, epilogue %lld\n", li,
+             clock64() - t_begin, tw[0], tw[1], tw[4], tw[5], tw[2], tw[3]);
 #endif
   }
   else if (warp < kDW + kCW) {
