@@ -257,8 +257,10 @@ def run_gpu(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
 
-    for m in layers:
+    for m, ex in zip(layers, moes):
         m.set_profiling(True)
+        if ex is not None:
+            ex.st.shared_beside = False  # in line, so that its stage can be timed
     step()
     sync()
     nprof = max(3, min(args.steps, 10))

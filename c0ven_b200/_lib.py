@@ -16,7 +16,7 @@ SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_la
            "moe_layer_read_route", "moe_layer_read_stats", "moe_layer_stage_ms", "moe_layer_set_profiling", "moe_layer_stream", "moe_last_error",
            "moe_abi_layout", "moe_to_runs", "moe_from_runs",
            "moe_route_rows_static", "moe_route_rows_static_error", "moe_layer_route_device", "moe_layer_read_counts", "moe_layer_counts_device",
-           "moe_layer_wire_row_bytes", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
+           "moe_layer_wire_row_bytes", "moe_layer_received_ids_device", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
            "moe_layer_combine_device")
 
 
@@ -84,6 +84,7 @@ def lib():
         L.moe_layer_route_device.argtypes = [vp, vp, u32, vp]
         L.moe_layer_read_counts.argtypes = [vp, vp, vp]
         L.moe_layer_counts_device.argtypes = [vp, vp, vp]
+        L.moe_layer_received_ids_device.argtypes = [vp, vp, u32, vp, vp]
         L.moe_layer_wire_row_bytes.argtypes = [vp]
         L.moe_layer_wire_row_bytes.restype = u32
         L.moe_layer_gather_rows_device.argtypes = [vp, vp, vp, vp]

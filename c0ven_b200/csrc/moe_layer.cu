@@ -644,6 +644,16 @@ MOE_API moe_status moe_layer_counts_device(moe_layer *l, uint32_t *cnt_dev, void
   });
 }
 
+MOE_API moe_status moe_layer_received_ids_device(moe_layer *l, const uint32_t *cnt_all_dev, uint32_t world, int32_t *ids_dev, void *stream) {
+  if (!l || !cnt_all_dev || !ids_dev || world == 0) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    k_received_ids<<<world * l->local, 128, 0, st>>>(cnt_all_dev, l->NE, l->cfg.expert_first, l->local, ids_dev);
+    launched(l, cudaGetLastError(), "received ids");
+  });
+}
+
 MOE_API uint32_t moe_layer_wire_row_bytes(const moe_layer *l) { return l ? wire_row_bytes(act_is_q8k(l->cfg.gate_type), l->E) : 0; }
 
 MOE_API moe_status moe_layer_gather_rows_device(moe_layer *l, void *rows_dev, int32_t *ids_dev, void *stream) {

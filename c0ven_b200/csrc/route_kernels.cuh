@@ -378,6 +378,25 @@ static __global__ void __launch_bounds__(256) k_chunk_hist(const int32_t *__rest
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
 }
 
+// The expert of every row a GPU receives in the rows' all-to-all: the sources one after another, each source's rows in
+// expert order. cnt_all [world][NE] is every GPU's rows per expert; this GPU owns experts first .. first + per. Block
+// b = source * per + local expert sums the runs before its own and fills its run.
+static __global__ void __launch_bounds__(128) k_received_ids(const uint32_t *__restrict__ cnt_all, uint32_t NE, uint32_t first, uint32_t per,
+                                                     int32_t *__restrict__ ids) {
+  __shared__ uint32_t part[128];
+  const uint32_t b = blockIdx.x;
+  uint32_t sum = 0;
+  for (uint32_t p = threadIdx.x; p < b; p += 128) sum += cnt_all[(uint64_t)(p / per) * NE + first + p % per];
+  part[threadIdx.x] = sum;
+  __syncthreads();
+  for (uint32_t off = 64; off; off >>= 1) {
+    if (threadIdx.x < off) part[threadIdx.x] += part[threadIdx.x + off];
+    __syncthreads();
+  }
+  const uint32_t start = part[0], n = cnt_all[(uint64_t)(b / per) * NE + first + b % per];
+  for (uint32_t i = threadIdx.x; i < n; i += 128) ids[start + i] = (int32_t)(first + b % per);
+}
+
 // dst[r] = src[row_src[r]] for r < R: the rows' f16 activations put in expert order, 16 bytes a thread, so that the
 // tile kernels' bulk-tensor copies find a tile's rows one after another.
 static __global__ void __launch_bounds__(256) k_gather_f16(const __half *__restrict__ src, const uint32_t *__restrict__ row_src, uint64_t R,

@@ -62,6 +62,9 @@ class GpuStages:
         self.stream = torch.cuda.ExternalStream(stream_ptr or self.moe.stream, device=self.device)
         self.wire = self.moe.wire_row_bytes
         self._bufs = {}
+        # The shared expert needs no other GPU: it runs on a stream of its own beside the exchanges and the experts.
+        self.side = torch.cuda.Stream(device=self.device)
+        self.shared_beside = not profile
 
     def route(self, x: torch.Tensor) -> torch.Tensor:
         """Routes and packs x's rows; returns the rows per expert, an int32 tensor [n_experts] on the device."""
@@ -86,6 +89,26 @@ class GpuStages:
 
     def shared(self):
         self.moe.shared_device(self._sp)
+
+    def shared_start(self):
+        """The shared expert on the side stream, after what the main stream holds so far (the routing)."""
+        if not self.shared_beside:
+            return
+        self.side.wait_stream(self.stream)
+        self.moe.shared_device(self.side.cuda_stream)
+
+    def shared_finish(self):
+        """The main stream waits for the shared expert; without the side stream, runs it in line."""
+        if self.shared_beside:
+            self.stream.wait_stream(self.side)
+        else:
+            self.shared()
+
+    def ids_from_counts(self, cnt_all: torch.Tensor, world: int, R: int) -> torch.Tensor:
+        """The expert of every received row, computed on the device from the gathered counts."""
+        ids = self.empty((max(R, 1),), torch.int32, "ids_in")
+        self.moe.received_ids_device(cnt_all.data_ptr(), world, ids.data_ptr(), self._sp)
+        return ids[:R]
 
     def combine(self, y: torch.Tensor, out: torch.Tensor):
         self.moe.combine_device(y.data_ptr(), y.dtype == torch.float16, out.data_ptr(), self._sp)
@@ -124,6 +147,8 @@ class ExpertParallelMoE:
         st, W = self.st, self.world
         with torch.cuda.stream(st.stream) if hasattr(st, "stream") else _null():
             cnt = st.route(x)
+            if hasattr(st, "shared_start"):
+                st.shared_start()
             cnt_all = st.empty((W * cnt.numel(),), cnt.dtype, "cnt_all")
             dist.all_gather_into_tensor(cnt_all, cnt, group=self.group)
             counts = cnt_all.cpu().numpy().reshape(W, -1)      # the step's one wait on the host
@@ -132,11 +157,17 @@ class ExpertParallelMoE:
             R = sum(recv)
             rows_in = st.empty((R, rows.shape[1]), rows.dtype, "rows_in")
             dist.all_to_all_single(rows_in, rows, recv, send, group=self.group)
-            ids_in = st.to_device(received_ids(counts, self.rank))
+            if hasattr(st, "ids_from_counts"):
+                ids_in = st.ids_from_counts(cnt_all, W, R)
+            else:
+                ids_in = st.to_device(received_ids(counts, self.rank))
             y_in = st.experts(rows_in, ids_in)                 # [R][E] in arrival order
-            st.shared()                                        # the shared expert needs no other GPU
             y = st.empty((rows.shape[0], y_in.shape[1]), y_in.dtype, "y")
             dist.all_to_all_single(y, y_in, send, recv, group=self.group)
+            if hasattr(st, "shared_finish"):
+                st.shared_finish()
+            else:
+                st.shared()
             if out is None:
                 out = st.empty(tuple(x.shape), torch.float32)
             st.combine(y, out)

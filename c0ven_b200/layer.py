@@ -115,6 +115,9 @@ class MoELayer:
     def counts_device(self, cnt_ptr: int, stream=None):
         self._check(_lib.lib().moe_layer_counts_device(self._h, cnt_ptr, stream))
 
+    def received_ids_device(self, cnt_all_ptr: int, world: int, ids_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_received_ids_device(self._h, cnt_all_ptr, world, ids_ptr, stream))
+
     @property
     def wire_row_bytes(self) -> int:
         return _lib.lib().moe_layer_wire_row_bytes(self._h)

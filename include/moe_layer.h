@@ -128,6 +128,9 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
  *            what the all-to-all's split sizes are made of.
  *   gather:  rows_dev[r] = the quantised activation row (moe_layer_wire_row_bytes bytes) of assignment row r in expert
  *            order, ids_dev[r] = its expert. Experts are owned in contiguous ranges, so this is destination order.
+ *   received_ids: from every GPU's counts (cnt_all_dev [world][n_experts], the all-gather of counts), ids_dev[r] = the
+ *            expert of the r-th row this GPU receives when every GPU sends its rows in gather's order: sources one
+ *            after another, each in expert order. So no ids travel and the host computes none.
  *   experts: R rows received (any order) with their expert ids, all among this GPU's experts; y_dev[r] = that expert's
  *            FFN on row r, [R][n_embd] in the order received, f32 or (y_f16 != 0) f16.
  *   shared:  the shared expert on the routed rows (may run on another stream than the experts).
@@ -136,6 +139,7 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
 MOE_API moe_status moe_layer_route_device(moe_layer *l, const float *x_dev, uint32_t T, void *stream);
 MOE_API moe_status moe_layer_read_counts(moe_layer *l, uint32_t *cnt_host, void *stream);
 MOE_API moe_status moe_layer_counts_device(moe_layer *l, uint32_t *cnt_dev, void *stream);
+MOE_API moe_status moe_layer_received_ids_device(moe_layer *l, const uint32_t *cnt_all_dev, uint32_t world, int32_t *ids_dev, void *stream);
 MOE_API uint32_t moe_layer_wire_row_bytes(const moe_layer *l);
 MOE_API moe_status moe_layer_gather_rows_device(moe_layer *l, void *rows_dev, int32_t *ids_dev, void *stream);
 MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, const int32_t *ids_dev, uint32_t R, void *y_dev,
