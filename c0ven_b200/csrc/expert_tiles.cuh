@@ -35,7 +35,8 @@ constexpr uint32_t kTileM = 128;   // weight rows a CTA takes
 constexpr uint32_t kTileN = 256;   // activation rows at most
 constexpr uint32_t kTileK = 64;    // values of the contraction a stage holds
 constexpr uint32_t kTileDecoders = 512;  // threads that decode weights: 16 warps, enough of them to hide their loads' latency
-constexpr uint32_t kTileThreads = kTileDecoders + 64;  // and the warp whose first lane issues the copies, and the MMA warp
+constexpr uint32_t kTileEpilogue = 128;  // threads that turn accumulators into results: a warp per quarter of the weight rows
+constexpr uint32_t kTileThreads = kTileDecoders + kTileEpilogue + 64;  // and the warp whose first lane issues the copies, and the MMA warp
 constexpr uint32_t kTileBoxRows = 64;    // rows one bulk-tensor copy brings (the tensor map's box: 64 values x 64 rows)
 
 struct ExpertTilesArgs {
@@ -382,7 +383,7 @@ struct TileSmem {
   static constexpr uint32_t kStages = NMAT == 2 ? 3 : 4;
   static constexpr uint32_t kWBytes = kTileM * kTileK * 2, kXBytes = kTileN * kTileK * 2;
   static constexpr uint32_t kStageBytes = NMAT * kWBytes + kXBytes;
-  static constexpr uint32_t kBarriers = kStages * kStageBytes;  // full[kStages], empty[kStages], acc full, acc empty; tmem address; abort
+  static constexpr uint32_t kBarriers = kStages * kStageBytes;  // full[kStages], empty[kStages], accumulators full[2], empty[2], empty after a two-buffer item; tmem address; abort
   static constexpr uint32_t kGrid = kBarriers + 128;            // IQ3_S's codebook, 2 KB
   static constexpr uint32_t kBytes = kGrid + 2048 + 1024;       // and room to align the base to 1024
 };
@@ -412,10 +413,15 @@ __device__ __forceinline__ ItemTile item_tile(const ExpertTilesArgs &a, uint32_t
 
 // NMAT 2: out = swiglu(gate x, up x); NMAT 1: out = down h. Persistent: the grid is one CTA per SM (fewer when there is
 // less work), and CTA b takes the work items b, b + gridDim.x, ...; item i is weight-row tile i % (R / 128) of big tile
-// i / (R / 128), so neighbouring CTAs share a tile's activations in L2. Three roles: 16 decode warps (quants to f16
-// weights in shared memory, and the epilogue), a warp whose first lane issues the bulk-tensor copies of the rows'
-// activations, and the warp that owns tensor memory and whose first lane issues the MMAs. A warp arrives on a barrier once, by one
-// lane: hundreds of arrivals per stage on one barrier word would serialise in shared memory and set the stage's pace.
+// i / (R / 128), so neighbouring CTAs share a tile's activations in L2. Four roles: 16 decode warps (quants to f16
+// weights in shared memory), 4 epilogue warps (accumulators to the result), a warp whose first lane issues the
+// bulk-tensor copies of the rows' activations, and the warp that owns tensor memory and whose first lane issues the
+// MMAs. A warp arrives on a barrier once, by one lane.
+//
+// Tensor memory is two buffers of 256 columns. An item of at most 128 rows (any item, for NMAT 1) takes one buffer,
+// alternately, so the epilogue warps drain item i while the MMAs of item i + 1 run and the decode warps never stop. A
+// gate/up item of more than 128 rows needs both buffers (gate in one, up in the other): the MMAs of the next item
+// wait for its epilogue, and to keep that short the decode warps join the epilogue warps for it.
 // Dynamic shared memory TileSmem::kBytes.
 template <int QT, int NMAT>
 __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTilesArgs a, const __grid_constant__ CUtensorMap act_map,
@@ -424,9 +430,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   using SM = TileSmem<NMAT>;
   using Dec = Decoder<QT>;
   using Raw = typename Dec::Raw;
-  constexpr uint32_t S = SM::kStages, kCols = NMAT == 2 ? 512 : 256;
-  constexpr uint32_t kDW = kTileDecoders / 32, kCW = 1;  // decode warps, the copy warp
-  constexpr uint32_t kHalves = NMAT * kTileM * 2;        // (matrix, row, half) units to decode per stage: a thread takes one
+  constexpr uint32_t S = SM::kStages, kCols = 512;
+  constexpr uint32_t kDW = kTileDecoders / 32, kEW = kTileEpilogue / 32, kCopyWarp = kDW + kEW, kMmaWarp = kCopyWarp + 1;
+  constexpr uint32_t kHalves = NMAT * kTileM * 2;  // (matrix, row, half) units to decode per stage: a thread takes one
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
@@ -439,23 +445,26 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](uint32_t s) { return bar0 + 8 * s; };
   auto empty_bar = [&](uint32_t s) { return bar0 + 8 * (S + s); };
-  const uint32_t acc_full = bar0 + 8 * (2 * S), acc_empty = bar0 + 8 * (2 * S + 1);
-  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 2);
+  auto acc_full = [&](uint32_t b) { return bar0 + 8 * (2 * S + b); };
+  auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (2 * S + 2 + b); };
+  const uint32_t acc_empty_wide = bar0 + 8 * (2 * S + 4);
+  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 5);
   volatile uint32_t *abort = tmem_slot + 1;
   uint32_t *grid = (uint32_t *)(smem + SM::kGrid);
 
   // A stage is full when every decode warp has stored its weights (one arrival a warp) and the rows' copies have landed
-  // (the copy thread's arrival states their bytes; the copy unit counts them off). The accumulators are empty again when every decode warp
-  // has read its part of them.
+  // (the copy thread's arrival states their bytes; the copy unit counts them off). An accumulator buffer is empty again
+  // when the epilogue warps have read it; after an item that took both buffers, also when the decode warps have.
   if (tid == 0) {
     for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW + 1), mbar_init(empty_bar(s), 1);
-    mbar_init(acc_full, 1), mbar_init(acc_empty, kDW);
+    for (uint32_t b = 0; b < 2; b++) mbar_init(acc_full(b), 1), mbar_init(acc_empty(b), kEW);
+    mbar_init(acc_empty_wide, kDW);
     *abort = 0;
     fence_barrier_init();
   }
   if constexpr (QT == QT_IQ3_S)
     for (uint32_t i = tid; i < 512; i += blockDim.x) grid[i] = grid_global[i];
-  if (warp == kDW + kCW) tmem_alloc(smem_u32(tmem_slot), kCols);
+  if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_slot), kCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -470,6 +479,34 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
 #define TT(i, stmt) { stmt; }
 #endif
 
+  // Every role walks the same items and keeps the same books: how often each buffer has been used (the parity of its
+  // barriers' phases), which buffer the next one-buffer item takes, and how many two-buffer items there have been.
+  uint32_t use0 = 0, use1 = 0, next_buf = 0, wides = 0;  // two scalars, not an array: they stay in registers
+  auto use_of = [&](uint32_t b) { return b ? use1 : use0; };
+  auto use_inc = [&](uint32_t b) { use0 += b == 0, use1 += b == 1; };
+  auto is_wide = [&](uint32_t count) { return NMAT == 2 && count > kTileN / 2; };
+
+  // Columns q (this warp's quarter of the weight rows: TMEM lanes 32 q ..) of chunks slot, slot + nslots, ... of 16 rows
+  // each, from the accumulators at column colg (and colu, the up product) to the result.
+  auto drain = [&](const ItemTile &t, uint32_t r0, uint32_t colg, uint32_t colu, uint32_t slot, uint32_t nslots) {
+    const uint32_t q = warp % 4, r = r0 + 32 * q + lane, N = (t.count + 15) & ~15u;
+    for (uint32_t c = slot; c < N / 16; c += nslots) {
+      uint32_t gv[16], uv[16];
+      tmem_ld16(tmem_base + ((32 * q) << 16) + colg + 16 * c, gv);
+      if constexpr (NMAT == 2) tmem_ld16(tmem_base + ((32 * q) << 16) + colu + 16 * c, uv);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const uint32_t n = 16 * c + j;
+        if (n < t.count) {
+          float v = __uint_as_float(gv[j]);
+          if constexpr (NMAT == 2) v = swiglu_fast(v, __uint_as_float(uv[j]), a.limit);
+          a.out[(uint64_t)(t.start + n) * a.out_stride + r] = v;
+        }
+      }
+    }
+  };
+
   if (warp < kDW) {
     // Decode warps. This thread's unit: half h of row m of matrix tid / 256 (threads past the units decode nothing): 8
     // consecutive threads take the 8 rows of a core matrix, so a quarter-warp's 16-byte stores fill 128 contiguous bytes.
@@ -479,7 +516,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     uint32_t li = 0;
     for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
       const ItemTile t = item_tile(a, item / RT);
-      const uint32_t r0 = (item % RT) * kTileM, N = (t.count + 15) & ~15u;
+      const uint32_t r0 = (item % RT) * kTileM;
       const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
       // Quants come from HBM the first time an expert is touched; a request for the L2 goes out kAhead stages before
       // the load into registers, which itself goes a stage before the decode.
@@ -499,8 +536,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         }
       };
       auto stage_step = [&](Raw &r, uint32_t it) {
-        const uint32_t g = li * KT + it, s = g % S, use = g / S, k0 = it * kTileK;
-        if (use > 0) TT(0, ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error));
+        const uint32_t g = li * KT + it, s = g % S, use_s = g / S, k0 = it * kTileK;
+        if (use_s > 0) TT(0, ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error));
         if (!ok) return;
         tc_fence_after();
         if (k0 % 256 == 0) hdr = hdr_next;
@@ -519,47 +556,59 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         if (it + 2 < KT) TT(5, fetch(raw[0], (it + 2) * kTileK));
         stage_step(raw[1], it + 1);
       }
-      // Epilogue: warp w reads TMEM lanes 32 (w % 4) .., its row of the weights; the warps of a quarter share the columns.
-      if (ok) TT(2, ok = mbar_wait(acc_full, li & 1, abort, a.error));
-#ifdef MOE_TILE_TIMING
-      const long long t_epi = clock64();
-#endif
-      if (ok) {
-        tc_fence_after();
-        const uint32_t q = warp % 4, r = r0 + 32 * q + lane;
-        for (uint32_t c = warp / 4; c < N / 16; c += kDW / 4) {
-          uint32_t gv[16], uv[16];
-          tmem_ld16(tmem_base + ((32 * q) << 16) + 16 * c, gv);
-          if constexpr (NMAT == 2) tmem_ld16(tmem_base + ((32 * q) << 16) + kTileN + 16 * c, uv);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; j++) {
-            const uint32_t n = 16 * c + j;
-            if (n < t.count) {
-              float v = __uint_as_float(gv[j]);
-              if constexpr (NMAT == 2) v = swiglu_fast(v, __uint_as_float(uv[j]), a.limit);
-#ifdef MOE_TILE_NOEPI
-              if (v == 1.2345e30f)
-#endif
-              a.out[(uint64_t)(t.start + n) * a.out_stride + r] = v;
-            }
-          }
+      if (is_wide(t.count)) {
+        // Both buffers: the next item's MMAs wait for this epilogue, so these warps take four fifths of it.
+        if (ok) TT(2, ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error));
+        if (ok) TT(2, ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error));
+        if (ok) {
+          tc_fence_after();
+          TT(3, drain(t, r0, 0, kTileN, warp / 4, kDW / 4 + 1));
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_wide);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty);
+        use0++, use1++, wides++;
+      } else {
+        use_inc(next_buf), next_buf ^= 1;
       }
-#ifdef MOE_TILE_TIMING
-      tw[3] += clock64() - t_epi;
-#endif
     }
 #ifdef MOE_TILE_TIMING
     if (blockIdx.x == 0 && tid == 0)
       printf("decode warp: items %u total %lld | wait empty %lld, decode+store %lld, fence+arrive %lld, fetch %lld, wait acc %lld, epilogue %lld\n", li,
              clock64() - t_begin, tw[0], tw[1], tw[4], tw[5], tw[2], tw[3]);
 #endif
-  }
-  else if (warp < kDW + kCW) {
+  } else if (warp < kDW + kEW) {
+    // Epilogue warps: warp w reads TMEM lanes 32 (w % 4) .., its quarter of the weight rows.
+    uint32_t li = 0;
+    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+      const ItemTile t = item_tile(a, item / RT);
+      const uint32_t r0 = (item % RT) * kTileM;
+      if (is_wide(t.count)) {
+        if (ok) TT(2, ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error));
+        if (ok) TT(2, ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error));
+        if (!ok) break;
+        tc_fence_after();
+        TT(3, drain(t, r0, 0, kTileN, kDW / 4, kDW / 4 + 1));
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(0)), mbar_arrive(acc_empty(1));
+        use0++, use1++, wides++;
+      } else {
+        const uint32_t b = next_buf;
+        TT(2, ok = mbar_wait(acc_full(b), use_of(b) & 1, abort, a.error));
+        if (!ok) break;
+        tc_fence_after();
+        TT(3, drain(t, r0, b * kTileN, b * kTileN + kTileN / 2, 0, 1));
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(b));
+        use_inc(b), next_buf ^= 1;
+      }
+    }
+#ifdef MOE_TILE_TIMING
+    if (blockIdx.x == 0 && lane == 0 && warp == kDW) printf("epilogue warp: items %u total %lld | wait acc %lld, epilogue %lld\n", li, clock64() - t_begin, tw[2], tw[3]);
+#endif
+  } else if (warp == kCopyWarp) {
     // The copy thread: per stage, the 64 values of the tile's rows, 64 rows a copy, in the swizzled layout. A copy may
     // run past the tile's rows into the next expert's, or past the tensor (zeros): those columns of the result are dropped.
     if (lane == 0) {
@@ -568,8 +617,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         const ItemTile t = item_tile(a, item / RT);
         const uint32_t nbox = (t.count + kTileBoxRows - 1) / kTileBoxRows;
         for (uint32_t it = 0; it < KT && ok; it++) {
-          const uint32_t g = li * KT + it, s = g % S, use = g / S;
-          if (use > 0) TT(0, ok = mbar_wait(empty_bar(s), (use - 1) & 1, abort, a.error));
+          const uint32_t g = li * KT + it, s = g % S, use_s = g / S;
+          if (use_s > 0) TT(0, ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error));
           if (!ok) break;
           const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + NMAT * SM::kWBytes;
           mbar_arrive_expect(full_bar(s), nbox * kTileBoxRows * kTileK * 2);
@@ -590,10 +639,18 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   } else if (lane == 0) {
     // The MMA thread: per stage, four K steps of 16 for each matrix; the commit frees the stage when they are done.
     uint32_t li = 0;
+    bool after_wide = false;
     for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t idesc = instr_desc((t.count + 15) & ~15u);
-      if (li > 0) TT(1, ok = mbar_wait(acc_empty, (li - 1) & 1, abort, a.error));
+      const bool wide = is_wide(t.count);
+      const uint32_t b = next_buf, colg = wide ? 0 : b * kTileN, colu = wide ? kTileN : colg + kTileN / 2;
+      // The buffers this item writes must have been read: by the epilogue warps, and after a two-buffer item by the
+      // decode warps too.
+      if (after_wide) TT(1, ok = mbar_wait(acc_empty_wide, (wides - 1) & 1, abort, a.error));
+      after_wide = false;
+      for (uint32_t bb = 0; bb < 2 && ok; bb++)
+        if ((wide || bb == b) && use_of(bb) > 0) TT(1, ok = mbar_wait(acc_empty(bb), (use_of(bb) - 1) & 1, abort, a.error));
       for (uint32_t it = 0; it < KT && ok; it++) {
         const uint32_t g = li * KT + it, s = g % S;
         TT(0, ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error));
@@ -603,12 +660,19 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
 #pragma unroll
         for (uint32_t k = 0; k < kTileK / 16; k++) {
           const uint64_t db = smem_desc_sw128(xt + 32 * k);
-          mma_f16(tmem_base, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
-          if constexpr (NMAT == 2) mma_f16(tmem_base + kTileN, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
+          mma_f16(tmem_base + colg, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
+          if constexpr (NMAT == 2) mma_f16(tmem_base + colu, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
         }
         mma_commit(empty_bar(s));
       }
-      if (ok) mma_commit(acc_full);
+      if (!ok) break;
+      if (wide) {
+        mma_commit(acc_full(0)), mma_commit(acc_full(1));
+        use0++, use1++, wides++, after_wide = true;
+      } else {
+        mma_commit(acc_full(b));
+        use_inc(b), next_buf ^= 1;
+      }
     }
 #ifdef MOE_TILE_TIMING
     if (blockIdx.x == 0) printf("mma thread: items %u total %lld | wait full %lld, wait accumulators free %lld\n", li, clock64() - t_begin, tw[0], tw[1]);
@@ -616,7 +680,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kDW + kCW) {
+  if (warp == kMmaWarp) {
     __syncwarp();
     tc_fence_after();
     tmem_free(tmem_base, kCols);
