@@ -291,6 +291,15 @@ def run_gpu(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_s = float(t.item())
 
+    # Expert parallel: the rows each rank's experts ran in the last step (routing skew shows here: the busiest rank
+    # bounds the step).
+    ep_rows = None
+    if world > 1:
+        rows_t = torch.tensor([sum(m.expert_rows for m in moes)], device="cuda", dtype=torch.int64)
+        all_rows = [torch.zeros_like(rows_t) for _ in range(world)]
+        dist.all_gather(all_rows, rows_t)
+        ep_rows = [int(v.item()) for v in all_rows]
+
     def teardown():
         # Every rank waits for the others, then the process ends here, without the interpreter's teardown: the order in
         # which that would drop the layers' streams, the collectives' and the allocator's blocks used on them is not
@@ -311,7 +320,11 @@ def run_gpu(args, w):
     alg = {k: sum(a[k] for a in algs) for k in algs[0]}
     dom = max(("gate_up", "down"), key=lambda k: stage[k])
     dom_ms = stage[dom]
-    if tensor_rows > 0:
+    # The routed experts' kernel family decides the bound: the stats count the shared expert's rows too when it took the
+    # tile kernel (T a layer), so a step whose routed experts all ran as integer-dot rows is bandwidth-bound.
+    shared_rows = T if T >= (args.tensor_min or 16) else 0
+    routed_tensor_rows = sum(max(0, s["last_tensor_rows"] - shared_rows) for s in stats)
+    if routed_tensor_rows * 2 > T * K * nlayers:
         achieved = alg["flops_" + dom] / (dom_ms * 1e-3) / 1e12
         roof = dict(bound="tensor", achieved=achieved, peak=peaks["bf16_tflops"], unit="TFLOP/s", frac=achieved / peaks["bf16_tflops"])
     else:
@@ -338,7 +351,7 @@ def run_gpu(args, w):
                 dtype="f16" if tensor_rows > 0 else "i8", data="synthetic",
                 config=dict(workload=w["name"], rows=world * T, rows_per_gpu=T, layers=nlayers, runs=w.get("runs"), hidden=E, ffn=F,
                             experts=NE, top_k=K, weights=synth.TYPE_NAMES[w["gate_type"]], zipf_s=w.get("zipf_s", 0.0),
-                            experts_hit=hit, tiles=sum(s["last_tiles"] for s in stats), parallelism=par,
+                            experts_hit=hit, tiles=sum(s["last_tiles"] for s in stats), parallelism=par, expert_rows_per_gpu=ep_rows,
                             l2="flushed between timed steps"),
                 roofline=roof, stage_ms=stage, layer_bytes=alg["bytes_layer"], layer_flops=alg["flops_layer"],
                 cpu_baseline=cpu, clocks=clocks.summary(),

@@ -237,14 +237,18 @@ struct Unit<QT_IQ3_S> {
   __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc,
                                              uint32_t n, const uint32_t *grid) {
     const uint32_t b = u / 4, c = u % 4;
+    // A codebook word is four values in 1 .. 15; a sign bit negates its byte: (v ^ 0xFF) + 1 = 256 - v stays within the
+    // byte for v >= 1, so the four bytes take one exclusive-or and one 32-bit add. The nibble's bits reach the bytes'
+    // low bits by one multiply: bit i times 2^(7 i) lands on bit 8 i, and no two products share a bit.
     int g[16];
+    const uint32_t qh9 = x.qh << 8;
 #pragma unroll
     for (int i = 0; i < 16; i++) {
       const uint32_t word = i < 4 ? x.qs.x : i < 8 ? x.qs.y : i < 12 ? x.qs.z : x.qs.w;
-      const uint32_t idx = ((word >> (8 * (i & 3))) & 0xFF) | (((x.qh >> i) & 1u) << 8);
+      const uint32_t idx = ((word >> (8 * (i & 3))) & 0xFF) | ((qh9 >> i) & 0x100u);
       const uint32_t nib = ((i < 8 ? x.sg.x : x.sg.y) >> (4 * (i & 7))) & 0xF;
-      const uint32_t mask = ((nib & 1u) | ((nib & 2u) << 7) | ((nib & 4u) << 14) | ((nib & 8u) << 21)) * 0xFFu;
-      g[i] = (int)__vsub4(grid[idx] ^ mask, mask);
+      const uint32_t lsb = (nib * 0x00204081u) & 0x01010101u;
+      g[i] = (int)((grid[idx] ^ (lsb * 0xFFu)) + lsb);
     }
     const int sc0 = 2 * (int)(x.sc & 0xF) + 1, sc1 = 2 * (int)((x.sc >> 4) & 0xF) + 1;
 #pragma unroll
@@ -277,8 +281,10 @@ __device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32
 
 // Passes of a warp whose loads are issued together: about 16 loads of 16 bytes a lane, fewer when many activation rows
 // already fill the registers with accumulators.
-__host__ __device__ constexpr int rows_batch(int nmat, int nu, int m) {
-  const int want = 16 / (nmat * nu) > 0 ? 16 / (nmat * nu) : 1, cap = m >= 4 ? 4 : 8;
+__host__ __device__ constexpr int rows_batch(int nmat, int nu, int m, bool heavy) {
+  // heavy: a unit that holds many registers while it waits (IQ3_S: quants, signs, high bits, scale): fewer passes at
+  // once leave room for a second CTA on the SM, which its arithmetic-bound decode needs more than loads in flight.
+  const int want = 16 / (nmat * nu) > 0 ? 16 / (nmat * nu) : 1, cap = heavy ? 2 : m >= 4 ? 4 : 8;
   return want < cap ? want : cap;
 }
 
@@ -309,7 +315,7 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, li = lane % G, sub = lane / G;
   constexpr uint32_t RPP = 32 / G;  // weight rows a warp takes per pass
   constexpr int NU = UPL > 0 ? UPL : 1;
-  constexpr int RB = rows_batch(NMAT, NU, M);  // passes whose loads go out together
+  constexpr int RB = rows_batch(NMAT, NU, M, QT == QT_IQ3_S);  // passes whose loads go out together
   using Raw = typename Unit<QT>::Raw;
   const uint32_t rows_per_warp = UPL > 0 ? RPP * RB : a.rows_per_cta / 8;
   const uint32_t r_begin = blockIdx.x * (8 * rows_per_warp) + warp * rows_per_warp;

@@ -12,7 +12,7 @@ static cudaError_t launch_one(ExpertRowsArgs a, uint32_t max_groups, const uint3
   // With the row length known at compile time a CTA's eight warps take one batch of passes each; else the caller's count.
   constexpr uint32_t rpp = 32 / G;
   if (UPL > 0)
-    a.rows_per_cta = 8 * rpp * rows_batch(NMAT, UPL, M);
+    a.rows_per_cta = 8 * rpp * rows_batch(NMAT, UPL, M, QT == QT_IQ3_S);
   else if (a.rows_per_cta < 8 * rpp)
     a.rows_per_cta = 8 * rpp;
   const size_t smem = (size_t)M * act_row_stride(q8k, a.K) + (QT == QT_IQ3_S ? 2048 : 0);

@@ -479,6 +479,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
 #define TT(i, stmt) { stmt; }
 #endif
 
+  // CTA b's item of round r: the items come sorted by size (full tiles first, then the others by falling row count), and
+  // the rounds deal them boustrophedon (b, then G - 1 - b, ...), so that every CTA gets a like share of long and short
+  // items. kNoItem past the end; a CTA's last round may have no item for it while others still have one.
+  constexpr uint32_t kNoItem = 0xFFFFFFFFu;
+  auto item_at = [&](uint32_t rnd) {
+    const uint32_t base = rnd * gridDim.x;
+    const uint32_t i = base + ((rnd & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+    return i < nitems ? i : kNoItem;
+  };
+
   // Every role walks the same items and keeps the same books: how often each buffer has been used (the parity of its
   // barriers' phases), which buffer the next one-buffer item takes, and how many two-buffer items there have been.
   uint32_t use0 = 0, use1 = 0, next_buf = 0, wides = 0;  // two scalars, not an array: they stay in registers
@@ -514,7 +524,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     const bool decodes = tid < kHalves;
     const uint32_t mat = tid / 256, u = tid % 256, m = (u & 7) | ((u >> 4) << 3), h = (u >> 3) & 1;
     uint32_t li = 0;
-    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+    for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t r0 = (item % RT) * kTileM;
       const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
@@ -580,7 +590,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   } else if (warp < kDW + kEW) {
     // Epilogue warps: warp w reads TMEM lanes 32 (w % 4) .., its quarter of the weight rows.
     uint32_t li = 0;
-    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+    for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t r0 = (item % RT) * kTileM;
       if (is_wide(t.count)) {
@@ -613,7 +623,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     // run past the tile's rows into the next expert's, or past the tensor (zeros): those columns of the result are dropped.
     if (lane == 0) {
       uint32_t li = 0;
-      for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+      for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
         const ItemTile t = item_tile(a, item / RT);
         const uint32_t nbox = (t.count + kTileBoxRows - 1) / kTileBoxRows;
         for (uint32_t it = 0; it < KT && ok; it++) {
@@ -640,7 +650,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     // The MMA thread: per stage, four K steps of 16 for each matrix; the commit frees the stage when they are done.
     uint32_t li = 0;
     bool after_wide = false;
-    for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
+    for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t idesc = instr_desc((t.count + 15) & ~15u);
       const bool wide = is_wide(t.count);

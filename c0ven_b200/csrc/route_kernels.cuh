@@ -428,7 +428,7 @@ __host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { r
 // and groups. first_expert: the id of slot 0. group_max: the most rows a group holds (<= kGroupMax).
 static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
                                                   uint32_t first_expert, uint32_t tensor_min, uint32_t group_max, PackOut o) {
-  __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512];
+  __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512], s_hit2[512];
   const uint32_t e = threadIdx.x;
   uint32_t run = 0;
   if (e < NE) {
@@ -461,12 +461,32 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
       o.tiles[tile0 + i] = MoeTile{first_expert + e, e, first + i * kTileRows, min(kTileRows, n - i * kTileRows)};
     for (uint32_t i = 0; i < ng; i++)
       o.groups[group0 + i] = MoeGroup{e, first + i * group_max, min(group_max, n - i * group_max)};
-    const uint32_t big0 = s_big[e] - nb;
-    for (uint32_t i = 0; i < nb; i++) o.big[big0 + i] = BigTile{e, first + i * kTileN, min(kTileN, n - i * kTileN)};
+  }
+  // Big tiles, sorted by size for the tile kernels' round-robin over CTAs: every full tile of kTileN rows first (in
+  // expert order), then the experts' last, shorter tiles by falling row count (ties in expert order). s_bigrows is free
+  // to reuse: the scan's total was read above.
+  const uint32_t total_rows_big = s_bigrows[511], nfull = tensor ? n / kTileN : 0, rem = tensor ? n % kTileN : 0;
+  __syncthreads();
+  s_hit2[e] = nfull, s_bigrows[e] = rem;
+  __syncthreads();
+  for (uint32_t off = 1; off < 512; off <<= 1) {
+    const uint32_t a = e >= off ? s_hit2[e - off] : 0;
+    __syncthreads();
+    s_hit2[e] += a;
+    __syncthreads();
+  }
+  if (e < NE) {
+    const uint32_t first = s_rows[e] - n, full0 = s_hit2[e] - nfull, all_full = s_hit2[511];
+    for (uint32_t i = 0; i < nfull; i++) o.big[full0 + i] = BigTile{e, first + i * kTileN, kTileN};
+    if (rem) {
+      uint32_t rank = 0;
+      for (uint32_t j = 0; j < 512; j++) rank += s_bigrows[j] > rem || (s_bigrows[j] == rem && j < e);
+      o.big[all_full + rank] = BigTile{e, first + nfull * kTileN, rem};
+    }
   }
   if (e == 511) {
     o.counters[0] = s_tiles[e], o.counters[1] = s_groups[e], o.counters[2] = s_hit[e], o.counters[3] = s_rows[e];
-    o.counters[4] = s_big[e], o.counters[5] = s_bigrows[e];
+    o.counters[4] = s_big[e], o.counters[5] = total_rows_big;
   }
 }
 

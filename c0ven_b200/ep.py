@@ -141,7 +141,7 @@ class ExpertParallelMoE:
     def __init__(self, stages, group=None):
         self.st, self.group = stages, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.sent_rows = self.received_rows = 0
+        self.sent_rows = self.received_rows = self.expert_rows = 0  # of the last step: rows sent to and received from other ranks; rows its experts ran
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         st, W = self.st, self.world
@@ -171,7 +171,7 @@ class ExpertParallelMoE:
             if out is None:
                 out = st.empty(tuple(x.shape), torch.float32)
             st.combine(y, out)
-        self.sent_rows, self.received_rows = sum(send) - send[self.rank], R - recv[self.rank]
+        self.sent_rows, self.received_rows, self.expert_rows = sum(send) - send[self.rank], R - recv[self.rank], R
         return out
 
 
