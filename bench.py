@@ -98,9 +98,9 @@ class ClockSampler:
 _STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", "copies")
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), by
-# (workload, stage); the summaries under profiles/ say which capture. None: not captured.
-TRAFFIC = {("ragged3521_q4_k_zipf", "gate_up"): 444.7e6, ("ragged3521_q4_k_zipf", "down"): 422.4e6,
-           ("decode1_q8_0", "gate_up"): 531.6e6, ("stack48_verify32_iq3_s", "gate_up"): 220.6e6}
+# (workload, rows, stage), per launch (one layer); the summaries under profiles/ say which capture. None: not captured.
+TRAFFIC = {("ragged3521_q4_k_zipf", 3521, "gate_up"): 444.7e6, ("ragged3521_q4_k_zipf", 3521, "down"): 422.4e6,
+           ("decode1_q8_0", 32, "gate_up"): 531.6e6, ("stack48_verify32_iq3_s", 32, "gate_up"): 220.6e6}
 
 
 def algorithmic(w: dict, T: int, experts_hit: int, world: int = 1) -> dict:
@@ -331,7 +331,7 @@ def run_gpu(args, w):
     else:
         achieved = alg["bytes_" + dom] / (dom_ms * 1e-3) / 1e9
         roof = dict(bound="hbm", achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s", frac=achieved / peaks["hbm_gbs"])
-    roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=TRAFFIC.get((w["name"], dom)))
+    roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=TRAFFIC.get((w["name"], T, dom)) if world == 1 else None)
     cpu = None
     if world == 1 and not args.no_cpu and nlayers == 1:
         from oracle import oracle

@@ -118,6 +118,7 @@ struct moe_layer {
   uint32_t E = 0, F = 0, NE = 0, K = 0, N = 0, local = 0, Tmax = 0;
   uint64_t Rmax = 0;  // expert rows a call may bring: max_tokens * n_used, or max_expert_rows
   bool has_shared = false, profile = false, can_tensor = false;
+  uint32_t sms = 148;  // the device's SM count
   std::unique_ptr<Stream> stream, aux;  // aux: the shared expert runs beside the routed ones
   std::unique_ptr<Event> fork_ev, join_ev;
   // Steps of few rows are bound by launches, not work: the whole call is recorded once per (rows, buffers, stream)
@@ -208,6 +209,11 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->Tmax = c.max_tokens ? c.max_tokens : 4352;
   l->has_shared = c.shexp_gate_type != 0;
   l->profile = c.flags & MOE_FLAG_PROFILE;
+  {
+    int n = 0;
+    CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, c.device));
+    l->sms = n > 0 ? (uint32_t)n : 148;
+  }
   l->can_tensor = !(c.flags & MOE_FLAG_NO_TENSOR) && c.n_embd % kTileK == 0 && c.n_ff % kTileM == 0;
   l->stream = std::make_unique<Stream>();
   l->aux = std::make_unique<Stream>();
@@ -306,6 +312,13 @@ uint32_t tensor_min_for(const moe_layer *l, uint64_t R) {
   return R >= 1280 ? 1 : 16;
 }
 
+// With the default threshold and a short step, the pack may lower the threshold itself to as few as 2 rows, as long as
+// no more than this many experts then take the tile kernels (half the SMs: each expert is four gate/up items). 0: fixed,
+// as in steps of a few rows, where two more launches would cost more than they could save.
+uint32_t tensor_budget_for(const moe_layer *l, uint64_t R) {
+  return l->can_tensor && !l->cfg.tensor_min_rows && R >= 64 && R < 1280 ? l->sms / 2 : 0;
+}
+
 // Quantise x, the router's logits and top-k, and the pack of the step's T * K assignments over every expert.
 void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   const uint32_t E = l->E, NE = l->NE, K = l->K, N = l->N;
@@ -344,7 +357,8 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   // On one GPU the pack also lists the groups and big tiles of the experts' kernels; expert parallel, it only sorts.
   const uint32_t tm = l->local == NE ? tensor_min_for(l, A) : 0;
   l->last_tensor_min = tm;
-  k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, group_cap(A, NE), l->pack.out());
+  k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, l->local == NE ? tensor_budget_for(l, A) : 0, group_cap(A, NE),
+                                 l->pack.out());
   launched(l, cudaGetLastError(), "pack scan");
   const uint32_t chunk_len = kChunkTokens * K;
   k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->pack.base.get(),
@@ -364,7 +378,9 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   const int M = group_rows(std::min<uint64_t>(std::min<uint64_t>(gmax, most), tm ? std::min<uint64_t>(R, tm - 1) : R));
   const uint32_t max_groups =
       tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(R, (uint64_t)nexp * ((tm - 2) / gmax + 1)) : 0) : (uint32_t)std::min<uint64_t>(R, R / gmax + nexp);
-  const uint32_t max_big = tm && R >= tm ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm)) : 0;
+  // The pack may have lowered the threshold to 2 (tensor_budget_for): the tile launches are sized for that.
+  const uint32_t tm_low = tm && tensor_budget_for(l, R) ? std::min<uint32_t>(tm, 2) : tm;
+  const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
   mark(l, ST_GATE_UP, st);
   if (max_big) {
     ExpertTilesArgs a{};
@@ -687,7 +703,7 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
     const uint32_t nchunks = (R + kLocalChunk - 1) / kLocalChunk;
     k_chunk_hist<<<nchunks, 256, 0, st>>>(ids_dev, R, kLocalChunk, nexp, l->cfg.expert_first, pk.chunk_hist.get());
     launched(l, cudaGetLastError(), "local counts");
-    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, group_cap(R, nexp), pk.out());
+    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, tensor_budget_for(l, R), group_cap(R, nexp), pk.out());
     launched(l, cudaGetLastError(), "local pack scan");
     k_pack_fill<<<nchunks, 512, kLocalChunk * sizeof(int32_t), st>>>(ids_dev, R, kLocalChunk, nexp, pk.base.get(), pk.chunk_off.get(), 1,
                                                                  pk.inv.get(), pk.row_src.get(), l->cfg.expert_first);

@@ -425,19 +425,46 @@ struct PackOut {
 __host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { return tensor_min != 0 && n >= tensor_min; }
 
 // One CTA of 512 threads, thread e for expert e: sums the chunks' counts, scans them over the experts, writes tiles
-// and groups. first_expert: the id of slot 0. group_max: the most rows a group holds (<= kGroupMax).
+// and groups. first_expert: the id of slot 0. group_max: the most rows a group holds (<= kGroupMax). tensor_budget, when
+// not 0, lets the step lower tensor_min itself: to the least of 2, 4, 8 rows that sends at most tensor_budget experts
+// to the tile kernels. With skewed routing a short step has a few experts with many rows, which the tile kernels take
+// in the time the integer-dot kernel needs for one of them; with even routing it has hundreds of experts with one or
+// two rows, whose tiles would be all decode and no product: the threshold moves only if the experts that then change
+// kernels hold at least half of the step's rows.
 static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
-                                                  uint32_t first_expert, uint32_t tensor_min, uint32_t group_max, PackOut o) {
+                                                  uint32_t first_expert, uint32_t tensor_min, uint32_t tensor_budget, uint32_t group_max,
+                                                  PackOut o) {
   __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512], s_hit2[512];
   const uint32_t e = threadIdx.x;
   uint32_t run = 0;
   if (e < NE) {
-#pragma unroll 4
-    for (uint32_t c = 0; c < nchunks; c++) {
-      const uint32_t v = chunk_hist[(uint64_t)c * NE + e];
-      o.chunk_off[(uint64_t)c * NE + e] = run;
-      run += v;
+    // Sixteen chunks' counts are loaded at once: a lone CTA walking a thousand chunks one load at a time would spend
+    // the stage on memory latency.
+    for (uint32_t c0 = 0; c0 < nchunks; c0 += 16) {
+      uint32_t v[16];
+#pragma unroll
+      for (uint32_t j = 0; j < 16; j++) v[j] = c0 + j < nchunks ? chunk_hist[(uint64_t)(c0 + j) * NE + e] : 0;
+#pragma unroll
+      for (uint32_t j = 0; j < 16; j++) {
+        if (c0 + j < nchunks) o.chunk_off[(uint64_t)(c0 + j) * NE + e] = run;
+        run += v[j];
+      }
     }
+  }
+  if (tensor_budget) {
+    // Lower only if the experts that would move hold at least half of the step's rows: moving a few rows costs two
+    // more kernels for nothing.
+    __shared__ uint32_t s_rows_ge[3], s_total;
+    if (e < 3) s_rows_ge[e] = 0;
+    if (e == 3) s_total = 0;
+    __syncthreads();
+    if (run >= 2) atomicAdd(&s_rows_ge[0], run);
+    if (run >= 4) atomicAdd(&s_rows_ge[1], run);
+    if (run >= 8) atomicAdd(&s_rows_ge[2], run);
+    if (run) atomicAdd(&s_total, run);
+    const uint32_t ge2 = __syncthreads_count(run >= 2), ge4 = __syncthreads_count(run >= 4), ge8 = __syncthreads_count(run >= 8);
+    const int pick = ge2 <= tensor_budget ? 0 : ge4 <= tensor_budget ? 1 : ge8 <= tensor_budget ? 2 : -1;
+    if (pick >= 0 && 2 * s_rows_ge[pick] >= s_total) tensor_min = min(tensor_min, 2u << pick);
   }
   const bool tensor = n_is_tensor(run, tensor_min);
   const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = tensor ? 0 : (n + group_max - 1) / group_max;
