@@ -56,13 +56,17 @@ class ClockSampler:
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, device: int):
-        self.device, self.lines, self.proc = device, [], None
+    def __init__(self, devices):
+        """devices: the GPU indices to watch, or None to watch nothing (with several ranks only rank 0 samples, every
+        rank's GPU in one nvidia-smi process: a poller per rank slows the ranks' own driver calls)."""
+        self.devices, self.lines, self.proc = devices, [], None
 
     def __enter__(self):
+        if not self.devices:
+            return self
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100" if len(self.devices) == 1 else "250",
+                                          "-i", ",".join(str(d) for d in self.devices)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
         except OSError:
             self.proc = None
@@ -242,7 +246,7 @@ def run_gpu(args, w):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
-    with ClockSampler(local) as clocks:
+    with ClockSampler([local] if world == 1 else (list(range(world)) if rank == 0 else None)) as clocks:
         for i in range(args.steps):
             flush.fill_(i & 0xFF)  # L2 flush between timed iterations, outside the timed interval
             torch.cuda.synchronize()

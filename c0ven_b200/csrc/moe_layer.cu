@@ -312,7 +312,7 @@ uint32_t tensor_min_for(const moe_layer *l, uint64_t R) {
   return R >= 1280 ? 1 : 16;
 }
 
-// With the default threshold and a short step, the pack may lower the threshold itself to as few as 2 rows, as long as
+// With the default threshold and a short step, the pack may lower the threshold itself to as few as 1 row, as long as
 // no more than this many experts then take the tile kernels (half the SMs: each expert is four gate/up items). 0: fixed,
 // as in steps of a few rows, where two more launches would cost more than they could save.
 uint32_t tensor_budget_for(const moe_layer *l, uint64_t R) {
@@ -378,8 +378,8 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   const int M = group_rows(std::min<uint64_t>(std::min<uint64_t>(gmax, most), tm ? std::min<uint64_t>(R, tm - 1) : R));
   const uint32_t max_groups =
       tm ? (tm > 1 ? (uint32_t)std::min<uint64_t>(R, (uint64_t)nexp * ((tm - 2) / gmax + 1)) : 0) : (uint32_t)std::min<uint64_t>(R, R / gmax + nexp);
-  // The pack may have lowered the threshold to 2 (tensor_budget_for): the tile launches are sized for that.
-  const uint32_t tm_low = tm && tensor_budget_for(l, R) ? std::min<uint32_t>(tm, 2) : tm;
+  // The pack may have lowered the threshold to 1 (tensor_budget_for): the tile launches are sized for that.
+  const uint32_t tm_low = tm && tensor_budget_for(l, R) ? 1 : tm;
   const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
   mark(l, ST_GATE_UP, st);
   if (max_big) {

@@ -426,7 +426,7 @@ __host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { r
 
 // One CTA of 512 threads, thread e for expert e: sums the chunks' counts, scans them over the experts, writes tiles
 // and groups. first_expert: the id of slot 0. group_max: the most rows a group holds (<= kGroupMax). tensor_budget, when
-// not 0, lets the step lower tensor_min itself: to the least of 2, 4, 8 rows that sends at most tensor_budget experts
+// not 0, lets the step lower tensor_min itself: to the least of 1, 2, 4, 8 rows that sends at most tensor_budget experts
 // to the tile kernels. With skewed routing a short step has a few experts with many rows, which the tile kernels take
 // in the time the integer-dot kernel needs for one of them; with even routing it has hundreds of experts with one or
 // two rows, whose tiles would be all decode and no product: the threshold moves only if the experts that then change
@@ -462,9 +462,14 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
     if (run >= 4) atomicAdd(&s_rows_ge[1], run);
     if (run >= 8) atomicAdd(&s_rows_ge[2], run);
     if (run) atomicAdd(&s_total, run);
-    const uint32_t ge2 = __syncthreads_count(run >= 2), ge4 = __syncthreads_count(run >= 4), ge8 = __syncthreads_count(run >= 8);
-    const int pick = ge2 <= tensor_budget ? 0 : ge4 <= tensor_budget ? 1 : ge8 <= tensor_budget ? 2 : -1;
-    if (pick >= 0 && 2 * s_rows_ge[pick] >= s_total) tensor_min = min(tensor_min, 2u << pick);
+    const uint32_t ge1 = __syncthreads_count(run >= 1), ge2 = __syncthreads_count(run >= 2), ge4 = __syncthreads_count(run >= 4),
+                   ge8 = __syncthreads_count(run >= 8);
+    if (ge1 <= tensor_budget) {
+      tensor_min = 1;  // few experts in all: every one to the tile kernels
+    } else {
+      const int pick = ge2 <= tensor_budget ? 0 : ge4 <= tensor_budget ? 1 : ge8 <= tensor_budget ? 2 : -1;
+      if (pick >= 0 && 2 * s_rows_ge[pick] >= s_total) tensor_min = min(tensor_min, 2u << pick);
+    }
   }
   const bool tensor = n_is_tensor(run, tensor_min);
   const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = tensor ? 0 : (n + group_max - 1) / group_max;
