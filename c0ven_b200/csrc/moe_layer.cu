@@ -381,12 +381,15 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   // The pack may have lowered the threshold to 1 (tensor_budget_for): the tile launches are sized for that.
   const uint32_t tm_low = tm && tensor_budget_for(l, R) ? 1 : tm;
   const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
+  if (max_big) {
+    // The rows in expert order first: a tile's rows are then one box after another for the kernel's copies. Part of
+    // the pack stage: the gate/up stage times the product's own kernels.
+    k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
+    launched(l, cudaGetLastError(), "rows to expert order");
+  }
   mark(l, ST_GATE_UP, st);
   if (max_big) {
     ExpertTilesArgs a{};
-    // The rows in expert order first: a tile's rows are then one box after another for the kernel's copies.
-    k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
-    launched(l, cudaGetLastError(), "rows to expert order");
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
@@ -400,8 +403,8 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
     launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
   }
+  mark(l, ST_DOWN, st);  // the down stage starts with its input's quantiser
   quantize_rows(l, l->h.get(), R, F, l->hq_routed, st);
-  mark(l, ST_DOWN, st);
   if (max_big) {
     ExpertTilesArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;

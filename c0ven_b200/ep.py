@@ -13,6 +13,8 @@ also runs on CPU ranks (gloo) in the tests, with a CPU stand-in for the stages.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 import torch.distributed as dist
@@ -64,7 +66,7 @@ class GpuStages:
         self._bufs = {}
         # The shared expert needs no other GPU: it runs on a stream of its own beside the exchanges and the experts.
         self.side = torch.cuda.Stream(device=self.device)
-        self.shared_beside = not profile
+        self.shared_beside = not profile and os.environ.get("C0VEN_EP_SHARED_INLINE") != "1"
 
     def route(self, x: torch.Tensor) -> torch.Tensor:
         """Routes and packs x's rows; returns the rows per expert, an int32 tensor [n_experts] on the device."""
