@@ -53,7 +53,7 @@ def build_layer(w: dict, seed: int = 0) -> dict:
 
 class ClockSampler:
     """nvidia-smi's SM clock and throttle reasons, sampled while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, devices):
@@ -81,13 +81,29 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    def window(self, t0: float, t1: float):
+        """The timed region, as time.time() values: summary() keeps the samples taken inside it (the poller starts
+        before the warm-up, so that its own start-up, which takes the driver's locks, is not in the timed steps)."""
+        self.t0, self.t1 = t0, t1
+
     def summary(self) -> dict:
+        import datetime
+
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for ln in self.lines:
             f = [s.strip() for s in ln.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+            except ValueError:
+                ts = None
+            rows.append((ts, f[1:]))
+        t0, t1 = getattr(self, "t0", None), getattr(self, "t1", None)
+        inside = [f for ts, f in rows if ts is not None and t0 is not None and t0 - 0.3 <= ts <= t1 + 0.3]
+        for f in inside or [f for _, f in rows]:
             try:
                 sm.append(float(f[1])), mx.append(float(f[2]))
             except ValueError:
@@ -239,14 +255,15 @@ def run_gpu(args, w):
 
     # Timed steps run as a caller would run them: no per-stage timing, the shared expert beside the routed ones, small
     # steps replayed from their recorded graph. The stages are timed afterwards, in a few more steps with the timing on.
-    for _ in range(args.warmup):
-        step()
-    sync()
-    k0 = kernels()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    barrier()
     with ClockSampler([local] if world == 1 else (list(range(world)) if rank == 0 else None)) as clocks:
+        for _ in range(args.warmup):
+            step()
+        sync()
+        k0 = kernels()
+        barrier()
+        t_begin = time.time()
         for i in range(args.steps):
             flush.fill_(i & 0xFF)  # L2 flush between timed iterations, outside the timed interval
             torch.cuda.synchronize()
@@ -254,6 +271,7 @@ def run_gpu(args, w):
             step()
             ends[i].record(stream)
             sync()
+        clocks.window(t_begin, time.time())
         barrier()
     launches = kernels() - k0
     ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / args.steps
