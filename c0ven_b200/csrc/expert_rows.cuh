@@ -283,8 +283,10 @@ __device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32
 // already fill the registers with accumulators.
 __host__ __device__ constexpr int rows_batch(int nmat, int nu, int m, bool heavy) {
   // heavy: a unit that holds many registers while it waits (IQ3_S: quants, signs, high bits, scale): fewer passes at
-  // once leave room for a second CTA on the SM, which its arithmetic-bound decode needs more than loads in flight.
-  const int want = 16 / (nmat * nu) > 0 ? 16 / (nmat * nu) : 1, cap = heavy ? 2 : m >= 4 ? 4 : 8;
+  // once leave room for more CTAs on the SM (three with one pass of gate and up, measured faster than two passes; two
+  // passes for the down product, measured faster than one), which its arithmetic-bound decode needs more than loads
+  // in flight.
+  const int want = 16 / (nmat * nu) > 0 ? 16 / (nmat * nu) : 1, cap = heavy ? (nmat == 2 ? 1 : 2) : m >= 4 ? 4 : 8;
   return want < cap ? want : cap;
 }
 

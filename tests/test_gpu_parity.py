@@ -168,3 +168,33 @@ def test_full_shape_ragged_batch(t):
     st = gpu.stats()
     assert 0 < st["last_tensor_rows"] < 620 * 11
     gpu.close()
+
+
+def test_full_size_ragged3521_q4_k():
+    """Configuration 2 at its full size: 3,521 rows as runs {1, 8, 512, 3000}, Q4_K, Zipf 1.1, every expert on the
+    tile kernels. The routing of all 3,521 rows is compared bit for bit with the oracle's (ids, the pack permutation,
+    the tiles); the outputs of a sample of rows from every run with the oracle's for those rows computed alone, which
+    the oracle's per-token independence allows (core/tests/cpu_experts_test.cpp:240-275 in kind); and the first 100
+    rows run as their own batch route the same."""
+    layer = synth.make_layer(gate_type=synth.Q4_K, zipf_s=1.1, seed=0)
+    T = 3521
+    x = synth.make_input(T, 2048, seed=1)
+    gpu = MoELayer(layer, max_tokens=T)
+    out = gpu.forward(x)
+    ids, w, inv, tiles = gpu.route(T)
+    st = gpu.stats()
+    assert st["last_tensor_rows"] >= T * 10   # 35,210 rows >= 1,280: every expert takes the tile kernels
+    rl = O.router_logits(x, layer["router"], layer["shexp_gate_inp"], layer["router_bias"])
+    rids, rw, _ = O.router_topk(rl, 10)
+    assert np.array_equal(ids, rids)
+    assert np.allclose(w, rw, rtol=1e-5, atol=1e-7)
+    cnt, base, rinv, rtiles = O.pack(rids, 512)
+    assert np.array_equal(inv, rinv) and np.array_equal(tiles, rtiles)
+    assert sorted(inv.tolist()) == list(range(T * 10))
+    sample = np.array([0, 1, 5, 8, 9, 100, 300, 520, 521, 1000, 2000, 3000, 3520])
+    ref = O.moe_forward(layer, x[sample])[0]
+    rel, cos = errors(out[sample], ref)
+    assert rel <= MAX_REL and cos >= MIN_COS, (rel, cos)
+    gpu.forward(x[:100])
+    assert np.array_equal(gpu.route(100)[0], ids[:100])
+    gpu.close()
