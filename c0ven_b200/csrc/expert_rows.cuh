@@ -279,14 +279,18 @@ __device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32
     Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n);
 }
 
-// Passes of a warp whose loads are issued together: about 16 loads of 16 bytes a lane, fewer when many activation rows
+// 16-byte loads a lane keeps in flight: with 8 the Q8_0 kernels fit three CTAs on an SM (16 took 114 registers, two CTAs),
+// measured 2 to 5 % faster on steps of 1 to 32 rows.
+constexpr int kRowsInFlight = 8;
+
+// Passes of a warp whose loads are issued together: about kRowsInFlight loads of 16 bytes a lane, fewer when many activation rows
 // already fill the registers with accumulators.
 __host__ __device__ constexpr int rows_batch(int nmat, int nu, int m, bool heavy) {
   // heavy: a unit that holds many registers while it waits (IQ3_S: quants, signs, high bits, scale): fewer passes at
   // once leave room for more CTAs on the SM (three with one pass of gate and up, measured faster than two passes; two
   // passes for the down product, measured faster than one), which its arithmetic-bound decode needs more than loads
   // in flight.
-  const int want = 16 / (nmat * nu) > 0 ? 16 / (nmat * nu) : 1, cap = heavy ? (nmat == 2 ? 1 : 2) : m >= 4 ? 4 : 8;
+  const int want = kRowsInFlight / (nmat * nu) > 0 ? kRowsInFlight / (nmat * nu) : 1, cap = heavy ? (nmat == 2 ? 1 : 2) : m >= 4 ? 4 : 8;
   return want < cap ? want : cap;
 }
 
