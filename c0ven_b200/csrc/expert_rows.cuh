@@ -43,6 +43,7 @@ struct ExpertRowsArgs {
   const uint32_t *ngroups;
   uint32_t dense_rows;
   uint32_t n_min, n_max;    // of the groups, only those with n_min <= n <= n_max rows are this launch's (0, 0: all)
+  uint32_t slabs;           // row slabs a CTA takes one after another (0 or 1: one); only with the row length known at compile time
   float *out;  // out[expert-order row][r]
   uint32_t out_stride;
   float limit;  // SwiGLU limit, 0: off
@@ -304,8 +305,11 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   constexpr bool q8k = act_is_q8k(QT);
   uint32_t slot, start, n;
   if (a.groups) {
-    if (blockIdx.y >= *a.ngroups) return;
+    // Both loads go out together: the list is as long as the grid, so the entry can be read before the count says
+    // whether it is one (a CTA's life is a chain of dependent loads; this takes one link out).
+    const uint32_t ng = __ldg(a.ngroups);
     const MoeGroup g = a.groups[blockIdx.y];
+    if (blockIdx.y >= ng) return;
     slot = g.slot, start = g.start, n = g.n;
     if (a.n_max && (n < a.n_min || n > a.n_max)) return;
   } else {
@@ -324,16 +328,19 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   constexpr int RB = rows_batch(NMAT, NU, M, QT == QT_IQ3_S);  // passes whose loads go out together
   using Raw = typename Unit<QT>::Raw;
   const uint32_t rows_per_warp = UPL > 0 ? RPP * RB : a.rows_per_cta / 8;
-  const uint32_t r_begin = blockIdx.x * (8 * rows_per_warp) + warp * rows_per_warp;
+  // A CTA takes `slabs` slabs of 8 * rows_per_warp weight rows one after another, so that what it does once (being
+  // launched, finding its group, staging the activations) is spread over more weight bytes.
+  const uint32_t slabs = UPL > 0 && a.slabs > 1 ? a.slabs : 1, slab_rows = 8 * rows_per_warp;
+  const uint32_t r_begin = blockIdx.x * slabs * slab_rows + warp * rows_per_warp;
 
   // With the row length known at compile time, every load of the warp's rows goes out first, before the activations
   // are staged: the weights come from HBM and their latency is the kernel's, so as many bytes as the registers hold
   // are put in flight at once.
   Raw raw[RB][NMAT][NU];
-  if constexpr (UPL > 0) {
+  auto fetch_slab = [&](uint32_t base) {
 #pragma unroll
     for (int b = 0; b < RB; b++) {
-      const uint32_t r = r_begin + b * RPP + sub;
+      const uint32_t r = base + b * RPP + sub;
       if (r < a.R) {
 #pragma unroll
         for (int j = 0; j < NU; j++) {
@@ -342,7 +349,8 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
         }
       }
     }
-  }
+  };
+  if constexpr (UPL > 0) fetch_slab(r_begin);
 
   uint32_t *grid = (uint32_t *)(smem + M * stride);
   if constexpr (QT == QT_IQ3_S)
@@ -387,22 +395,26 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   };
 
   if constexpr (UPL > 0) {
+    for (uint32_t sl = 0; sl < slabs; sl++) {
+      const uint32_t base = r_begin + sl * slab_rows;
+      if (sl > 0) fetch_slab(base);
 #pragma unroll
-    for (int b = 0; b < RB; b++) {
-      const uint32_t r = r_begin + b * RPP + sub;
-      float acc[NMAT][M];
+      for (int b = 0; b < RB; b++) {
+        const uint32_t r = base + b * RPP + sub;
+        float acc[NMAT][M];
 #pragma unroll
-      for (int m = 0; m < NMAT; m++)
+        for (int m = 0; m < NMAT; m++)
 #pragma unroll
-        for (int t = 0; t < M; t++) acc[m][t] = 0.0f;
-      if (r < a.R) {
+          for (int t = 0; t < M; t++) acc[m][t] = 0.0f;
+        if (r < a.R) {
 #pragma unroll
-        for (int j = 0; j < NU; j++) {
-          unit_dot<QT, M>(raw[b][0][j], K, li + G * j, smem, stride, acc[0], n, grid);
-          if constexpr (NMAT == 2) unit_dot<QT, M>(raw[b][1][j], K, li + G * j, smem, stride, acc[1], n, grid);
+          for (int j = 0; j < NU; j++) {
+            unit_dot<QT, M>(raw[b][0][j], K, li + G * j, smem, stride, acc[0], n, grid);
+            if constexpr (NMAT == 2) unit_dot<QT, M>(raw[b][1][j], K, li + G * j, smem, stride, acc[1], n, grid);
+          }
         }
+        finish(acc, r);
       }
-      finish(acc, r);
     }
   } else {
     for (uint32_t rr = 0; rr < rows_per_warp; rr += RPP) {

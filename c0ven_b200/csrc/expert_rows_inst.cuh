@@ -21,7 +21,15 @@ static cudaError_t launch_one(ExpertRowsArgs a, uint32_t max_groups, const uint3
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  const dim3 grid((a.R + a.rows_per_cta - 1) / a.rows_per_cta, max_groups);
+  // Slabs per CTA: four when that still leaves some thousand CTAs (two per CTA slot of a 148-SM GPU), else two, else
+  // one. Measured on 32 rows of Q8_0 (247 experts): gate/up 0.142 ms with one slab a CTA, 0.112 with four, 0.119 with eight.
+  uint32_t slabs = 1;
+  if (UPL > 0) {
+    const uint64_t ctas = (uint64_t)((a.R + a.rows_per_cta - 1) / a.rows_per_cta) * max_groups;
+    slabs = ctas >= 4 * 1184 ? 4 : ctas >= 2 * 1184 ? 2 : 1;
+  }
+  a.slabs = slabs;
+  const dim3 grid((a.R + a.rows_per_cta * slabs - 1) / (a.rows_per_cta * slabs), max_groups);
   kernel<<<grid, 256, smem, st>>>(a, grid_global);
   return cudaGetLastError();
 }

@@ -101,7 +101,9 @@ struct PackBuffers {
     const uint64_t nchunks = (max_rows + chunk_len - 1) / chunk_len + 1;
     chunk_hist.alloc(nchunks * n), chunk_off.alloc(nchunks * n);
     cnt.alloc(n), base.alloc(n), counters.alloc(8), inv.alloc(max_rows), row_src.alloc(max_rows);
-    tiles.alloc(max_rows / kTileRows + n), groups.alloc(max_rows / kGroupMax + n), big.alloc(max_rows / kTileN + n);
+    tiles.alloc(max_rows / kTileRows + n), big.alloc(max_rows / kTileN + n);
+    // As long as any grid over it: the integer-dot kernel reads its entry before it knows the list's length.
+    groups.alloc(max_rows + n);
   }
   PackOut out() const { return PackOut{cnt.get(), base.get(), chunk_off.get(), tiles.get(), groups.get(), big.get(), counters.get()}; }
 };
