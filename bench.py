@@ -120,7 +120,7 @@ _STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine",
 # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), by
 # (workload, rows, stage), per launch (one layer); the summaries under profiles/ say which capture. None: not captured.
 TRAFFIC = {("ragged3521_q4_k_zipf", 3521, "gate_up"): 444.7e6, ("ragged3521_q4_k_zipf", 3521, "down"): 422.4e6,
-           ("decode1_q8_0", 32, "gate_up"): 531.6e6, ("stack48_verify32_iq3_s", 32, "gate_up"): 220.6e6}
+           ("decode1_q8_0", 32, "gate_up"): 554.2e6, ("decode1_q8_0", 32, "down"): 280.5e6, ("stack48_verify32_iq3_s", 32, "gate_up"): 220.6e6}
 
 
 def algorithmic(w: dict, T: int, experts_hit: int, world: int = 1) -> dict:
