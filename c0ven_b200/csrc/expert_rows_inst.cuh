@@ -41,7 +41,9 @@ static cudaError_t launch_shape(const ExpertRowsArgs &a, uint32_t max_groups, co
   // instantiation, which finds a row's units at run time.
   constexpr uint32_t U2048 = 2048 / Unit<QT>::kValues, U512 = 512 / Unit<QT>::kValues, U256 = 256 / Unit<QT>::kValues;
   if (upr == U2048) return launch_one<QT, NMAT, M, 32, U2048 / 32>(a, max_groups, grid_global, st);
-  if (upr == U512) return launch_one<QT, NMAT, M, (U512 < 32 ? U512 : 32), 1>(a, max_groups, grid_global, st);
+  // A row of 32 units (Q8_0's 512 values): 16 lanes with two units each, two rows a warp pass, so that a reduction and a
+  // store serve twice the bytes.
+  if (upr == U512) return launch_one<QT, NMAT, M, (U512 < 32 ? U512 : 16), (U512 < 32 ? 1 : U512 / 16)>(a, max_groups, grid_global, st);
   if (upr == U256) return launch_one<QT, NMAT, M, (U256 < 32 ? U256 : 32), 1>(a, max_groups, grid_global, st);
   return launch_one<QT, NMAT, M, 32, 0>(a, max_groups, grid_global, st);
 }
