@@ -352,20 +352,28 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   }
   launched(l, cudaGetLastError(), "router logits");
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
-  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), by_pieces ? l->pieces.get() : nullptr, l->bias.get(), l->gate_parts.get(),
-                                                      E / 256, T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->pack.chunk_hist.get());
-  launched(l, cudaGetLastError(), "router top-k");
-  mark(l, ST_PACK, st);
   // On one GPU the pack also lists the groups and big tiles of the experts' kernels; expert parallel, it only sorts.
-  const uint32_t tm = l->local == NE ? tensor_min_for(l, A) : 0;
+  const uint32_t tm = l->local == NE ? tensor_min_for(l, A) : 0, budget = l->local == NE ? tensor_budget_for(l, A) : 0;
   l->last_tensor_min = tm;
-  k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, l->local == NE ? tensor_budget_for(l, A) : 0, group_cap(A, NE),
-                                 l->pack.out());
-  launched(l, cudaGetLastError(), "pack scan");
   const uint32_t chunk_len = kChunkTokens * K;
-  k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->pack.base.get(),
-                                                             l->pack.chunk_off.get(), K, l->pack.inv.get(), l->pack.row_src.get());
-  launched(l, cudaGetLastError(), "pack fill");
+  if (nchunks == 1 && !by_pieces && NE <= 512) {
+    // One chunk: top-k, scan and fill in one CTA (the pack stage then has no kernel of its own).
+    k_router_topk_pack<<<1, 32 * kChunkTokens, chunk_len * sizeof(int32_t), st>>>(l->rl.get(), l->bias.get(), T, NE, K, l->ids.get(), l->w.get(),
+                                                                                  l->gs.get(), tm, budget, group_cap(A, NE), l->pack.out(),
+                                                                                  l->pack.inv.get(), l->pack.row_src.get());
+    launched(l, cudaGetLastError(), "router top-k and pack");
+    mark(l, ST_PACK, st);
+  } else {
+    k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), by_pieces ? l->pieces.get() : nullptr, l->bias.get(), l->gate_parts.get(),
+                                                        E / 256, T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->pack.chunk_hist.get());
+    launched(l, cudaGetLastError(), "router top-k");
+    mark(l, ST_PACK, st);
+    k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, budget, group_cap(A, NE), l->pack.out());
+    launched(l, cudaGetLastError(), "pack scan");
+    k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->pack.base.get(),
+                                                               l->pack.chunk_off.get(), K, l->pack.inv.get(), l->pack.row_src.get());
+    launched(l, cudaGetLastError(), "pack fill");
+  }
   l->last_T = T, l->last_pack = &l->pack;
 }
 

@@ -275,13 +275,12 @@ constexpr int kMaxPerLane = 16;  // experts a lane holds at most: 512 / 32
 
 // The logits come as rows rl[t][NE + 1] (the gate's logit last), or, with pieces set, as the partial sums
 // pieces[p][t][e] of k_router_pieces, added here in order with the bias, and the gate's logit as gate_parts[t][nparts].
-static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const float *__restrict__ pieces,
-                                                                  const float *__restrict__ bias, const float *__restrict__ gate_parts,
-                                                                  uint32_t nparts, uint32_t T, uint32_t NE,
-                                                                  uint32_t K, int32_t *__restrict__ ids,
-                                                                  float *__restrict__ w, float *__restrict__ gs,
-                                                                  uint32_t *__restrict__ chunk_hist) {
-  __shared__ uint32_t hist[512];
+// The block's part: its rows' ids, weights and gates written, the chunk's count of every expert left in hist (shared,
+// 512 words) and, when s_ids is not null, the chunk's ids there too (shared, kChunkTokens * K words).
+__device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, const float *__restrict__ pieces,
+                                                  const float *__restrict__ bias, const float *__restrict__ gate_parts, uint32_t nparts,
+                                                  uint32_t T, uint32_t NE, uint32_t K, int32_t *__restrict__ ids, float *__restrict__ w,
+                                                  float *__restrict__ gs, uint32_t *hist, int32_t *s_ids) {
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
   __syncthreads();
   const uint32_t lane = threadIdx.x % 32, t = blockIdx.x * kChunkTokens + threadIdx.x / 32, per = NE / 32;
@@ -346,6 +345,7 @@ static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const 
       ids[(uint64_t)t * K + lane] = (int32_t)my_id;
       w[(uint64_t)t * K + lane] = pk / fmaxf(tot, 6.1035e-5f);
       atomicAdd(&hist[my_id], 1u);
+      if (s_ids) s_ids[(threadIdx.x / 32) * K + lane] = (int32_t)my_id;
     }
     if (lane == 0) {
       float g;
@@ -359,6 +359,16 @@ static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const 
     }
   }
   __syncthreads();
+}
+
+static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const float *__restrict__ pieces,
+                                                                  const float *__restrict__ bias, const float *__restrict__ gate_parts,
+                                                                  uint32_t nparts, uint32_t T, uint32_t NE,
+                                                                  uint32_t K, int32_t *__restrict__ ids,
+                                                                  float *__restrict__ w, float *__restrict__ gs,
+                                                                  uint32_t *__restrict__ chunk_hist) {
+  __shared__ uint32_t hist[512];
+  router_topk_block(rl, pieces, bias, gate_parts, nparts, T, NE, K, ids, w, gs, hist, nullptr);
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
 }
 
@@ -431,30 +441,17 @@ __host__ __device__ inline bool n_is_tensor(uint32_t n, uint32_t tensor_min) { r
 // in the time the integer-dot kernel needs for one of them; with even routing it has hundreds of experts with one or
 // two rows, whose tiles would be all decode and no product: the threshold moves only if the experts that then change
 // kernels hold at least half of the step's rows.
-static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
-                                                  uint32_t first_expert, uint32_t tensor_min, uint32_t tensor_budget, uint32_t group_max,
-                                                  PackOut o) {
+// The scan itself, for every thread of a CTA of 512 threads or more (the threads past 511 only keep the barriers):
+// thread e < NE brings its expert's row count `run`; returns the first row of the expert's run.
+__device__ __forceinline__ uint32_t pack_scan_block(uint32_t e, uint32_t run, uint32_t NE, uint32_t first_expert, uint32_t tensor_min,
+                                                    uint32_t tensor_budget, uint32_t group_max, const PackOut &o) {
   __shared__ uint32_t s_rows[512], s_tiles[512], s_groups[512], s_hit[512], s_big[512], s_bigrows[512], s_hit2[512];
-  const uint32_t e = threadIdx.x;
-  uint32_t run = 0;
-  if (e < NE) {
-    // Sixteen chunks' counts are loaded at once: a lone CTA walking a thousand chunks one load at a time would spend
-    // the stage on memory latency.
-    for (uint32_t c0 = 0; c0 < nchunks; c0 += 16) {
-      uint32_t v[16];
-#pragma unroll
-      for (uint32_t j = 0; j < 16; j++) v[j] = c0 + j < nchunks ? chunk_hist[(uint64_t)(c0 + j) * NE + e] : 0;
-#pragma unroll
-      for (uint32_t j = 0; j < 16; j++) {
-        if (c0 + j < nchunks) o.chunk_off[(uint64_t)(c0 + j) * NE + e] = run;
-        run += v[j];
-      }
-    }
-  }
+  __shared__ uint32_t s_rows_ge[3], s_total;
+  const bool in = e < 512;
+  if (!in || e >= NE) run = 0;
   if (tensor_budget) {
     // Lower only if the experts that would move hold at least half of the step's rows: moving a few rows costs two
     // more kernels for nothing.
-    __shared__ uint32_t s_rows_ge[3], s_total;
     if (e < 3) s_rows_ge[e] = 0;
     if (e == 3) s_total = 0;
     __syncthreads();
@@ -474,18 +471,19 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
   const bool tensor = n_is_tensor(run, tensor_min);
   const uint32_t n = run, nt = (n + kTileRows - 1) / kTileRows, ng = tensor ? 0 : (n + group_max - 1) / group_max;
   const uint32_t nb = tensor ? (n + kTileN - 1) / kTileN : 0;
-  s_rows[e] = n, s_tiles[e] = nt, s_groups[e] = ng, s_hit[e] = n > 0, s_big[e] = nb, s_bigrows[e] = tensor ? n : 0;
+  if (in) s_rows[e] = n, s_tiles[e] = nt, s_groups[e] = ng, s_hit[e] = n > 0, s_big[e] = nb, s_bigrows[e] = tensor ? n : 0;
   __syncthreads();
   for (uint32_t off = 1; off < 512; off <<= 1) {
-    const uint32_t a = e >= off ? s_rows[e - off] : 0, b = e >= off ? s_tiles[e - off] : 0;
-    const uint32_t c = e >= off ? s_groups[e - off] : 0, d = e >= off ? s_hit[e - off] : 0;
-    const uint32_t f = e >= off ? s_big[e - off] : 0, g = e >= off ? s_bigrows[e - off] : 0;
+    const bool take = in && e >= off;
+    const uint32_t a = take ? s_rows[e - off] : 0, b = take ? s_tiles[e - off] : 0;
+    const uint32_t c = take ? s_groups[e - off] : 0, d = take ? s_hit[e - off] : 0;
+    const uint32_t f = take ? s_big[e - off] : 0, g = take ? s_bigrows[e - off] : 0;
     __syncthreads();
-    s_rows[e] += a, s_tiles[e] += b, s_groups[e] += c, s_hit[e] += d, s_big[e] += f, s_bigrows[e] += g;
+    if (in) s_rows[e] += a, s_tiles[e] += b, s_groups[e] += c, s_hit[e] += d, s_big[e] += f, s_bigrows[e] += g;
     __syncthreads();
   }
+  const uint32_t first = in ? s_rows[e] - n : 0;
   if (e < NE) {
-    const uint32_t first = s_rows[e] - n;
     o.cnt[e] = n;
     o.base[e] = first;
     const uint32_t tile0 = s_tiles[e] - nt, group0 = s_groups[e] - ng;
@@ -496,19 +494,19 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
   }
   // Big tiles, sorted by size for the tile kernels' round-robin over CTAs: every full tile of kTileN rows first (in
   // expert order), then the experts' last, shorter tiles by falling row count (ties in expert order). s_bigrows is free
-  // to reuse: the scan's total was read above.
+  // to reuse: the scan's total is read first.
   const uint32_t total_rows_big = s_bigrows[511], nfull = tensor ? n / kTileN : 0, rem = tensor ? n % kTileN : 0;
   __syncthreads();
-  s_hit2[e] = nfull, s_bigrows[e] = rem;
+  if (in) s_hit2[e] = nfull, s_bigrows[e] = rem;
   __syncthreads();
   for (uint32_t off = 1; off < 512; off <<= 1) {
-    const uint32_t a = e >= off ? s_hit2[e - off] : 0;
+    const uint32_t a = in && e >= off ? s_hit2[e - off] : 0;
     __syncthreads();
-    s_hit2[e] += a;
+    if (in) s_hit2[e] += a;
     __syncthreads();
   }
   if (e < NE) {
-    const uint32_t first = s_rows[e] - n, full0 = s_hit2[e] - nfull, all_full = s_hit2[511];
+    const uint32_t full0 = s_hit2[e] - nfull, all_full = s_hit2[511];
     for (uint32_t i = 0; i < nfull; i++) o.big[full0 + i] = BigTile{e, first + i * kTileN, kTileN};
     if (rem) {
       uint32_t rank = 0;
@@ -520,6 +518,29 @@ static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__rest
     o.counters[0] = s_tiles[e], o.counters[1] = s_groups[e], o.counters[2] = s_hit[e], o.counters[3] = s_rows[e];
     o.counters[4] = s_big[e], o.counters[5] = total_rows_big;
   }
+  return first;
+}
+
+static __global__ void __launch_bounds__(512) k_pack_scan(const uint32_t *__restrict__ chunk_hist, uint32_t nchunks, uint32_t NE,
+                                                  uint32_t first_expert, uint32_t tensor_min, uint32_t tensor_budget, uint32_t group_max,
+                                                  PackOut o) {
+  const uint32_t e = threadIdx.x;
+  uint32_t run = 0;
+  if (e < NE) {
+    // Sixteen chunks' counts are loaded at once: a lone CTA walking a thousand chunks one load at a time would spend
+    // the stage on memory latency.
+    for (uint32_t c0 = 0; c0 < nchunks; c0 += 16) {
+      uint32_t v[16];
+#pragma unroll
+      for (uint32_t j = 0; j < 16; j++) v[j] = c0 + j < nchunks ? chunk_hist[(uint64_t)(c0 + j) * NE + e] : 0;
+#pragma unroll
+      for (uint32_t j = 0; j < 16; j++) {
+        if (c0 + j < nchunks) o.chunk_off[(uint64_t)(c0 + j) * NE + e] = run;
+        run += v[j];
+      }
+    }
+  }
+  pack_scan_block(e, run, NE, first_expert, tensor_min, tensor_budget, group_max, o);
 }
 
 // One CTA per chunk, thread e for expert e: walks the chunk's ids in order and hands out its expert's rows in that
@@ -541,6 +562,30 @@ static __global__ void __launch_bounds__(512) k_pack_fill(const int32_t *__restr
       row_src[row] = (a0 + i) / src_div;
       row++;
     }
+}
+
+// A step of one chunk (at most kChunkTokens rows): top-k, scan and fill in one CTA, three launches less for the steps
+// that launches bound. Dynamic shared memory kChunkTokens * K words for the chunk's ids.
+static __global__ void __launch_bounds__(32 * kChunkTokens, 1) k_router_topk_pack(const float *__restrict__ rl, const float *__restrict__ bias, uint32_t T,
+                                                                       uint32_t NE, uint32_t K, int32_t *__restrict__ ids, float *__restrict__ w,
+                                                                       float *__restrict__ gs, uint32_t tensor_min, uint32_t tensor_budget,
+                                                                       uint32_t group_max, PackOut o, uint32_t *__restrict__ inv,
+                                                                       uint32_t *__restrict__ row_src) {
+  __shared__ uint32_t hist[512];
+  extern __shared__ int32_t s_chunk_ids[];
+  router_topk_block(rl, nullptr, bias, nullptr, 0, T, NE, K, ids, w, gs, hist, s_chunk_ids);
+  const uint32_t e = threadIdx.x;
+  const uint32_t run = e < NE ? hist[e] : 0;
+  uint32_t row = pack_scan_block(e, run, NE, 0, tensor_min, tensor_budget, group_max, o);
+  if (e < NE && run) {
+    const uint32_t A = T * K;
+    for (uint32_t i = 0; i < A; i++)
+      if ((uint32_t)s_chunk_ids[i] == e) {
+        inv[i] = row;
+        row_src[row] = i / K;
+        row++;
+      }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
