@@ -341,8 +341,13 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
     }
     const uint32_t warps = tm <= 2 ? 1 : 8;
     const dim3 grid((N + 4 * warps - 1) / (4 * warps), (T + tm - 1) / tm);
-    if (tm == 1)
+    const bool deep = (E / kRouterPieces) % 64 == 0;  // sixteen loads in flight a lane: a step of one row is all latency
+    if (tm == 1 && deep)
+      k_router_logits_rows<1, 16><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+    else if (tm == 1)
       k_router_logits_rows<1><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
+    else if (tm == 2 && deep)
+      k_router_logits_rows<2, 16><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
     else if (tm == 2)
       k_router_logits_rows<2><<<grid, 32, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
     else

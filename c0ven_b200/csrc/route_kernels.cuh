@@ -125,10 +125,10 @@ static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restri
 // order, the pieces then added in order, and an expert's bias last. Both kernels and the CPU oracle keep this one
 // order, so that the logits, and with them the chosen experts, agree bit for bit whatever the row count.
 
-// Few rows (up to TM per CTA pass): a warp takes 4 weight rows, 8 lanes a row, lane s taking piece s; 8 loads of 16 bytes
-// in flight per lane (a piece is a multiple of 32 values). A CTA is one warp when the step has one or two rows, so that
+// Few rows (up to TM per CTA pass): a warp takes 4 weight rows, 8 lanes a row, lane s taking piece s; D loads of 16 bytes
+// in flight per lane (a piece is a multiple of 4 D values: 8 always, 16 when the piece is a multiple of 64 values). A CTA is one warp when the step has one or two rows, so that
 // the router's 4 MB spread over 129 CTAs, and eight warps otherwise, so that the staged rows serve 32 weight rows.
-template <int TM>
+template <int TM, int D = 8>
 static __global__ void __launch_bounds__(256) k_router_logits_rows(const float *__restrict__ x, uint32_t T, uint32_t E,
                                                           const float *__restrict__ W, uint32_t N,
                                                           const float *__restrict__ bias, uint32_t NE,
@@ -139,9 +139,9 @@ static __global__ void __launch_bounds__(256) k_router_logits_rows(const float *
   const uint32_t lane = threadIdx.x % 32, s = lane % 8, row = (blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32) * 4 + lane / 8;
   // The first weights are on their way while the rows are staged.
   const float4 *w = (const float4 *)(W + (uint64_t)min(row, N - 1) * E + s * piece);
-  float4 wq[8];
+  float4 wq[D];
 #pragma unroll
-  for (int i = 0; i < 8; i++) wq[i] = __ldg(w + i);
+  for (int i = 0; i < D; i++) wq[i] = __ldg(w + i);
   for (uint32_t i = threadIdx.x; i < TM * (E / 4); i += blockDim.x) {
     const uint32_t t = i / (E / 4), k4 = i % (E / 4), k = 4 * k4;
     const float4 v = t < tn ? ((const float4 *)(x + (uint64_t)(t0 + t) * E))[k4] : make_float4(0, 0, 0, 0);
@@ -152,16 +152,16 @@ static __global__ void __launch_bounds__(256) k_router_logits_rows(const float *
 #pragma unroll
   for (int t = 0; t < TM; t++) p[t] = 0.0f;
   const float *xp = xs + s * pstride;
-  for (uint32_t i0 = 0; i0 < piece / 4; i0 += 8) {
-    float4 cur[8];
+  for (uint32_t i0 = 0; i0 < piece / 4; i0 += D) {
+    float4 cur[D];
 #pragma unroll
-    for (int i = 0; i < 8; i++) cur[i] = wq[i];
-    if (i0 + 8 < piece / 4) {
+    for (int i = 0; i < D; i++) cur[i] = wq[i];
+    if (i0 + D < piece / 4) {
 #pragma unroll
-      for (int i = 0; i < 8; i++) wq[i] = __ldg(w + i0 + 8 + i);
+      for (int i = 0; i < D; i++) wq[i] = __ldg(w + i0 + D + i);
     }
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < D; i++) {
 #pragma unroll
       for (int t = 0; t < TM; t++) {
         const float4 xv = *(const float4 *)(xp + t * rstride + 4 * (i0 + i));
