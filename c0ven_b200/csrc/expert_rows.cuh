@@ -257,7 +257,8 @@ struct Unit<QT_IQ3_S> {
       if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
       const uint8_t *a = acts + t * stride;
       const int4 *av = (const int4 *)(a + 256 * b + 64 * c);
-      const int4 a0 = av[0], a1 = av[1], a2 = av[2], a3 = av[3];
+      const uint32_t sw = (u >> 1) & 3;  // act_slot's swizzle
+      const int4 a0 = av[0 ^ sw], a1 = av[1 ^ sw], a2 = av[2 ^ sw], a3 = av[3 ^ sw];
       int s0 = __dp4a(g[0], a0.x, 0), s1 = __dp4a(g[8], a2.x, 0);
       s0 = __dp4a(g[1], a0.y, s0), s1 = __dp4a(g[9], a2.y, s1);
       s0 = __dp4a(g[2], a0.z, s0), s1 = __dp4a(g[10], a2.z, s1);
@@ -278,6 +279,15 @@ __device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32
     Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n, grid);
   else
     Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n);
+}
+
+// Where the 16-byte piece i of an activation row's codes sits in shared memory. IQ3_S's units read four pieces 64 bytes
+// apart from lane to lane, which without a swizzle puts a quarter-warp on two groups of four banks (four wavefronts an
+// access instead of one): piece (i & 3) of unit i / 4 is stored at (i & 3) ^ ((unit >> 1) & 3).
+template <int QT>
+__device__ __forceinline__ uint32_t act_slot(uint32_t i) {
+  if constexpr (QT == QT_IQ3_S) return (i & ~3u) | ((i & 3u) ^ ((i >> 3) & 3u));
+  return i;
 }
 
 // 16-byte loads a lane keeps in flight: with 8 the Q8_0 kernels fit three CTAs on an SM (16 took 114 registers, two CTAs),
@@ -362,7 +372,7 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
       const uint64_t row = a.act_row ? a.act_row[start + t] : start + t;
       const int4 *src = (const int4 *)(a.act.q + row * a.act.q_stride);
       const float *sd = (const float *)((const uint8_t *)a.act.d + row * a.act.d_stride);
-      for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int4 *)dst)[i] = src[i];
+      for (uint32_t i = threadIdx.x; i < K / 16; i += 256) ((int4 *)dst)[act_slot<QT>(i)] = src[i];
       if (q8k) {
         const int16_t *sb = (const int16_t *)((const uint8_t *)a.act.bs + row * a.act.bs_stride);
         for (uint32_t i = threadIdx.x; i < K / 256; i += 256) ((float *)(dst + K))[i] = sd[i];
