@@ -194,6 +194,7 @@ struct Decoder;
 // Q8_0: w = d * q. A half is one block.
 template <>
 struct Decoder<QT_Q8_0> {
+  static constexpr uint32_t kStageBytes = 64;  // bytes of a row's main quants run a 64-value stage reads
   struct Hdr {};
   __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
   struct Raw {
@@ -231,6 +232,7 @@ struct Decoder<QT_Q8_0> {
 // block's d, dmin and scales are one 16-byte piece, loaded once for its four stages.
 template <>
 struct Decoder<QT_Q4_K> {
+  static constexpr uint32_t kStageBytes = 32;  // bytes of a row's main quants run a 64-value stage reads
   struct Hdr {
     uint4 v;  // d, dmin; then the 12 bytes of packed scales and minimums
   };
@@ -289,6 +291,7 @@ struct Decoder<QT_Q4_K> {
 // of 32 bytes of qh; a half is 32 bytes of ql with all 32 of qh, two groups of 16 with a scale each.
 template <>
 struct Decoder<QT_Q6_K> {
+  static constexpr uint32_t kStageBytes = 32;  // bytes of a row's main quants run a 64-value stage reads
   struct Hdr {};
   __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
   struct Raw {
@@ -335,6 +338,7 @@ struct Decoder<QT_Q6_K> {
 // signs, a nibble of scale. The codebook is in shared memory.
 template <>
 struct Decoder<QT_IQ3_S> {
+  static constexpr uint32_t kStageBytes = 16;  // bytes of a row's main quants run a 64-value stage reads
   struct Hdr {};
   __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
   struct Raw {
@@ -530,7 +534,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
       // Quants come from HBM the first time an expert is touched; a request for the L2 goes out kAhead stages before
       // the load into registers, which itself goes a stage before the decode.
-      constexpr uint32_t kAhead = 6;
+      constexpr uint32_t kLineStages = 128 / Dec::kStageBytes;
+      constexpr uint32_t kAhead = kLineStages > 6 ? kLineStages : 6 / kLineStages * kLineStages;  // a whole number of lines, about 6 stages
       Raw raw[2];
       typename Dec::Hdr hdr, hdr_next;  // the block's scales: fetched with its first stage's quants, used from that stage on
       auto fetch = [&](Raw &r, uint32_t k0) {
@@ -541,7 +546,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
 #else
           r = Dec::fetch(wm, nblk, K, r0 + m, k0, h);
           if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0);
-          if (k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, h));
+          // One request a 128-byte line: the line holds kLineStages stages of the row, and both halves' threads read it.
+          if (h == 0 && (k0 / kTileK) % kLineStages == 0 && k0 + kAhead * kTileK < K)
+            prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
 #endif
         }
       };
@@ -557,7 +564,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         TT(4, fence_async_smem(); __syncwarp(); if (lane == 0) mbar_arrive(full_bar(s)));
       };
       if (decodes)
-        for (uint32_t p = 1; p < kAhead && p < KT; p++) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, h));
+        for (uint32_t p = kLineStages; h == 0 && p < kAhead && p < KT; p += kLineStages)
+          prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, 0));
       TT(5, fetch(raw[0], 0));
       for (uint32_t it = 0; it < KT && ok; it += 2) {
         if (it + 1 < KT) TT(5, fetch(raw[1], (it + 1) * kTileK));
