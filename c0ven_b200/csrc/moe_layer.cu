@@ -353,7 +353,10 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
     else
       k_router_logits_rows<8><<<grid, 256, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
   } else {
-    k_router_pieces<<<dim3((NE + 127) / 128, (T + 127) / 128, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
+    if (router_rows_per_thread(T, NE, 2 * l->sms) == 6)
+      k_router_pieces<6><<<dim3((NE + 127) / 128, (T + 95) / 96, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
+    else
+      k_router_pieces<8><<<dim3((NE + 127) / 128, (T + 127) / 128, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
   }
   launched(l, cudaGetLastError(), "router logits");
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;

@@ -184,21 +184,23 @@ static __global__ void __launch_bounds__(256) k_router_logits_rows(const float *
   }
 }
 
-// Many rows: the product piece by piece. A CTA takes a 128 x 128 tile of (rows, experts) and one of the kRouterPieces
+// Many rows: the product piece by piece. A CTA takes a 128 x 128 (or 96 x 128) tile of (rows, experts) and one of the kRouterPieces
 // pieces of the hidden size, 8 x 8 outputs a thread, 16 values of the piece a step, each output one chain of fused
 // multiply-adds in index order; it leaves the piece's partial sums in P[piece][row][expert]. The top-k kernel adds a
 // row's pieces in order. Splitting by piece gives eight times the CTAs, which keeps every SM busy at a few thousand
 // rows, and frees the registers the running totals would take. The shared expert's gate logit does not come from
 // here: the activation quantiser sums it (k_quant_*'s gate argument).
+template <int RM>
 static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__restrict__ x, uint32_t T, uint32_t E,
                                                                 const float *__restrict__ W, uint32_t NE, float *__restrict__ P) {
-  constexpr int BM = 128, BN = 128, BK = 16, LD = BM + 4;
+  constexpr int BM = RM == 8 ? 128 : 96, BN = 128, BK = 16, LD = 128 + 4;
+  static_assert(RM == 8 || RM == 6, "tiles of 128 or 96 rows");
   __shared__ __align__(16) float As[2][BK][LD], Bs[2][BK][LD];
   const uint32_t tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
   const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, piece = E / kRouterPieces, kbeg = blockIdx.z * piece;
-  float acc[8][8];
+  float acc[RM][8];
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < RM; i++)
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
   // A thread's loads per step: two float4 of x and two of W, rows lr and the quarter lq of the step's 16 values and the
@@ -209,7 +211,7 @@ static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__
     const uint32_t r = m0 + lr, e = n0 + lr;
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-      ra[i] = r < T ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
+      ra[i] = (lr < BM && r < T) ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
       rb[i] = e < NE ? __ldg((const float4 *)(W + (uint64_t)e * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
     }
   };
@@ -230,11 +232,20 @@ static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__
     if (s + 1 < steps) fetch(kbeg + (s + 1) * BK);
 #pragma unroll
     for (int k = 0; k < BK; k++) {
-      const float4 a0 = *(const float4 *)&As[buf][k][ty * 4], a1 = *(const float4 *)&As[buf][k][64 + ty * 4];
+      // A thread's rows: ty * 4 .. + 3 and, past row 64, ty * 4 .. + 3 again (128-row tiles) or ty * 2, ty * 2 + 1 (96).
+      const float4 a0 = *(const float4 *)&As[buf][k][ty * 4];
+      float av[RM] = {a0.x, a0.y, a0.z, a0.w};
+      if constexpr (RM == 8) {
+        const float4 a1 = *(const float4 *)&As[buf][k][64 + ty * 4];
+        av[4] = a1.x, av[5] = a1.y, av[6] = a1.z, av[7] = a1.w;
+      } else {
+        const float2 a1 = *(const float2 *)&As[buf][k][64 + ty * 2];
+        av[4] = a1.x, av[5] = a1.y;
+      }
       const float4 b0 = *(const float4 *)&Bs[buf][k][tx * 4], b1 = *(const float4 *)&Bs[buf][k][64 + tx * 4];
-      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int i = 0; i < 8; i++)
+      for (int i = 0; i < RM; i++)
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
@@ -243,8 +254,8 @@ static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__
   }
   float *out = P + (uint64_t)blockIdx.z * T * NE;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const uint32_t t = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+  for (int i = 0; i < RM; i++) {
+    const uint32_t t = m0 + (i < 4 ? ty * 4 + i : 64 + ty * (RM - 4) + i - 4);
     if (t >= T) continue;
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -256,6 +267,19 @@ static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__
           if (e + j < NE) out[(uint64_t)t * NE + e + j] = acc[i][4 * h + j];
     }
   }
+}
+
+// Rows a thread of k_router_pieces takes (8: tiles of 128 rows, 6: of 96) for T rows on a GPU that holds `slots` of its
+// CTAs at once: the height whose whole waves cost less. 3,521 rows in tiles of 128 are 896 CTAs, three waves of 296 and
+// eight CTAs of a fourth; in tiles of 96, 1,184 CTAs, four waves three quarters as long.
+inline int router_rows_per_thread(uint32_t T, uint32_t NE, uint32_t slots) {
+  auto cost = [&](int rm) {
+    const uint64_t ctas = (uint64_t)((T + 16 * rm - 1) / (16 * rm)) * ((NE + 127) / 128) * kRouterPieces;
+    return ((ctas + slots - 1) / slots) * rm;
+  };
+  // A 96-row tile does 48 multiply-adds for the shared-memory loads that feed 64 in a 128-row tile: measured, a row
+  // costs it about a fifth more (3,521 rows: 0.257 -> 0.236 ms; 32,768 rows: 1.90 -> 2.03 ms when it was chosen there).
+  return cost(6) * 6 < cost(8) * 5 ? 6 : 8;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
