@@ -123,6 +123,11 @@ TRAFFIC = {("ragged3521_q4_k_zipf", 3521, "gate_up"): 444.7e6, ("ragged3521_q4_k
            ("decode1_q8_0", 32, "gate_up"): 554.2e6, ("decode1_q8_0", 32, "down"): 280.5e6, ("stack48_verify32_iq3_s", 32, "gate_up"): 220.6e6}
 
 
+def traffic_for(name: str, T: int, stage: str):
+    """The captured DRAM bytes per launch of a workload's dominant kernel, or None when there is no capture."""
+    return TRAFFIC.get((name, T, stage))
+
+
 def algorithmic(w: dict, T: int, experts_hit: int, world: int = 1) -> dict:
     """Bytes and flops one GPU's part of the layer needs for its T rows, with `experts_hit` distinct experts hit there.
     Expert parallel, the rows a GPU's experts compute are taken as its share, T * K, of all the rows."""
@@ -144,45 +149,59 @@ def cpu_step(layer, x, threads):
     return time.perf_counter() - t0
 
 
+def static_config(w: dict, args, world: int) -> dict:
+    """What names the workload, the same in both arms: nothing measured goes here."""
+    T_total, scaling = args.tokens or w["tokens"], w.get("scaling", "weak")
+    T = T_total if world == 1 or scaling == "weak" else max(1, T_total // world)
+    return dict(workload=w["name"], rows=world * T, rows_per_gpu=T, layers=args.layers or w.get("layers", 1), runs=w.get("runs"),
+                hidden=E, ffn=F, experts=NE, top_k=K, weights=synth.TYPE_NAMES[w["gate_type"]],
+                down_weights=synth.TYPE_NAMES[w.get("down_type") or w["gate_type"]], zipf_s=w.get("zipf_s", 0.0),
+                l2="flushed between timed steps")
+
+
+CPU_PASSES = 5  # passes the CPU path is timed over, after one warm pass, in both CPU legs; the median is reported
+
+
+def cpu_leg(layer, x_full, Tc):
+    """The CPU expert path (the oracle port) on the first Tc rows, every core the process may run on."""
+    from oracle import oracle
+
+    threads = oracle.host_threads()
+    x = np.ascontiguousarray(x_full[:Tc])
+    cpu_step(layer, x, threads)
+    dt = statistics.median([cpu_step(layer, x, threads) for _ in range(CPU_PASSES)])
+    return dict(value=Tc / dt, unit=UNIT, cores=threads, kind="port",
+                sample=f"first {Tc} of {x_full.shape[0]} rows a pass, median of {CPU_PASSES} passes after one warm pass"), dt
+
+
 def run_reference(args, w):
-    """The CPU expert path on the host's cores: the oracle port, every thread the process may use."""
+    """The CPU expert path on the host's cores: the oracle port, every core the process may run on."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle
-
     T_full = args.tokens or w["tokens"]
     T = min(T_full, args.cpu_tokens)
-    layer, x = build_layer(w), synth.make_input(T_full, E, seed=1)[:T]
-    threads = oracle.threads()
-    for _ in range(max(1, min(args.warmup, 2))):
-        cpu_step(layer, x, threads)
-    times = [cpu_step(layer, x, threads) for _ in range(args.steps)]
-    dt = statistics.median(times)
-    v = T / dt
-    sample = f"first {T} of {T_full} rows per step, median of {args.steps} steps"
+    layer, x = build_layer(w), synth.make_input(T_full, E, seed=1)
+    cpu, dt = cpu_leg(layer, x, T)
+    v = cpu["value"]
     print(json.dumps(dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
-                          ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="i8",
+                          ms_per_step=dt * 1e3, higher_is_better=True, scaling=w.get("scaling", "weak"), vs_baseline=None, dtype="i8",
                           data="synthetic", impl="reference",
-                          config=dict(workload=w["name"], rows=T_full, hidden=E, ffn=F, experts=NE, top_k=K,
-                                      weights=synth.TYPE_NAMES[w["gate_type"]]),
-                          cpu_baseline=dict(value=v, unit=UNIT, cores=threads, kind="port", sample=sample),
+                          config=static_config(w, args, int(os.environ.get("WORLD_SIZE", "1"))),
+                          cpu_baseline=cpu,
                           e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))))
 
 
-def run_gpu(args, w):
+MIN_TIMED_S = 0.5     # device time a reported figure is taken over, at least
+MAX_TIMED_STEPS = 2000
+
+
+def measure(args, w, steps, world, rank, local, dist, cpu=True):
+    """One workload on this process's GPU (and, with world > 1, its peers): the JSON line's fields, on rank 0."""
     import torch
 
     from c0ven_b200 import MoELayer, ep
 
-    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     T_total, nlayers = args.tokens or w["tokens"], args.layers or w.get("layers", 1)
     scaling = w.get("scaling", "weak")
     # Weak scaling: every rank brings the workload's rows. Strong: the workload's rows are shared out.
@@ -194,7 +213,7 @@ def run_gpu(args, w):
 
     # The layers of a stack share their experts' bytes on the host (each layer still has its own copy in HBM, so the
     # traffic is a stack's) and differ in their routers.
-    layers, moes, main_sp = [], [], None
+    layers, moes, stages, main_sp = [], [], [], None
     for i in range(nlayers):
         lw = base if i == 0 else dict(base, router=(np.random.default_rng(100 + i).standard_normal((NE, E)) * 0.02).astype(np.float32))
         if world == 1:
@@ -204,11 +223,11 @@ def run_gpu(args, w):
         else:
             st = ep.GpuStages(lw, rank, world, max_tokens=T, device=local, y_f16=True, profile=False,
                               tensor_min_rows=args.tensor_min, stream_ptr=main_sp)
-            layers.append(st.moe), moes.append(ep.ExpertParallelMoE(st))
+            stages.append(st), layers.append(st.moe), moes.append(ep.ExpertParallelMoE(st))
             main_sp = main_sp or st.moe.stream
     stream = torch.cuda.ExternalStream(main_sp, device=local)
     x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
-    res, xn = torch.empty_like(x_dev), torch.empty_like(x_dev)
+    res, xn = (torch.empty_like(x_dev), torch.empty_like(x_dev)) if nlayers > 1 else (None, None)
 
     def run_layer(i, xin, xout):
         if world == 1:
@@ -253,10 +272,29 @@ def run_gpu(args, w):
     def kernels():
         return sum(m.stats()["kernels"] for m in layers)
 
+    def agree(v, op):
+        """A number every rank then holds: the ranks' maximum (or whatever op says)."""
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        if dist:
+            dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def timed_step(i):
+        flush.fill_(i & 0xFF)  # L2 flush between timed iterations, outside the timed interval
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        step()
+        e.record(stream)
+        sync()
+        return s.elapsed_time(e)
+
     # Timed steps run as a caller would run them: no per-stage timing, the shared expert beside the routed ones, small
     # steps replayed from their recorded graph. The stages are timed afterwards, in a few more steps with the timing on.
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    # The `steps` steps asked for are timed first; if they hold less than MIN_TIMED_S of device time, more follow until
+    # they do, so that the figure and the clock record beside it rest on half a second of work. Every step is timed by
+    # its own pair of events; the figure is the median step, each step taken as its slowest rank.
+    MAX = torch.distributed.ReduceOp.MAX if dist else None
     with ClockSampler([local] if world == 1 else (list(range(world)) if rank == 0 else None)) as clocks:
         for _ in range(args.warmup):
             step()
@@ -264,29 +302,27 @@ def run_gpu(args, w):
         k0 = kernels()
         barrier()
         t_begin = time.time()
-        for i in range(args.steps):
-            flush.fill_(i & 0xFF)  # L2 flush between timed iterations, outside the timed interval
-            torch.cuda.synchronize()
-            starts[i].record(stream)
-            step()
-            ends[i].record(stream)
-            sync()
+        times = [timed_step(i) for i in range(steps)]
+        mean_ms = agree(sum(times) / len(times), MAX)
+        extra = int(min(MAX_TIMED_STEPS, max(0, MIN_TIMED_S * 1e3 / max(mean_ms, 1e-3) - steps)) + 0.999)
+        times += [timed_step(steps + i) for i in range(extra)]
         clocks.window(t_begin, time.time())
         barrier()
     launches = kernels() - k0
-    ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / args.steps
-    t = torch.tensor([ms], device="cuda")
+    tt = torch.tensor(times, device="cuda", dtype=torch.float64)
     if dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+        dist.all_reduce(tt, op=MAX)
+    ms = float(tt.median().item())
+    ms_asked = float(tt[:steps].mean().item())
 
-    for m, ex in zip(layers, moes):
+    for m in layers:
         m.set_profiling(True)
+    for ex in moes:
         if ex is not None:
             ex.st.shared_beside = False  # in line, so that its stage can be timed
     step()
     sync()
-    nprof = max(3, min(args.steps, 10))
+    nprof = max(3, min(steps, 10))
     stage = {k: 0.0 for k in _STAGES}
     for i in range(nprof):
         flush.fill_(i & 0xFF)
@@ -304,15 +340,16 @@ def run_gpu(args, w):
     for _ in range(2):
         step_host()
     barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
+    e2e_times = []
+    while len(e2e_times) < steps or (sum(e2e_times) < MIN_TIMED_S and len(e2e_times) < MAX_TIMED_STEPS):
+        t0 = time.perf_counter()
         step_host()
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / args.steps
-    t = torch.tensor([e2e_s], device="cuda")
-    if dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
+        torch.cuda.synchronize()
+        e2e_times.append(time.perf_counter() - t0)
+        if dist and len(e2e_times) >= steps:  # every rank stops after the same step
+            if agree(sum(e2e_times), torch.distributed.ReduceOp.MIN) >= MIN_TIMED_S:
+                break
+    e2e_s = agree(statistics.median(e2e_times), MAX)
 
     # Expert parallel: the rows each rank's experts ran in the last step (routing skew shows here: the busiest rank
     # bounds the step).
@@ -323,19 +360,18 @@ def run_gpu(args, w):
         dist.all_gather(all_rows, rows_t)
         ep_rows = [int(v.item()) for v in all_rows]
 
-    def teardown():
-        # Every rank waits for the others, then the process ends here, without the interpreter's teardown: the order in
-        # which that would drop the layers' streams, the collectives' and the allocator's blocks used on them is not
-        # ours to set, and a block freed after its stream has gone aborts the process.
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        sys.stdout.flush()
-        os._exit(0)
-
+    # The order things are dropped in: every tensor first (and the allocator's cached blocks with them, while the
+    # streams they were used on still exist), then the layers with their streams.
+    torch.cuda.synchronize()
+    del x_dev, out_dev, res, xn, flush, tt
+    moes.clear()
+    torch.cuda.empty_cache()
+    for st in stages:
+        st.close()
+    for m in layers:
+        m.close()
     if rank != 0:
-        teardown()
-        return
+        return None
     peaks = measured_peaks()
     hit = sum(s["last_experts_hit"] for s in stats)
     tensor_rows = sum(s["last_tensor_rows"] for s in stats)
@@ -353,36 +389,57 @@ def run_gpu(args, w):
     else:
         achieved = alg["bytes_" + dom] / (dom_ms * 1e-3) / 1e9
         roof = dict(bound="hbm", achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s", frac=achieved / peaks["hbm_gbs"])
-    roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=TRAFFIC.get((w["name"], T, dom)) if world == 1 else None)
-    cpu = None
-    if world == 1 and not args.no_cpu and nlayers == 1:
-        from oracle import oracle
-
-        Tc = min(T, args.cpu_tokens)
-        threads = oracle.threads()
-        xh = x_host.numpy()
-        cpu_step(base, xh[:Tc], threads)
-        dt = statistics.median([cpu_step(base, xh[:Tc], threads) for _ in range(3)])
-        cpu = dict(value=Tc / dt, unit=UNIT, cores=threads, kind="port", sample=f"first {Tc} of {T} rows, median of 3 passes")
+    roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=traffic_for(w["name"], T, dom) if world == 1 else None)
+    cpu_line = None
+    if world == 1 and cpu and not args.no_cpu and nlayers == 1:
+        cpu_line, _ = cpu_leg(base, x_host.numpy(), min(T, args.cpu_tokens))
     if world == 1:
         par = "1 GPU"
     else:
         par = (f"expert parallel x{world}: {NE // world} experts and {T} rows per GPU ({scaling} scaling), "
                "all-to-all of q8 rows out and f16 results back")
-    line = dict(metric=METRIC, value=world * T / (ms * 1e-3), unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
-                ms_per_step=ms, higher_is_better=True, scaling=scaling, vs_baseline=None,
-                dtype="f16" if tensor_rows > 0 else "i8", data="synthetic",
-                config=dict(workload=w["name"], rows=world * T, rows_per_gpu=T, layers=nlayers, runs=w.get("runs"), hidden=E, ffn=F,
-                            experts=NE, top_k=K, weights=synth.TYPE_NAMES[w["gate_type"]], zipf_s=w.get("zipf_s", 0.0),
-                            experts_hit=hit, tiles=sum(s["last_tiles"] for s in stats), parallelism=par, expert_rows_per_gpu=ep_rows,
-                            l2="flushed between timed steps"),
+    return dict(metric=METRIC, value=world * T / (ms * 1e-3), unit=UNIT, n_gpus=world, steps=steps, warmup=args.warmup,
+                ms_per_step=ms, timed_steps=len(times), ms_per_step_mean_of_steps=ms_asked, higher_is_better=True, scaling=scaling,
+                vs_baseline=None, dtype="f16" if tensor_rows > 0 else "i8", data="synthetic",
+                config=static_config(w, args, world),
+                run=dict(experts_hit=hit, tiles=sum(s["last_tiles"] for s in stats), parallelism=par, expert_rows_per_gpu=ep_rows,
+                         timing=f"median of {len(times)} steps, each between its own events ({steps} asked for; more until {MIN_TIMED_S} s is timed)"),
                 roofline=roof, stage_ms=stage, layer_bytes=alg["bytes_layer"], layer_flops=alg["flops_layer"],
-                cpu_baseline=cpu, clocks=clocks.summary(),
+                cpu_baseline=cpu_line, clocks=clocks.summary(),
                 e2e=dict(value=world * T / e2e_s, unit=UNIT, h2d_bytes_per_step=T * E * 4, d2h_bytes_per_step=T * E * 4,
-                         ms_per_step=e2e_s * 1e3),
+                         ms_per_step=e2e_s * 1e3, timed_steps=len(e2e_times)),
                 gpu_launches=launches)
-    print(json.dumps(line), flush=True)
-    teardown()
+
+
+DEFAULT_WORKLOAD = "prefill32768_q4_k"   # the largest configuration one GPU holds, and the one the targets are quoted on
+SECOND_WORKLOAD = "ragged3521_q4_k_zipf"  # reported beside it when the default runs on one GPU
+
+
+def run_gpu(args, w):
+    import torch
+
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import datetime
+
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
+    line = measure(args, w, args.steps, world, rank, local, dist)
+    if world == 1 and w["name"] == DEFAULT_WORKLOAD and not args.tokens and not args.layers and not args.no_second:
+        second = measure(args, workload(SECOND_WORKLOAD), args.steps, world, rank, local, dist)
+        line[SECOND_WORKLOAD] = {k: second[k] for k in ("value", "unit", "ms_per_step", "timed_steps", "config", "run", "roofline", "stage_ms",
+                                                         "cpu_baseline", "e2e", "gpu_launches", "dtype")}
+        line["gpu_launches"] += second["gpu_launches"]
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
@@ -391,9 +448,10 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="ragged3521_q4_k_zipf", choices=list(synth.CONFIGS))
-    ap.add_argument("--cpu-tokens", type=int, default=3521, help="rows of the batch the CPU baseline takes per pass")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(synth.CONFIGS))
+    ap.add_argument("--cpu-tokens", type=int, default=2048, help="rows of the batch the CPU baseline takes per pass")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-second", action="store_true", help="the default workload alone, without the ragged batch beside it")
     ap.add_argument("--layers", type=int, default=0, help="layers instead of the workload's")
     ap.add_argument("--tokens", type=int, default=0, help="rows instead of the workload's (the sweep's points)")
     ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
@@ -406,7 +464,6 @@ def main():
         run_reference(args, w)
     else:
         run_gpu(args, w)
-
 
 
 if __name__ == "__main__":

@@ -22,8 +22,6 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-DMOE_API_EXPORT", "-I" + os.path.join(ROOT, "include"),
           "-I" + os.path.join(ROOT, "build"), "-I" + CSRC, "-ccbin", "g++",
           "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unknown-pragmas"]
-# Extra flags for a diagnostic build, e.g. MOE_BUILD_FLAGS=-DMOE_TILE_TIMING (per-CTA cycle counts printed by the tile kernel).
-COMMON += os.environ.get("MOE_BUILD_FLAGS", "").split()
 
 
 def sources() -> list[str]:

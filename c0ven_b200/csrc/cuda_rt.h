@@ -1,4 +1,4 @@
-// The thin device layer under the MoE layer: one device's buffers, stream, events and pinned host memory, with every
+// The thin device layer under the MoE layer: one device's buffers, streams and events, with every
 // CUDA error turned into an exception the C ABI catches. It stands where the reference has core/ze (Runtime, List,
 // EventPool: core/ze/ze.h:50-217) and offers only what this path uses. Waits are polls against a deadline, never an
 // unbounded synchronise (the reference's list timeout, core/ze/ze.cpp:549-560).
@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <chrono>
 #include <cstdint>
 #include <stdexcept>
@@ -31,6 +32,24 @@ inline void cuda_check(cudaError_t e, const char *what, const char *file, int li
 }
 #define CUDA_OK(call) ::moe::cuda_check((call), #call, __FILE__, __LINE__)
 
+// What a launch helper needs to know about the device it launches on; the layer finds it once, at create.
+struct LaunchCtx {
+  int device = 0;
+  uint32_t sms = 148;
+};
+
+// A kernel's opt-in to more than 48 KB of dynamic shared memory holds per device: `done` has a bit per device ordinal
+// (one static word per kernel instantiation), so the attribute is set on a kernel's first launch on a device and not
+// again. Ordinals past 31 set it every time.
+template <class Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, size_t bytes, std::atomic<uint32_t> &done, int device) {
+  const uint32_t bit = device >= 0 && device < 32 ? 1u << device : 0u;
+  if (bit && (done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && bit) done.fetch_or(bit, std::memory_order_release);
+  return e;
+}
+
 // Device memory of n elements of T, freed with its owner.
 template <class T>
 class DeviceBuffer {
@@ -52,29 +71,6 @@ class DeviceBuffer {
   T *get() const { return p_; }
   size_t size() const { return n_; }
   size_t bytes() const { return n_ * sizeof(T); }
-
- private:
-  T *p_ = nullptr;
-  size_t n_ = 0;
-};
-
-// Pinned host memory.
-template <class T>
-class PinnedBuffer {
- public:
-  PinnedBuffer() = default;
-  PinnedBuffer(const PinnedBuffer &) = delete;
-  PinnedBuffer &operator=(const PinnedBuffer &) = delete;
-  ~PinnedBuffer() {
-    if (p_) cudaFreeHost(p_);
-  }
-  void alloc(size_t n) {
-    if (p_) cudaFreeHost(p_), p_ = nullptr;
-    if (n) CUDA_OK(cudaMallocHost((void **)&p_, n * sizeof(T)));
-    n_ = n;
-  }
-  T *get() const { return p_; }
-  size_t size() const { return n_; }
 
  private:
   T *p_ = nullptr;

@@ -42,7 +42,6 @@ struct ExpertRowsArgs {
   const MoeGroup *groups;   // null: dense_rows rows of slot 0, taken M at a time
   const uint32_t *ngroups;
   uint32_t dense_rows;
-  uint32_t n_min, n_max;    // of the groups, only those with n_min <= n <= n_max rows are this launch's (0, 0: all)
   uint32_t slabs;           // row slabs a CTA takes one after another (0 or 1: one); only with the row length known at compile time
   float *out;  // out[expert-order row][r]
   uint32_t out_stride;
@@ -63,6 +62,7 @@ __device__ __forceinline__ int dot4x4(const uint4 &w, const int4 &a) {
 
 // Bytes of one activation row in shared memory: codes, then the scales (padded to 16), then q8_K's sums.
 __host__ __device__ constexpr uint32_t act_d_bytes(bool q8k, uint32_t K) { return q8k ? ((K / 64 + 15) & ~15u) : K / 8; }
+constexpr uint32_t kRowsMaxK = 16384;  // the longest activation row the integer-dot kernels stage (8 rows of it fit an SM's shared memory)
 __host__ __device__ constexpr uint32_t act_row_stride(bool q8k, uint32_t K) { return K + act_d_bytes(q8k, K) + (q8k ? K / 8 : 0) + 16; }
 
 // SwiGLU as the CPU path states it (core/cpu/experts.cpp:21-27).
@@ -321,7 +321,6 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
     const MoeGroup g = a.groups[blockIdx.y];
     if (blockIdx.y >= ng) return;
     slot = g.slot, start = g.start, n = g.n;
-    if (a.n_max && (n < a.n_min || n > a.n_max)) return;
   } else {
     start = blockIdx.y * M;
     if (start >= a.dense_rows) return;

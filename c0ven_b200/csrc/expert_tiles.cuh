@@ -20,7 +20,6 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
-#include <cstdio>
 
 #include "expert_rows.cuh"
 #include "formats.h"
@@ -474,14 +473,6 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
-#ifdef MOE_TILE_TIMING
-  // Cycles this thread spent in each kind of wait or work; CTA 0 prints one thread of each role at the end.
-  long long tw[6] = {0, 0, 0, 0, 0, 0};
-  const long long t_begin = clock64();
-#define TT(i, stmt) { const long long t_ = clock64(); stmt; tw[i] += clock64() - t_; }
-#else
-#define TT(i, stmt) { stmt; }
-#endif
 
   // CTA b's item of round r: the items come sorted by size (full tiles first, then the others by falling row count), and
   // the rounds deal them boustrophedon (b, then G - 1 - b, ...), so that every CTA gets a like share of long and short
@@ -540,47 +531,42 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       typename Dec::Hdr hdr, hdr_next;  // the block's scales: fetched with its first stage's quants, used from that stage on
       auto fetch = [&](Raw &r, uint32_t k0) {
         if (decodes) {
-#ifdef MOE_TILE_FAKELOAD
-          r = Dec::fetch(wm, nblk, K, 0, 0, h);
-          if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, 0, 0);
-#else
           r = Dec::fetch(wm, nblk, K, r0 + m, k0, h);
           if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0);
           // One request a 128-byte line: the line holds kLineStages stages of the row, and both halves' threads read it.
           if (h == 0 && (k0 / kTileK) % kLineStages == 0 && k0 + kAhead * kTileK < K)
             prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
-#endif
         }
       };
       auto stage_step = [&](Raw &r, uint32_t it) {
         const uint32_t g = li * KT + it, s = g % S, use_s = g / S, k0 = it * kTileK;
-        if (use_s > 0) TT(0, ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error));
+        if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
         if (!ok) return;
         tc_fence_after();
         if (k0 % 256 == 0) hdr = hdr_next;
-#ifndef MOE_TILE_NODECODE
-        if (decodes) TT(1, Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid));
-#endif
-        TT(4, fence_async_smem(); __syncwarp(); if (lane == 0) mbar_arrive(full_bar(s)));
+        if (decodes) Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
       };
       if (decodes)
         for (uint32_t p = kLineStages; h == 0 && p < kAhead && p < KT; p += kLineStages)
           prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, 0));
-      TT(5, fetch(raw[0], 0));
+      fetch(raw[0], 0);
       for (uint32_t it = 0; it < KT && ok; it += 2) {
-        if (it + 1 < KT) TT(5, fetch(raw[1], (it + 1) * kTileK));
+        if (it + 1 < KT) fetch(raw[1], (it + 1) * kTileK);
         stage_step(raw[0], it);
         if (!ok || it + 1 >= KT) break;
-        if (it + 2 < KT) TT(5, fetch(raw[0], (it + 2) * kTileK));
+        if (it + 2 < KT) fetch(raw[0], (it + 2) * kTileK);
         stage_step(raw[1], it + 1);
       }
       if (is_wide(t.count)) {
         // Both buffers: the next item's MMAs wait for this epilogue, so these warps take four fifths of it.
-        if (ok) TT(2, ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error));
-        if (ok) TT(2, ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error));
+        if (ok) ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error);
+        if (ok) ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error);
         if (ok) {
           tc_fence_after();
-          TT(3, drain(t, r0, 0, kTileN, warp / 4, kDW / 4 + 1));
+          drain(t, r0, 0, kTileN, warp / 4, kDW / 4 + 1);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty_wide);
@@ -590,11 +576,6 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         use_inc(next_buf), next_buf ^= 1;
       }
     }
-#ifdef MOE_TILE_TIMING
-    if (blockIdx.x == 0 && tid == 0)
-      printf("decode warp: items %u total %lld | wait empty %lld, decode+store %lld, fence+arrive %lld, fetch %lld, wait acc %lld, epilogue %lld\n", li,
-             clock64() - t_begin, tw[0], tw[1], tw[4], tw[5], tw[2], tw[3]);
-#endif
   } else if (warp < kDW + kEW) {
     // Epilogue warps: warp w reads TMEM lanes 32 (w % 4) .., its quarter of the weight rows.
     uint32_t li = 0;
@@ -602,30 +583,27 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t r0 = (item % RT) * kTileM;
       if (is_wide(t.count)) {
-        if (ok) TT(2, ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error));
-        if (ok) TT(2, ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error));
+        if (ok) ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error);
+        if (ok) ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error);
         if (!ok) break;
         tc_fence_after();
-        TT(3, drain(t, r0, 0, kTileN, kDW / 4, kDW / 4 + 1));
+        drain(t, r0, 0, kTileN, kDW / 4, kDW / 4 + 1);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty(0)), mbar_arrive(acc_empty(1));
         use0++, use1++, wides++;
       } else {
         const uint32_t b = next_buf;
-        TT(2, ok = mbar_wait(acc_full(b), use_of(b) & 1, abort, a.error));
+        ok = mbar_wait(acc_full(b), use_of(b) & 1, abort, a.error);
         if (!ok) break;
         tc_fence_after();
-        TT(3, drain(t, r0, b * kTileN, b * kTileN + kTileN / 2, 0, 1));
+        drain(t, r0, b * kTileN, b * kTileN + kTileN / 2, 0, 1);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty(b));
         use_inc(b), next_buf ^= 1;
       }
     }
-#ifdef MOE_TILE_TIMING
-    if (blockIdx.x == 0 && lane == 0 && warp == kDW) printf("epilogue warp: items %u total %lld | wait acc %lld, epilogue %lld\n", li, clock64() - t_begin, tw[2], tw[3]);
-#endif
   } else if (warp == kCopyWarp) {
     // The copy thread: per stage, the 64 values of the tile's rows, 64 rows a copy, in the swizzled layout. A copy may
     // run past the tile's rows into the next expert's, or past the tensor (zeros): those columns of the result are dropped.
@@ -636,7 +614,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         const uint32_t nbox = (t.count + kTileBoxRows - 1) / kTileBoxRows;
         for (uint32_t it = 0; it < KT && ok; it++) {
           const uint32_t g = li * KT + it, s = g % S, use_s = g / S;
-          if (use_s > 0) TT(0, ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error));
+          if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
           if (!ok) break;
           const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + NMAT * SM::kWBytes;
           mbar_arrive_expect(full_bar(s), nbox * kTileBoxRows * kTileK * 2);
@@ -650,9 +628,6 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         while (clock64() - t0 < 400000) {
         }
       }
-#ifdef MOE_TILE_TIMING
-      if (blockIdx.x == 0) printf("copy thread: total %lld | wait empty %lld\n", clock64() - t_begin, tw[0]);
-#endif
     }
   } else if (lane == 0) {
     // The MMA thread: per stage, four K steps of 16 for each matrix; the commit frees the stage when they are done.
@@ -665,13 +640,13 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       const uint32_t b = next_buf, colg = wide ? 0 : b * kTileN, colu = wide ? kTileN : colg + kTileN / 2;
       // The buffers this item writes must have been read: by the epilogue warps, and after a two-buffer item by the
       // decode warps too.
-      if (after_wide) TT(1, ok = mbar_wait(acc_empty_wide, (wides - 1) & 1, abort, a.error));
+      if (after_wide) ok = mbar_wait(acc_empty_wide, (wides - 1) & 1, abort, a.error);
       after_wide = false;
       for (uint32_t bb = 0; bb < 2 && ok; bb++)
-        if ((wide || bb == b) && use_of(bb) > 0) TT(1, ok = mbar_wait(acc_empty(bb), (use_of(bb) - 1) & 1, abort, a.error));
+        if ((wide || bb == b) && use_of(bb) > 0) ok = mbar_wait(acc_empty(bb), (use_of(bb) - 1) & 1, abort, a.error);
       for (uint32_t it = 0; it < KT && ok; it++) {
         const uint32_t g = li * KT + it, s = g % S;
-        TT(0, ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error));
+        ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error);
         if (!ok) break;
         tc_fence_after();
         const uint32_t stage = smem_u32(smem + s * SM::kStageBytes), xt = stage + NMAT * SM::kWBytes;
@@ -692,9 +667,6 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         use_inc(b), next_buf ^= 1;
       }
     }
-#ifdef MOE_TILE_TIMING
-    if (blockIdx.x == 0) printf("mma thread: items %u total %lld | wait full %lld, wait accumulators free %lld\n", li, clock64() - t_begin, tw[0], tw[1]);
-#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -706,7 +678,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
 }
 
 // act_map: the activation rows, f16 [rows][a.K] in the order of the tiles (tensor_map.h).
+struct LaunchCtx;
 template <int QT, int NMAT>
-cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, const CUtensorMap &act_map, uint32_t max_tiles, const uint32_t *grid_global, cudaStream_t st);
+cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, const CUtensorMap &act_map, uint32_t max_tiles, const uint32_t *grid_global,
+                                const LaunchCtx &ctx, cudaStream_t st);
 
 }  // namespace moe

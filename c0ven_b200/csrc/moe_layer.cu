@@ -5,6 +5,7 @@
 // (core/cpu/experts.cpp:152-284).
 #include <algorithm>
 #include <cstring>
+#include <initializer_list>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -23,13 +24,13 @@
 namespace moe {
 
 template <int QT, int NMAT>
-cudaError_t launch_expert_rows(const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid_global, cudaStream_t st);
+cudaError_t launch_expert_rows(const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid_global, const LaunchCtx &ctx, cudaStream_t st);
 
 static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, int M, uint32_t max_groups, const uint32_t *grid,
-                               cudaStream_t st) {
+                               const LaunchCtx &ctx, cudaStream_t st) {
 #define ROWS_CASE(T)                                                                                            \
   case T:                                                                                                       \
-    return nmat == 2 ? launch_expert_rows<T, 2>(a, M, max_groups, grid, st) : launch_expert_rows<T, 1>(a, M, max_groups, grid, st);
+    return nmat == 2 ? launch_expert_rows<T, 2>(a, M, max_groups, grid, ctx, st) : launch_expert_rows<T, 1>(a, M, max_groups, grid, ctx, st);
   switch (qt) {
     ROWS_CASE(QT_Q8_0)
     ROWS_CASE(QT_Q4_K)
@@ -41,10 +42,10 @@ static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, i
 }
 
 static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a, const CUtensorMap &map, uint32_t max_tiles, const uint32_t *grid,
-                                cudaStream_t st) {
+                                const LaunchCtx &ctx, cudaStream_t st) {
 #define TILES_CASE(T)                                                                                  \
   case T:                                                                                              \
-    return nmat == 2 ? launch_expert_tiles<T, 2>(a, map, max_tiles, grid, st) : launch_expert_tiles<T, 1>(a, map, max_tiles, grid, st);
+    return nmat == 2 ? launch_expert_tiles<T, 2>(a, map, max_tiles, grid, ctx, st) : launch_expert_tiles<T, 1>(a, map, max_tiles, grid, ctx, st);
   switch (qt) {
     TILES_CASE(QT_Q8_0)
     TILES_CASE(QT_Q4_K)
@@ -121,6 +122,7 @@ struct moe_layer {
   uint64_t Rmax = 0;  // expert rows a call may bring: max_tokens * n_used, or max_expert_rows
   bool has_shared = false, profile = false, can_tensor = false;
   uint32_t sms = 148;  // the device's SM count
+  LaunchCtx ctx;
   std::unique_ptr<Stream> stream, aux;  // aux: the shared expert runs beside the routed ones
   std::unique_ptr<Event> fork_ev, join_ev;
   // Steps of few rows are bound by launches, not work: the whole call is recorded once per (rows, buffers, stream)
@@ -185,8 +187,8 @@ void upload_matrix(DeviceBuffer<uint8_t> &dst, uint32_t type, const void *src, u
 
 void check_config(const moe_layer_config &c, const moe_layer_weights &w) {
   auto bad = [](const std::string &m) { throw BadArgument(m); };
-  if (c.n_embd == 0 || c.n_embd % 256) bad("n_embd must be a multiple of 256");
-  if (c.n_ff == 0 || c.n_ff % 256) bad("n_ff must be a multiple of 256");
+  if (c.n_embd == 0 || c.n_embd % 256 || c.n_embd > kRowsMaxK) bad("n_embd must be a multiple of 256, at most 16384");
+  if (c.n_ff == 0 || c.n_ff % 256 || c.n_ff > kRowsMaxK) bad("n_ff must be a multiple of 256, at most 16384");
   if (c.n_experts == 0 || c.n_experts % 32 || c.n_experts > 512) bad("n_experts must be a multiple of 32, at most 512");
   if (c.n_used == 0 || c.n_used > 16 || c.n_used > c.n_experts) bad("n_used must be 1 .. 16 and at most n_experts");
   if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K or IQ3_S");
@@ -215,6 +217,7 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
     int n = 0;
     CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, c.device));
     l->sms = n > 0 ? (uint32_t)n : 148;
+    l->ctx = LaunchCtx{c.device, l->sms};
   }
   l->can_tensor = !(c.flags & MOE_FLAG_NO_TENSOR) && c.n_embd % kTileK == 0 && c.n_ff % kTileM == 0;
   l->stream = std::make_unique<Stream>();
@@ -227,6 +230,15 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->Rmax = c.max_expert_rows ? c.max_expert_rows : A;
   if (l->Rmax < A && !ep) l->Rmax = A;
   const uint64_t R = l->Rmax;
+  {
+    // The integer-dot kernels take one group per index of their grid's second extent, 65,535 at most: a layer whose
+    // largest call could list more groups than that is refused here, not in the middle of a step.
+    const uint32_t tm = !l->can_tensor ? 0 : c.tensor_min_rows ? c.tensor_min_rows : 16;
+    const uint64_t routed = tm ? std::min<uint64_t>(R, (uint64_t)l->local * ((tm > 1 ? tm - 2 : 0) / kGroupMax + 1)) : std::min<uint64_t>(R, R / kGroupMax + l->local);
+    const uint64_t dense = l->has_shared && (!l->can_tensor || tm > T) ? ((uint64_t)T + 7) / 8 : 0;
+    if (routed > 65535 || dense > 65535)
+      throw BadArgument("max_tokens (or max_expert_rows) is too large for the integer-dot kernels' grid: lower it, or leave the tensor-core kernels on");
+  }
 
   // The router's rows, then the shared expert's gate vector as row NE (zeros without one).
   std::vector<float> rw((size_t)l->N * E, 0.0f);
@@ -411,7 +423,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
-    launched(l, launch_tiles(c.gate_type, 2, a, l->xg_map, max_big, l->grid.get(), st), "experts gate/up tiles");
+    launched(l, launch_tiles(c.gate_type, 2, a, l->xg_map, max_big, l->grid.get(), l->ctx, st), "experts gate/up tiles");
   }
   if (max_groups) {
     ExpertRowsArgs a{};
@@ -419,7 +431,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.act = src.view, a.act_row = src.act_row;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit;
-    launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), st), "experts gate/up");
+    launched(l, launch_rows(c.gate_type, 2, a, M, max_groups, l->grid.get(), l->ctx, st), "experts gate/up");
   }
   mark(l, ST_DOWN, st);  // the down stage starts with its input's quantiser
   quantize_rows(l, l->h.get(), R, F, l->hq_routed, st);
@@ -428,7 +440,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = y, a.out_stride = E, a.error = l->error.get();
-    launched(l, launch_tiles(c.down_type, 1, a, l->hq_routed.h_map, max_big, l->grid.get(), st), "experts down tiles");
+    launched(l, launch_tiles(c.down_type, 1, a, l->hq_routed.h_map, max_big, l->grid.get(), l->ctx, st), "experts down tiles");
   }
   if (max_groups) {
     ExpertRowsArgs a{};
@@ -436,7 +448,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.act = l->hq_routed.view(), a.act_row = nullptr;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
     a.out = y, a.out_stride = E;
-    launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), st), "experts down");
+    launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), l->ctx, st), "experts down");
   }
 }
 
@@ -453,12 +465,12 @@ void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
     ExpertTilesArgs a{};
     a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.dense_rows = T;
     a.out = hs, a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
-    launched(l, launch_tiles(c.shexp_gate_type, 2, a, xs.h_map, dense_tiles, l->grid.get(), st), "shared gate/up tiles");
+    launched(l, launch_tiles(c.shexp_gate_type, 2, a, xs.h_map, dense_tiles, l->grid.get(), l->ctx, st), "shared gate/up tiles");
     quantize_rows(l, hs, T, F, l->hq_shared, st);
     ExpertTilesArgs b{};
     b.w0 = l->sd.get(), b.K = F, b.R = E, b.dense_rows = T;
     b.out = l->s.get(), b.out_stride = E, b.error = l->error.get();
-    launched(l, launch_tiles(c.shexp_down_type, 1, b, l->hq_shared.h_map, dense_tiles, l->grid.get(), st), "shared down tiles");
+    launched(l, launch_tiles(c.shexp_down_type, 1, b, l->hq_shared.h_map, dense_tiles, l->grid.get(), l->ctx, st), "shared down tiles");
     l->shared_on_tensor = true;
     return;
   }
@@ -468,12 +480,12 @@ void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
   ExpertRowsArgs a{};
   a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.rows_per_cta = 32;
   a.act = xs.view(), a.dense_rows = T, a.out = hs, a.out_stride = F, a.limit = c.swiglu_limit;
-  launched(l, launch_rows(c.shexp_gate_type, 2, a, M, dense_groups, l->grid.get(), st), "shared gate/up");
+  launched(l, launch_rows(c.shexp_gate_type, 2, a, M, dense_groups, l->grid.get(), l->ctx, st), "shared gate/up");
   quantize_rows(l, hs, T, F, l->hq_shared, st);
   ExpertRowsArgs b{};
   b.w0 = l->sd.get(), b.K = F, b.R = E, b.rows_per_cta = 128;
   b.act = l->hq_shared.view(), b.dense_rows = T, b.out = l->s.get(), b.out_stride = E;
-  launched(l, launch_rows(c.shexp_down_type, 1, b, M, dense_groups, l->grid.get(), st), "shared down");
+  launched(l, launch_rows(c.shexp_down_type, 1, b, M, dense_groups, l->grid.get(), l->ctx, st), "shared down");
 }
 
 template <class Y>
@@ -576,6 +588,13 @@ void read_counters(moe_layer *l) {
   l->stats.last_tensor_rows = c[5] + (l->shared_on_tensor ? l->last_T : 0);
 }
 
+// The kernels read rows through 16-byte loads: a device pointer that is not 16-byte aligned is refused here, where the
+// answer is a status, rather than found by a kernel, where it is a fault.
+void need_aligned16(std::initializer_list<const void *> ps) {
+  for (const void *p : ps)
+    if ((uintptr_t)p & 15) throw BadArgument("device pointers must be 16-byte aligned");
+}
+
 template <class Fn>
 moe_status guarded(moe_layer *l, Fn &&fn) {
   try {
@@ -643,6 +662,7 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
   std::lock_guard<std::mutex> lk(l->mu);
   return guarded(l, [&] {
     if (!x_dev || !out_dev || T == 0 || T > l->Tmax) throw BadArgument("x and out are required, and 1 <= T <= max_tokens");
+    need_aligned16({x_dev, out_dev});
     cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
     forward_step(l, x_dev, T, out_dev, st);
     if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
@@ -657,6 +677,7 @@ MOE_API moe_status moe_layer_route_device(moe_layer *l, const float *x_dev, uint
   std::lock_guard<std::mutex> lk(l->mu);
   return guarded(l, [&] {
     if (!x_dev || T == 0 || T > l->Tmax) throw BadArgument("x is required, and 1 <= T <= max_tokens");
+    need_aligned16({x_dev});
     stage_route(l, x_dev, T, stream ? (cudaStream_t)stream : l->stream->get());
     l->stats.calls++, l->stats.rows += T, l->stats.assignments += (uint64_t)T * l->K;
   });
@@ -698,6 +719,7 @@ MOE_API moe_status moe_layer_gather_rows_device(moe_layer *l, void *rows_dev, in
   std::lock_guard<std::mutex> lk(l->mu);
   return guarded(l, [&] {
     if (!rows_dev || !ids_dev || l->last_T == 0) throw BadArgument("rows and ids are required, after moe_layer_route_device");
+    need_aligned16({rows_dev});
     cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
     const uint32_t A = l->last_T * l->K;
     k_gather_wire<<<(A + 7) / 8, 256, 0, st>>>(l->xq_routed.view(), l->E, l->xq_routed.q8k, l->pack.row_src.get(), l->pack.inv.get(),
@@ -715,6 +737,7 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
     if (R > l->Rmax) throw BadArgument("more rows than max_expert_rows");
     if (R == 0) return;
     if (!rows_dev || !ids_dev || !y_dev) throw BadArgument("rows, ids and y are required");
+    need_aligned16({rows_dev, y_dev});
     cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
     const uint32_t E = l->E, nexp = l->local;
     const bool q8k = l->xq_routed.q8k;
@@ -763,6 +786,7 @@ MOE_API moe_status moe_layer_combine_device(moe_layer *l, const void *y_dev, uin
   std::lock_guard<std::mutex> lk(l->mu);
   return guarded(l, [&] {
     if (!y_dev || !out_dev || l->last_T == 0) throw BadArgument("y and out are required, after moe_layer_route_device");
+    need_aligned16({y_dev, out_dev});
     cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
     if (y_f16)
       stage_combine<__half>(l, (const __half *)y_dev, l->last_T, out_dev, st);
@@ -802,6 +826,37 @@ MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, ui
     }
     if (ntiles) *ntiles = counters[0];
     read_counters(l);
+  });
+}
+
+MOE_API moe_status moe_layer_read_groups(moe_layer *l, moe_group *groups, uint32_t cap, uint32_t *ngroups) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T == 0) throw BadArgument("no call has run yet");
+    static_assert(sizeof(moe_group) == sizeof(MoeGroup), "group layout");
+    l->stream->wait(0);
+    uint32_t counters[8];
+    CUDA_OK(cudaMemcpy(counters, l->pack.counters.get(), sizeof(counters), cudaMemcpyDeviceToHost));
+    if (groups && cap)
+      CUDA_OK(cudaMemcpy(groups, l->pack.groups.get(), std::min<size_t>(cap, counters[1]) * sizeof(moe_group), cudaMemcpyDeviceToHost));
+    if (ngroups) *ngroups = counters[1];
+  });
+}
+
+MOE_API moe_status moe_layer_read_quantized(moe_layer *l, uint32_t which, int8_t *codes, float *scales, int16_t *sums, uint32_t *is_q8k) {
+  if (!l || which > 1) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T == 0) throw BadArgument("no call has run yet");
+    if (which == 1 && l->local != l->NE) throw BadArgument("an expert-parallel layer's inner rows are those of the rows it received");
+    l->stream->wait(0);
+    const ActBuffers &b = which == 0 ? l->xq_routed : l->hq_routed;
+    const uint64_t rows = which == 0 ? l->last_T : (uint64_t)l->last_T * l->K;
+    if (codes) CUDA_OK(cudaMemcpy(codes, b.q.get(), rows * b.K, cudaMemcpyDeviceToHost));
+    if (scales) CUDA_OK(cudaMemcpy(scales, b.d.get(), rows * (b.q8k ? b.K / 256 : b.K / 32) * sizeof(float), cudaMemcpyDeviceToHost));
+    if (sums && b.q8k) CUDA_OK(cudaMemcpy(sums, b.bs.get(), rows * (b.K / 16) * sizeof(int16_t), cudaMemcpyDeviceToHost));
+    if (is_q8k) *is_q8k = b.q8k;
   });
 }
 
@@ -867,11 +922,13 @@ MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap) {
       ROW(moe_layer_stats, calls), ROW(moe_layer_stats, rows), ROW(moe_layer_stats, assignments), ROW(moe_layer_stats, kernels),
       ROW(moe_layer_stats, h2d_bytes), ROW(moe_layer_stats, d2h_bytes), ROW(moe_layer_stats, last_tiles),
       ROW(moe_layer_stats, last_experts_hit), ROW(moe_layer_stats, last_tensor_rows),
+      ROW(moe_group, slot), ROW(moe_group, start), ROW(moe_group, n),
       ROW(moe_abi_row, name), ROW(moe_abi_row, offset), ROW(moe_abi_row, size),
 #undef ROW
       {"moe_layer_config", 0, (uint32_t)sizeof(moe_layer_config)},
       {"moe_layer_weights", 0, (uint32_t)sizeof(moe_layer_weights)},
       {"moe_tile", 0, (uint32_t)sizeof(moe_tile)},
+      {"moe_group", 0, (uint32_t)sizeof(moe_group)},
       {"moe_layer_stats", 0, (uint32_t)sizeof(moe_layer_stats)},
       {"moe_abi_row", 0, (uint32_t)sizeof(moe_abi_row)},
   };

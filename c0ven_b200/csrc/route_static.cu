@@ -61,6 +61,8 @@ MOE_API moe_status moe_route_rows_static(const float *x_dev, uint32_t T, uint32_
                                          const float *bias_dev, uint32_t n_experts, uint32_t n_used, int32_t *ids_dev,
                                          float *w_dev, float *gate_dev, void *stream) {
   if (!x_dev || !router_dev || !ids_dev || !w_dev || !gate_dev) return fail(MOE_BAD_ARGUMENT, "x, router, ids, w and gate are required");
+  if (((uintptr_t)x_dev | (uintptr_t)router_dev) & 15)
+    return fail(MOE_BAD_ARGUMENT, "x and router must be 16-byte aligned: the kernels read them through 16-byte loads");
   if (T == 0 || T > kStaticRows)
     return fail(MOE_BAD_ARGUMENT, "rows must be 1 .. " + std::to_string(kStaticRows) + ": the static scratch holds no more");
   if (n_experts == 0 || n_experts % 32 || n_experts > kStaticExperts)

@@ -63,6 +63,7 @@ class GpuStages:
         self._sp = stream_ptr
         self.stream = torch.cuda.ExternalStream(stream_ptr or self.moe.stream, device=self.device)
         self.wire = self.moe.wire_row_bytes
+        self.max_expert_rows = max_expert_rows or max_tokens * layer["n_used"] * world
         self._bufs = {}
         # The shared expert needs no other GPU: it runs on a stream of its own beside the exchanges and the experts.
         self.side = torch.cuda.Stream(device=self.device)
@@ -146,7 +147,12 @@ class ExpertParallelMoE:
         self.sent_rows = self.received_rows = self.expert_rows = 0  # of the last step: rows sent to and received from other ranks; rows its experts ran
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """A stage that fails on one rank (a bad argument, a timeout, a launch error) must not leave the others waiting
+        in a collective: what can be known on every rank (a rank receiving more rows than it has room for) is checked
+        on every rank from the gathered counts, before any row moves; any other failure is held until the step's
+        collectives have all been entered with the sizes agreed, and raised then."""
         st, W = self.st, self.world
+        held = None
         with torch.cuda.stream(st.stream) if hasattr(st, "stream") else _null():
             cnt = st.route(x)
             if hasattr(st, "shared_start"):
@@ -155,17 +161,36 @@ class ExpertParallelMoE:
             dist.all_gather_into_tensor(cnt_all, cnt, group=self.group)
             counts = cnt_all.cpu().numpy().reshape(W, -1)      # the step's one wait on the host
             send, recv = split_sizes(counts, self.rank)
-            rows = st.gather()                                 # [A][wire] in expert order = destination order
+            most = getattr(st, "max_expert_rows", 0)
+            if most:
+                per = counts.shape[1] // W
+                by_owner = counts.reshape(W, W, per).sum(-1).sum(0)  # rows every rank receives: the same sum on every rank
+                if int(by_owner.max()) > most:
+                    raise RuntimeError(f"rank {int(by_owner.argmax())} would receive {int(by_owner.max())} rows, more than max_expert_rows "
+                                       f"{most}: every rank stops here, before the exchange")
             R = sum(recv)
+            try:
+                rows = st.gather()                             # [A][wire] in expert order = destination order
+            except Exception as e:  # noqa: BLE001
+                held, rows = e, st.empty((sum(send), st.wire), torch.uint8, "rows")
             rows_in = st.empty((R, rows.shape[1]), rows.dtype, "rows_in")
             dist.all_to_all_single(rows_in, rows, recv, send, group=self.group)
-            if hasattr(st, "ids_from_counts"):
-                ids_in = st.ids_from_counts(cnt_all, W, R)
-            else:
-                ids_in = st.to_device(received_ids(counts, self.rank))
-            y_in = st.experts(rows_in, ids_in)                 # [R][E] in arrival order
+            y_in = None
+            if held is None:
+                try:
+                    if hasattr(st, "ids_from_counts"):
+                        ids_in = st.ids_from_counts(cnt_all, W, R)
+                    else:
+                        ids_in = st.to_device(received_ids(counts, self.rank))
+                    y_in = st.experts(rows_in, ids_in)         # [R][E] in arrival order
+                except Exception as e:  # noqa: BLE001
+                    held = e
+            if y_in is None:
+                y_in = st.empty((R, x.shape[1]), getattr(st, "y_dtype", torch.float32), "y_in")
             y = st.empty((rows.shape[0], y_in.shape[1]), y_in.dtype, "y")
             dist.all_to_all_single(y, y_in, send, recv, group=self.group)
+            if held is not None:
+                raise held
             if hasattr(st, "shared_finish"):
                 st.shared_finish()
             else:

@@ -103,6 +103,26 @@ class MoELayer:
         self._check(_lib.lib().moe_layer_read_route(self._h, _ptr(ids), _ptr(w), _ptr(inv), _ptr(tiles), cap, C.byref(n)))
         return ids, w, inv, tiles[:n.value].copy()
 
+    def groups(self) -> np.ndarray:
+        """The last call's groups for the integer-dot kernels, [n][3] (slot, start, n), in expert order."""
+        n = C.c_uint32(0)
+        self._check(_lib.lib().moe_layer_read_groups(self._h, None, 0, C.byref(n)))
+        g = np.empty((max(n.value, 1), 3), dtype=np.uint32)
+        self._check(_lib.lib().moe_layer_read_groups(self._h, _ptr(g), n.value, C.byref(n)))
+        return g[:n.value].copy()
+
+    def quantized(self, T: int, inner: bool = False):
+        """The last call's quantised rows: codes [rows][K] int8, scales [rows][K/32 or K/256] f32, and for q8_K the
+        int16 sums [rows][K/16] (else None). inner: the routed experts' h rows in expert order instead of x."""
+        rows, Kv = (T * self.n_used, self.n_ff) if inner else (T, self.n_embd)
+        k = C.c_uint32(0)
+        self._check(_lib.lib().moe_layer_read_quantized(self._h, int(inner), None, None, None, C.byref(k)))
+        q = np.empty((rows, Kv), dtype=np.int8)
+        d = np.empty((rows, Kv // (256 if k.value else 32)), dtype=np.float32)
+        bs = np.empty((rows, Kv // 16), dtype=np.int16) if k.value else None
+        self._check(_lib.lib().moe_layer_read_quantized(self._h, int(inner), _ptr(q), _ptr(d), _ptr(bs), C.byref(k)))
+        return q, d, bs
+
     # Expert parallel, stage by stage (device addresses; queued on `stream`, the layer's own when None).
     def route_device(self, x_ptr: int, T: int, stream=None):
         self._check(_lib.lib().moe_layer_route_device(self._h, x_ptr, T, stream))

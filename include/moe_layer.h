@@ -116,7 +116,9 @@ MOE_API void moe_layer_destroy(moe_layer *l);
 MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, float *out);
 
 /* The same on DEVICE buffers, queued on the layer's stream (or on stream, a cudaStream_t, when not null); returns
- * without waiting. */
+ * without waiting. Every device pointer of rows this header takes (x, out, y, rows) must be 16-byte aligned, as whole
+ * allocations are: the kernels read rows through 16-byte loads, and a pointer that is not is refused with
+ * MOE_BAD_ARGUMENT. */
 MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, uint32_t T, float *out_dev, void *stream);
 
 /* Expert parallel: a layer created with fewer than n_experts experts runs stage by stage, and the caller moves rows
@@ -156,6 +158,25 @@ MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms);
 MOE_API moe_status moe_layer_read_route(moe_layer *l, int32_t *ids, float *w, uint32_t *inv, moe_tile *tiles,
                                         uint32_t tiles_cap, uint32_t *ntiles);
 
+/* The last call's groups for the integer-dot kernels (the reference's MoeGroup, shared/moe_tile.h:20-33, as a range:
+ * its assignments are rows start .. start + n of the expert order, which lists an expert's assignments in ascending
+ * order, so a group holds what core/tests/step_rows_test.cpp:40-58 puts in it; the list is in expert order, not in
+ * order of first assignment). Up to cap of them; *ngroups, how many there are. Waits for the stream. */
+typedef struct {
+  uint32_t slot;
+  uint32_t start;
+  uint32_t n; /* 1 .. 8 */
+} moe_group;
+MOE_API moe_status moe_layer_read_groups(moe_layer *l, moe_group *groups, uint32_t cap, uint32_t *ngroups);
+
+/* The last call's quantised activations, as the expert kernels read them (the a8 rows of kernels/include/a8.h:9-16;
+ * here in the CPU path's own q8_0 / q8_K forms, docs/spec/QUANT_FORMATS.md:463-465,528-535). which 0: the step's rows
+ * x, [T][n_embd]; which 1: the routed experts' inner rows h in expert order, [T * n_used][n_ff]. codes: one int8 a
+ * value; scales: one float per 32 values (q8_0, the f16 scale widened) or per 256 (q8_K); sums: q8_K's int16 sums of
+ * each 16 codes, untouched for q8_0. *is_q8k says which form. Any pointer may be null. Waits for the stream. */
+MOE_API moe_status moe_layer_read_quantized(moe_layer *l, uint32_t which, int8_t *codes, float *scales, int16_t *sums,
+                                            uint32_t *is_q8k);
+
 MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out);
 /* With MOE_FLAG_PROFILE: the last call's time in each stage, milliseconds, MOE_STAGES floats. Waits for the stream. */
 MOE_API moe_status moe_layer_stage_ms(moe_layer *l, float *ms);
@@ -176,8 +197,8 @@ MOE_API const char *moe_last_error(const moe_layer *l);
  * most 512 and n_embd at most 4096; more is refused with MOE_BAD_ARGUMENT.
  *   x_dev [T][n_embd] f32; router_dev [n_experts + 1][n_embd] f32, the router's rows and then the shared expert's gate
  *   vector (zeros if there is none); bias_dev [n_experts] or null; out: ids_dev, w_dev [T][n_used] in rank order,
- *   gate_dev [T] = sigmoid(gate . x). All DEVICE pointers of the current device, the caller's; queued on stream (a
- *   cudaStream_t; null: the default stream) without waiting.
+ *   gate_dev [T] = sigmoid(gate . x). All DEVICE pointers of the current device, the caller's (x_dev and router_dev
+ *   16-byte aligned); queued on stream (a cudaStream_t; null: the default stream) without waiting.
  * The first call on a device looks up the array's device address and sets one kernel attribute: make that call before
  * any stream capture begins. All calls share the one array: two calls whose kernels may overlap on a GPU (different
  * streams, no ordering between them) race on it; order them. Nothing in it needs clearing between calls.

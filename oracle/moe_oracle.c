@@ -36,6 +36,16 @@ int orc_threads(void) {
 #endif
 }
 
+/* The threads every later parallel loop takes. The reference sizes its pool from the cores the process may run on
+ * (docs/DESIGN.md:694-696), not from an environment variable: the caller counts them and says so here. */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* shared/quant.h:36-75 */
 uint32_t orc_block_values(uint32_t t) {
   switch (t) {

@@ -99,6 +99,7 @@ void orc_moe_forward(const orc_layer *L, const float *x, uint32_t T, float *out,
                      uint32_t *inv, orc_tile *tiles, uint32_t *ntiles, int threads);
 
 int orc_threads(void);
+void orc_set_threads(int n);
 
 #ifdef __cplusplus
 }

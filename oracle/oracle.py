@@ -78,6 +78,8 @@ def lib():
         L.orc_moe_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         L.orc_threads.restype = C.c_int
+        L.orc_set_threads.argtypes = [C.c_int]
+        L.orc_set_threads.restype = None
         _lib = L
     return _lib
 
@@ -91,6 +93,14 @@ def block_bytes(t): return lib().orc_block_bytes(t)
 def vec_dot_type(t): return lib().orc_vec_dot_type(t)
 def row_bytes(t, n): return lib().orc_row_bytes(t, n)
 def threads(): return lib().orc_threads()
+
+
+def host_threads() -> int:
+    """The cores this process may run on (the reference's rule for sizing its pool, docs/DESIGN.md:694-696), set as
+    the oracle's thread count whatever OMP_NUM_THREADS says (launchers such as torchrun set it to 1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_threads(n)
+    return n
 
 
 def dequantize(t: int, blocks: np.ndarray, n: int) -> np.ndarray:

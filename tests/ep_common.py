@@ -14,6 +14,7 @@ class OracleStages:
         self.L, self.rank, self.world = layer, rank, world
         self.first, self.count = ep.owner_ranges(layer["n_experts"], world)[rank]
         self.K, self.E, self.F = layer["n_used"], layer["n_embd"], layer["n_ff"]
+        self.wire = self.E * 4  # bytes of a row as it travels
 
     def route(self, x):
         self.x = x.numpy()
@@ -59,3 +60,36 @@ class OracleStages:
 
     def to_device(self, a):
         return torch.from_numpy(a)
+
+
+def run_ranks(worker, world, args=(), timeout=180):
+    """Runs worker(rank, world, port, queue, *args) as `world` daemon processes; returns what each put on the queue,
+    sorted. The results are read before the processes are joined (a full pipe would block the child's exit), and a
+    process still alive at the end, whatever the reason, is terminated and then killed, so that no rank is left inside a
+    collective holding a device."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, world, port, q) + tuple(args), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = [q.get(timeout=timeout) for _ in range(world)]
+        for p in procs:
+            p.join(timeout=30)
+        return sorted(res, key=lambda r: r[0])
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.kill()

@@ -1,36 +1,38 @@
 """Expert parallel on two CPU ranks (gloo): the exchange logic of c0ven_b200.ep (split sizes, the two all-to-alls,
 destination order, results back in place) with a CPU stand-in for the GPU stages. Each rank's outputs must be the
-bits the oracle gives for that rank's rows on one process."""
+bits the oracle gives for that rank's rows on one process. Failures are made on the host: a stage that raises on one
+rank, a rank that would receive more rows than it has room for, a rank that never joins a collective."""
+import datetime
 import os
-import socket
+import sys
 
 import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
 
-from c0ven_b200 import ep, synth
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from ep_common import run_ranks  # noqa: E402
 
-
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+from c0ven_b200 import ep, synth  # noqa: E402
 
 
-def _worker(rank, world, port, T, q):
-    import sys
-    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+def _init(rank, world, port, seconds=60):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=seconds))
+
+
+def _layer():
+    return synth.make_layer(n_embd=256, n_ff=256, n_experts=32, n_used=4, gate_type=synth.Q4_K, zipf_s=1.1, seed=3)
+
+
+def _worker(rank, world, port, q, T):
     from ep_common import OracleStages
     from oracle import oracle as O
 
-    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _init(rank, world, port)
     try:
-        layer = synth.make_layer(n_embd=256, n_ff=256, n_experts=32, n_used=4, gate_type=synth.Q4_K, zipf_s=1.1, seed=3)
+        layer = _layer()
         x = synth.make_input(T[rank], 256, seed=10 + rank)
         moe = ep.ExpertParallelMoE(OracleStages(layer, rank, world))
         out = moe.forward(torch.from_numpy(x)).numpy()
@@ -42,19 +44,98 @@ def _worker(rank, world, port, T, q):
 
 @pytest.mark.parametrize("T", [(37, 5), (1, 64)])
 def test_two_ranks_give_the_single_process_bits(T):
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, T, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
-    res = sorted(q.get(timeout=5) for _ in range(2))
+    res = run_ranks(_worker, 2, (T,))
     assert all(ok for _, ok, _, _ in res)
     # What one rank sent to the other is what the other received from it.
     assert res[0][2] == res[1][3] and res[1][2] == res[0][3]
+
+
+def _worker_stage_fails(rank, world, port, q, where):
+    """Rank 1's stage raises in the middle of a step. Rank 0 must still leave the step (its collectives are all
+    entered by rank 1 too, which raises only after them), and the step after that must work on both."""
+    from ep_common import OracleStages
+
+    _init(rank, world, port, seconds=30)
+    try:
+        st = OracleStages(_layer(), rank, world)
+        real = getattr(st, where)
+        calls = {"n": 0}
+
+        def failing(*a):
+            calls["n"] += 1
+            if rank == 1 and calls["n"] == 1:
+                raise RuntimeError("injected: the stage failed")
+            return real(*a)
+
+        setattr(st, where, failing)
+        moe = ep.ExpertParallelMoE(st)
+        x = torch.from_numpy(synth.make_input(9, 256, seed=rank))
+        first = "ok"
+        try:
+            moe.forward(x)
+        except RuntimeError as e:
+            first = str(e)
+        second = "ok"
+        try:
+            moe.forward(x)
+        except RuntimeError as e:  # pragma: no cover
+            second = str(e)
+        q.put((rank, first, second))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("where", ["gather", "experts"])
+def test_a_stage_that_fails_on_one_rank_does_not_strand_the_other(where):
+    res = run_ranks(_worker_stage_fails, 2, (where,), timeout=90)
+    assert res[0][1] == "ok" and "injected" in res[1][1]
+    assert res[0][2] == "ok" and res[1][2] == "ok"
+
+
+def _worker_too_many_rows(rank, world, port, q):
+    from ep_common import OracleStages
+
+    _init(rank, world, port, seconds=30)
+    try:
+        st = OracleStages(_layer(), rank, world)
+        st.max_expert_rows = 8   # far fewer than 2 x 20 rows x 4 experts can bring
+        moe = ep.ExpertParallelMoE(st)
+        try:
+            moe.forward(torch.from_numpy(synth.make_input(20, 256, seed=rank)))
+            q.put((rank, "ok"))
+        except RuntimeError as e:
+            q.put((rank, str(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_every_rank_refuses_a_step_one_rank_has_no_room_for():
+    res = run_ranks(_worker_too_many_rows, 2, timeout=90)
+    assert all("max_expert_rows" in msg for _, msg in res)
+    assert res[0][1] == res[1][1]   # the same message: the same decision, taken from the same gathered counts
+
+
+def _worker_lost_peer(rank, world, port, q):
+    """Rank 1 leaves before the step (between steps, nothing in flight). Rank 0's first collective ends with an error
+    after the process group's short timeout instead of waiting for ever."""
+    from ep_common import OracleStages
+
+    _init(rank, world, port, seconds=5)
+    if rank == 1:
+        q.put((rank, "left"))
+        return
+    moe = ep.ExpertParallelMoE(OracleStages(_layer(), rank, world))
+    t0 = datetime.datetime.now()
+    try:
+        moe.forward(torch.from_numpy(synth.make_input(4, 256, seed=0)))
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, f"error after {(datetime.datetime.now() - t0).total_seconds():.0f} s: {type(e).__name__}"))
+
+
+def test_a_lost_peer_ends_the_collective_with_an_error():
+    res = run_ranks(_worker_lost_peer, 2, timeout=120)
+    assert res[1][1] == "left" and res[0][1].startswith("error")
 
 
 def test_owner_ranges_and_split_sizes():

@@ -1,21 +1,17 @@
 """Expert parallel on two B200s (NCCL): each rank holds half the experts; a rank's outputs must equal, bit for bit,
 what one GPU holding every expert gives for the same rows when the results travel as f32 and every expert takes the
 same kind of kernel on both (tensor_min_rows 1), and stay within the layer's bar when they travel as f16. Needs two GPUs; skipped otherwise."""
+import datetime
 import os
-import socket
+import sys
 
 import numpy as np
 import pytest
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from ep_common import run_ranks  # noqa: E402
+
 pytestmark = pytest.mark.gpu
-
-
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
 
 
 def _worker(rank, world, port, q):
@@ -28,7 +24,8 @@ def _worker(rank, world, port, q):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=60))  # a lost peer ends the wait with an error
     res = []
     try:
         for t, T in ((synth.Q4_K, (300, 41)), (synth.IQ3_S, (7, 1))):
@@ -57,20 +54,10 @@ def _worker(rank, world, port, q):
 
 def test_two_gpus_match_one():
     import torch
-    import torch.multiprocessing as mp
 
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=600)
-        assert p.exitcode == 0
-    for rank, res in sorted(q.get(timeout=5) for _ in range(2)):
+    for rank, res in run_ranks(_worker, 2, timeout=600):
         for t, f16, same_bits, rel, sent in res:
             assert rel <= 1e-2, (rank, t, f16, rel)
             if not f16:
