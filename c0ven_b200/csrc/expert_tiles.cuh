@@ -46,8 +46,9 @@ struct ExpertTilesArgs {
   const BigTile *tiles;     // null: dense_rows rows of slot 0 in tiles of kTileN
   const uint32_t *ntiles;
   uint32_t dense_rows;
-  float *out;               // out[expert-order row][r], f32
+  void *out;                // out[expert-order row][r]: f32, or f16 when out_f16 is set
   uint32_t out_stride;
+  uint32_t out_f16;
   float limit;
   uint32_t *error;          // set non-zero when a wait ran out
 };
@@ -435,7 +436,11 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   using Raw = typename Dec::Raw;
   constexpr uint32_t S = SM::kStages, kCols = 512;
   constexpr uint32_t kDW = kTileDecoders / 32, kEW = kTileEpilogue / 32, kCopyWarp = kDW + kEW, kMmaWarp = kCopyWarp + 1;
-  constexpr uint32_t kHalves = NMAT * kTileM * 2;  // (matrix, row, half) units to decode per stage: a thread takes one
+  // A decode thread takes a whole row of a stage, 64 values as two halves of 32, so that what a stage costs a thread
+  // beside the arithmetic (the barrier round trip, the addresses, the block's scales) is paid once per 64 values. A
+  // stage's NMAT * 128 rows are one group of threads; the 512 decode threads form 2 groups (two matrices) or 4 (one),
+  // and group g takes stages g, g + groups, ...
+  constexpr uint32_t kGroupThreads = NMAT * kTileM, kDecGroups = kTileDecoders / kGroupThreads;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
@@ -459,7 +464,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   // (the copy thread's arrival states their bytes; the copy unit counts them off). An accumulator buffer is empty again
   // when the epilogue warps have read it; after an item that took both buffers, also when the decode warps have.
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW + 1), mbar_init(empty_bar(s), 1);
+    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW / kDecGroups + 1), mbar_init(empty_bar(s), 1);
     for (uint32_t b = 0; b < 2; b++) mbar_init(acc_full(b), 1), mbar_init(acc_empty(b), kEW);
     mbar_init(acc_empty_wide, kDW);
     *abort = 0;
@@ -506,59 +511,65 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         if (n < t.count) {
           float v = __uint_as_float(gv[j]);
           if constexpr (NMAT == 2) v = swiglu_fast(v, __uint_as_float(uv[j]), a.limit);
-          a.out[(uint64_t)(t.start + n) * a.out_stride + r] = v;
+          const uint64_t at = (uint64_t)(t.start + n) * a.out_stride + r;
+          if (a.out_f16)
+            ((__half *)a.out)[at] = __float2half_rn(v);
+          else
+            ((float *)a.out)[at] = v;
         }
       }
     }
   };
 
   if (warp < kDW) {
-    // Decode warps. This thread's unit: half h of row m of matrix tid / 256 (threads past the units decode nothing): 8
-    // consecutive threads take the 8 rows of a core matrix, so a quarter-warp's 16-byte stores fill 128 contiguous bytes.
+    // Decode warps. 8 consecutive threads take the 8 rows of a core matrix, so a quarter-warp's 16-byte stores fill 128
+    // contiguous bytes.
     const uint64_t nblk = (uint64_t)a.R * (K / block_values(QT));
-    const bool decodes = tid < kHalves;
-    const uint32_t mat = tid / 256, u = tid % 256, m = (u & 7) | ((u >> 4) << 3), h = (u >> 3) & 1;
+    const uint32_t first = tid / kGroupThreads, mat = (tid % kGroupThreads) / kTileM, m = tid % kTileM;
     uint32_t li = 0;
     for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t r0 = (item % RT) * kTileM;
       const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
       // Quants come from HBM the first time an expert is touched; a request for the L2 goes out kAhead stages before
-      // the load into registers, which itself goes a stage before the decode.
+      // the load into registers, which itself goes a stage of this thread's before the decode.
       constexpr uint32_t kLineStages = 128 / Dec::kStageBytes;
       constexpr uint32_t kAhead = kLineStages > 6 ? kLineStages : 6 / kLineStages * kLineStages;  // a whole number of lines, about 6 stages
-      Raw raw[2];
-      typename Dec::Hdr hdr, hdr_next;  // the block's scales: fetched with its first stage's quants, used from that stage on
-      auto fetch = [&](Raw &r, uint32_t k0) {
-        if (decodes) {
-          r = Dec::fetch(wm, nblk, K, r0 + m, k0, h);
-          if (k0 % 256 == 0) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0);
-          // One request a 128-byte line: the line holds kLineStages stages of the row, and both halves' threads read it.
-          if (h == 0 && (k0 / kTileK) % kLineStages == 0 && k0 + kAhead * kTileK < K)
-            prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
-        }
+      Raw raw[2][2];  // [buffer][half]
+      // The block's scales: fetched with the first of this thread's stages in the block, used from that stage on.
+      typename Dec::Hdr hdr, hdr_next;
+      uint32_t blk_fetched = 0xFFFFFFFFu, blk_used = 0xFFFFFFFFu;
+      auto fetch = [&](Raw (&r)[2], uint32_t it) {
+        const uint32_t k0 = it * kTileK;
+        r[0] = Dec::fetch(wm, nblk, K, r0 + m, k0, 0);
+        r[1] = Dec::fetch(wm, nblk, K, r0 + m, k0, 1);
+        if (k0 / 256 != blk_fetched) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
+        // One request a 128-byte line, which holds kLineStages stages of the row.
+        if (it % kLineStages == 0 && k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
       };
-      auto stage_step = [&](Raw &r, uint32_t it) {
+      auto stage_step = [&](Raw (&r)[2], uint32_t it) {
         const uint32_t g = li * KT + it, s = g % S, use_s = g / S, k0 = it * kTileK;
         if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
         if (!ok) return;
         tc_fence_after();
-        if (k0 % 256 == 0) hdr = hdr_next;
-        if (decodes) Dec::store(hdr, r, smem + s * SM::kStageBytes + mat * SM::kWBytes, m, h, k0, grid);
+        if (k0 / 256 != blk_used) hdr = hdr_next, blk_used = k0 / 256;
+        uint8_t *tile = smem + s * SM::kStageBytes + mat * SM::kWBytes;
+        Dec::store(hdr, r[0], tile, m, 0, k0, grid);
+        Dec::store(hdr, r[1], tile, m, 1, k0, grid);
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
       };
-      if (decodes)
-        for (uint32_t p = kLineStages; h == 0 && p < kAhead && p < KT; p += kLineStages)
-          prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, 0));
-      fetch(raw[0], 0);
-      for (uint32_t it = 0; it < KT && ok; it += 2) {
-        if (it + 1 < KT) fetch(raw[1], (it + 1) * kTileK);
+      if (first == 0)
+        for (uint32_t p = kLineStages; p < kAhead && p < KT; p += kLineStages) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, 0));
+      // This thread's stages: first, first + kDecGroups, ...; the quants of one are loaded while the one before decodes.
+      if (first < KT) fetch(raw[0], first);
+      for (uint32_t it = first; it < KT && ok; it += 2 * kDecGroups) {
+        if (it + kDecGroups < KT) fetch(raw[1], it + kDecGroups);
         stage_step(raw[0], it);
-        if (!ok || it + 1 >= KT) break;
-        if (it + 2 < KT) fetch(raw[0], (it + 2) * kTileK);
-        stage_step(raw[1], it + 1);
+        if (!ok || it + kDecGroups >= KT) break;
+        if (it + 2 * kDecGroups < KT) fetch(raw[0], it + 2 * kDecGroups);
+        stage_step(raw[1], it + kDecGroups);
       }
       if (is_wide(t.count)) {
         // Both buffers: the next item's MMAs wait for this epilogue, so these warps take four fifths of it.

@@ -4,10 +4,12 @@
 // (core/models/qwen4exp/model.cpp:1348-1418, prompt.cpp:606-656) with its CPU path's arithmetic
 // (core/cpu/experts.cpp:152-284).
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <initializer_list>
 #include <memory>
 #include <mutex>
+#include <stdexcept>
 #include <string>
 #include <thread>
 #include <vector>
@@ -19,6 +21,7 @@
 #include "iq3s_grid.h"
 #include "moe_layer.h"
 #include "route_kernels.cuh"
+#include "router_mma.cuh"
 #include "tensor_map.h"
 
 namespace moe {
@@ -110,6 +113,7 @@ struct PackBuffers {
 };
 
 enum Stage { ST_QUANT, ST_ROUTER, ST_PACK, ST_GATE_UP, ST_DOWN, ST_SHARED, ST_COMBINE, ST_COPIES };
+constexpr uint32_t kRouterExactRows = 64;  // steps of up to this many rows take the exact fp32 router product
 constexpr uint32_t kLocalChunk = 512;  // entries per chunk when packing rows that came from other GPUs
 
 }  // namespace moe
@@ -144,7 +148,14 @@ struct moe_layer {
   DeviceBuffer<uint32_t> grid;
   uint64_t gate_slice = 0, down_slice = 0;
   // A call's buffers.
-  DeviceBuffer<float> x, out, rl, pieces, gate_parts, w, gs, h, y, s;
+  DeviceBuffer<float> x, out, rl, gate_parts, w, gs, h, y, s;
+  // The router's product on the tensor cores (steps of more than 64 rows): the router's rows and the step's rows as
+  // pairs of f16 numbers, the approximate logits, and what bounds their error.
+  bool router_tensor = false, router_attr_set = false;
+  DeviceBuffer<__half> rw_hi, rw_lo, rx_hi, rx_lo;
+  DeviceBuffer<float> rw_unscale, approx, norm2_parts;
+  CUtensorMap rw_hi_map{}, rw_lo_map{}, rx_hi_map{}, rx_lo_map{};
+  float router_eps_rel = 0.0f, router_eps_abs = 0.0f;
   DeviceBuffer<int32_t> ids, ids_local;
   DeviceBuffer<uint32_t> error;
   DeviceBuffer<__half> wire_h;  // rows from other GPUs, dequantised for the tensor-core kernels
@@ -200,6 +211,8 @@ void check_config(const moe_layer_config &c, const moe_layer_weights &w) {
   if (c.shexp_gate_type && (!w.shexp_gate_inp || !w.gate_shexp || !w.up_shexp || !w.down_shexp))
     bad("a shared expert needs its gate vector and three matrices");
 }
+
+void setup_router_tensor(moe_layer *l, const float *router, const float *bias, cudaStream_t st);
 
 void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w) {
   check_config(c, w);
@@ -266,8 +279,9 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   }
 
   l->x.alloc((size_t)T * E), l->out.alloc((size_t)T * E);
-  l->rl.alloc((size_t)std::min<uint32_t>(T, 64) * l->N), l->gate_parts.alloc((size_t)T * (E / 256));
-  if (T > 64) l->pieces.alloc((size_t)kRouterPieces * T * NE);
+  l->router_tensor = l->can_tensor && T > kRouterExactRows;
+  l->rl.alloc((size_t)(l->router_tensor ? kRouterExactRows : T) * l->N), l->gate_parts.alloc((size_t)T * (E / 256));
+  if (l->router_tensor) setup_router_tensor(l, w.router, w.router_bias, st);
   l->ids.alloc(A), l->w.alloc(A), l->gs.alloc(T), l->error.alloc(1);
   l->pack.alloc(A, NE, kChunkTokens * K);
   if (ep) {
@@ -295,19 +309,79 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   CUDA_OK(cudaStreamSynchronize(st));
 }
 
+// The tensor-core router product's operands and error bound. Each of the router's rows is scaled by the power of two
+// that puts its largest magnitude in [1024, 2048), then split into f16 hi and lo parts (lo = f16(w - hi)): both parts
+// are then normal f16 numbers for every weight within 2^-13 of the row's largest, and hi + lo holds 22 bits of w.
+//
+// The bound. An approximate logit differs from the fp32 sum in the exact order by (a) the dropped lo * lo products and
+// the rounding of the lo parts, at most 2^-20 of sum |x_i w_i|; (b) the roundings of the accumulations, each taken as
+// at most 2^-23 of the running sum, one per MMA of 16 values and three MMAs a step: 3 E / 16 of them; (c) the exact
+// order's own roundings: chains of E / 8 fused multiply-adds at 2^-24 of the running sum each, then eight additions.
+// sum |x_i w_i| <= |x| |w_e| (Cauchy-Schwarz), so eps = eps_rel |x| max_e |w_e| with eps_rel = (3 E / 16 + E / 8 + 16) 2^-23
+// (2^-13.6 at E = 2048) covers all three in the worst case, where every rounding falls the same way; measured errors
+// are some hundred times smaller, and the GPU tests hold them under a quarter of the bound. The bias adds one rounding
+// of the biased logit, covered by eps_abs.
+void setup_router_tensor(moe_layer *l, const float *router, const float *bias, cudaStream_t st) {
+  const uint32_t E = l->E, NE = l->NE, T = l->Tmax;
+  const uint64_t wrows = std::max<uint32_t>(NE, kRouterTileExperts), xrows = std::max<uint32_t>(T, kRouterTileRows);
+  std::vector<__half> hi(wrows * E, __float2half_rn(0.0f)), lo(wrows * E, __float2half_rn(0.0f));
+  std::vector<float> unscale(NE, 1.0f);
+  double wn_max = 0.0;
+  for (uint32_t e = 0; e < NE; e++) {
+    const float *w = router + (size_t)e * E;
+    float m = 0.0f;
+    double n2 = 0.0;
+    for (uint32_t i = 0; i < E; i++) m = std::max(m, std::fabs(w[i])), n2 += (double)w[i] * w[i];
+    wn_max = std::max(wn_max, std::sqrt(n2));
+    int ex = 0;
+    if (m > 0.0f && std::isfinite(m)) std::frexp(m, &ex);
+    ex = std::min(std::max(ex, -100), 100);
+    const float s = std::ldexp(1.0f, 11 - ex);
+    unscale[e] = std::ldexp(1.0f, ex - 11);
+    for (uint32_t i = 0; i < E; i++) {
+      const float v = w[i] * s;
+      const __half h = __float2half_rn(v);
+      hi[(size_t)e * E + i] = h;
+      lo[(size_t)e * E + i] = __float2half_rn(v - __half2float(h));
+    }
+  }
+  float bias_max = 0.0f;
+  for (uint32_t e = 0; bias && e < NE; e++) bias_max = std::max(bias_max, std::fabs(bias[e]));
+  l->router_eps_rel = (float)(std::ldexp(3.0 * E / 16 + E / 8 + 16, -23) * wn_max);
+  l->router_eps_abs = std::ldexp(1.0f + bias_max, -20);
+  l->rw_hi.alloc(hi.size()), l->rw_lo.alloc(lo.size()), l->rw_unscale.alloc(NE);
+  CUDA_OK(cudaMemcpyAsync(l->rw_hi.get(), hi.data(), hi.size() * sizeof(__half), cudaMemcpyHostToDevice, st));
+  CUDA_OK(cudaMemcpyAsync(l->rw_lo.get(), lo.data(), lo.size() * sizeof(__half), cudaMemcpyHostToDevice, st));
+  CUDA_OK(cudaMemcpyAsync(l->rw_unscale.get(), unscale.data(), NE * sizeof(float), cudaMemcpyHostToDevice, st));
+  l->rx_hi.alloc(xrows * E), l->rx_lo.alloc(xrows * E);
+  CUDA_OK(cudaMemsetAsync(l->rx_hi.get(), 0, xrows * E * sizeof(__half), st));
+  CUDA_OK(cudaMemsetAsync(l->rx_lo.get(), 0, xrows * E * sizeof(__half), st));
+  l->approx.alloc((size_t)T * NE), l->norm2_parts.alloc((size_t)T * (E / 256));
+  l->rw_hi_map = make_rows_map(l->rw_hi.get(), wrows, E, kRouterTileExperts);
+  l->rw_lo_map = make_rows_map(l->rw_lo.get(), wrows, E, kRouterTileExperts);
+  l->rx_hi_map = make_rows_map(l->rx_hi.get(), xrows, E, kRouterTileRows);
+  l->rx_lo_map = make_rows_map(l->rx_lo.get(), xrows, E, kRouterTileRows);
+  CUDA_OK(cudaStreamSynchronize(st));
+}
+
 // gate: with the rows' product with this vector wanted too (the shared expert's gate logit), its parts go to gate_parts.
 void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, const ActBuffers &dst, cudaStream_t st,
-                   const float *gate = nullptr, float *gate_parts = nullptr) {
+                   const float *gate = nullptr, float *gate_parts = nullptr, RouterSplit rs = RouterSplit{}) {
   const uint64_t nblk = rows * (Kv / 256);
   if (nblk == 0) return;
   const ActView v = dst.view();
   const unsigned grid = (unsigned)((nblk + 7) / 8);
   if (dst.q8k)
-    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get(), gate, Kv / 256, gate_parts);
+    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get(), gate, Kv / 256, gate_parts, rs);
   else
-    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get(), gate, Kv / 256, gate_parts);
+    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get(), gate, Kv / 256, gate_parts, rs);
   launched(l, cudaGetLastError(), "quantize");
 }
+
+// Whether a call of R expert rows keeps its experts' results in f16: when every expert takes the tile kernels, whose
+// products are f16 products already. The down kernel then writes half the bytes and the combine reads half; the sum
+// over a row's experts stays in f32.
+bool results_f16(const moe_layer *l, uint32_t tm) { return l->can_tensor && tm == 1; }
 
 // Rows a group's kernel takes at once, for groups that hold at most n rows.
 int group_rows(uint64_t n) { return n > 4 ? 8 : n > 2 ? 4 : (int)n; }
@@ -337,12 +411,18 @@ uint32_t tensor_budget_for(const moe_layer *l, uint64_t R) {
 void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   const uint32_t E = l->E, NE = l->NE, K = l->K, N = l->N;
   const uint64_t A = (uint64_t)T * K;
-  const bool by_pieces = T > 64;
+  // Steps of up to kRouterExactRows rows (and every step of a layer kept off the tensor cores) take the exact fp32
+  // product; longer ones the tensor-core product, whose logits the top-k kernel treats as approximate.
+  const bool approx = l->router_tensor && T > kRouterExactRows;
   mark(l, ST_QUANT, st);
-  quantize_rows(l, x, T, E, l->xq_routed, st, by_pieces ? l->router.get() + (size_t)NE * E : nullptr, l->gate_parts.get());
+  if (approx)
+    quantize_rows(l, x, T, E, l->xq_routed, st, l->router.get() + (size_t)NE * E, l->gate_parts.get(),
+                  RouterSplit{l->rx_hi.get(), l->rx_lo.get(), l->norm2_parts.get()});
+  else
+    quantize_rows(l, x, T, E, l->xq_routed, st);
   if (l->has_shared && !l->shared_x_same) quantize_rows(l, x, T, E, l->xq_shared, st);
   mark(l, ST_ROUTER, st);
-  if (!by_pieces) {
+  if (!approx) {
     // Steps of up to 2 rows stage only those (8 KB a row); longer ones 8 rows a pass.
     const uint32_t tm = T <= 2 ? T : 8;
     const size_t smem = (size_t)tm * kRouterPieces * (E / kRouterPieces + 4) * sizeof(float);
@@ -365,10 +445,13 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
     else
       k_router_logits_rows<8><<<grid, 256, smem, st>>>(x, T, E, l->router.get(), N, l->bias.get(), NE, l->rl.get());
   } else {
-    if (router_rows_per_thread(T, NE, 2 * l->sms) == 6)
-      k_router_pieces<6><<<dim3((NE + 127) / 128, (T + 95) / 96, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
-    else
-      k_router_pieces<8><<<dim3((NE + 127) / 128, (T + 127) / 128, kRouterPieces), 256, 0, st>>>(x, T, E, l->router.get(), NE, l->pieces.get());
+    if (!l->router_attr_set) {
+      CUDA_OK(cudaFuncSetAttribute(k_router_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRouterSmemBytes));
+      l->router_attr_set = true;
+    }
+    const RouterMmaArgs ra{T, E, NE, l->rw_unscale.get(), l->approx.get(), l->error.get()};
+    const uint32_t items = ((T + kRouterTileRows - 1) / kRouterTileRows) * ((NE + kRouterTileExperts - 1) / kRouterTileExperts);
+    k_router_mma<<<std::min(items, l->sms), kRouterThreads, kRouterSmemBytes, st>>>(ra, l->rx_hi_map, l->rx_lo_map, l->rw_hi_map, l->rw_lo_map);
   }
   launched(l, cudaGetLastError(), "router logits");
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
@@ -376,7 +459,7 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   const uint32_t tm = l->local == NE ? tensor_min_for(l, A) : 0, budget = l->local == NE ? tensor_budget_for(l, A) : 0;
   l->last_tensor_min = tm;
   const uint32_t chunk_len = kChunkTokens * K;
-  if (nchunks == 1 && !by_pieces && NE <= 512) {
+  if (nchunks == 1 && NE <= 512) {
     // One chunk: top-k, scan and fill in one CTA (the pack stage then has no kernel of its own).
     k_router_topk_pack<<<1, 32 * kChunkTokens, chunk_len * sizeof(int32_t), st>>>(l->rl.get(), l->bias.get(), T, NE, K, l->ids.get(), l->w.get(),
                                                                                   l->gs.get(), tm, budget, group_cap(A, NE), l->pack.out(),
@@ -384,8 +467,12 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
     launched(l, cudaGetLastError(), "router top-k and pack");
     mark(l, ST_PACK, st);
   } else {
-    k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), by_pieces ? l->pieces.get() : nullptr, l->bias.get(), l->gate_parts.get(),
-                                                        E / 256, T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), l->pack.chunk_hist.get());
+    RouterApprox ap{};
+    if (approx)
+      ap = RouterApprox{l->approx.get(), x, l->router.get(), l->norm2_parts.get(), l->gate_parts.get(), E, E / 256,
+                        l->router_eps_rel, l->router_eps_abs};
+    k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), ap, l->bias.get(), T, NE, K, l->ids.get(), l->w.get(), l->gs.get(),
+                                                        l->pack.chunk_hist.get());
     launched(l, cudaGetLastError(), "router top-k");
     mark(l, ST_PACK, st);
     k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, budget, group_cap(A, NE), l->pack.out());
@@ -399,7 +486,9 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
 
 // The routed experts on the R rows a pack lists: gate/up and SwiGLU into h, h quantised, down into y (expert order).
 // most: the most rows one expert can have (a step's tokens; in an expert-parallel call, not known below R).
-void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint64_t most, uint32_t tm, float *y, cudaStream_t st) {
+// y16: the results in f16 (only with every expert on the tile kernels: the integer-dot kernels write f32).
+void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint64_t most, uint32_t tm, void *y, bool y16,
+                   cudaStream_t st) {
   const uint32_t E = l->E, F = l->F, nexp = pk.nexp;
   const moe_layer_config &c = l->cfg;
   // The most groups and big tiles the rows can make: an expert below tm rows has (tm - 2) / 8 + 1 groups at most, and one
@@ -439,7 +528,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     ExpertTilesArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
-    a.out = y, a.out_stride = E, a.error = l->error.get();
+    a.out = y, a.out_stride = E, a.out_f16 = y16, a.error = l->error.get();
     launched(l, launch_tiles(c.down_type, 1, a, l->hq_routed.h_map, max_big, l->grid.get(), l->ctx, st), "experts down tiles");
   }
   if (max_groups) {
@@ -447,7 +536,8 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E, a.rows_per_cta = 128;
     a.act = l->hq_routed.view(), a.act_row = nullptr;
     a.groups = pk.groups.get(), a.ngroups = pk.counters.get() + 1;
-    a.out = y, a.out_stride = E;
+    if (y16) throw std::logic_error("f16 results with experts on the integer-dot kernels");
+    a.out = (float *)y, a.out_stride = E;
     launched(l, launch_rows(c.down_type, 1, a, M, max_groups, l->grid.get(), l->ctx, st), "experts down");
   }
 }
@@ -511,12 +601,16 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
     l->join_ev->record(l->aux->get());
   }
   const ActSource src{l->xq_routed.view(), l->xq_routed.h.get(), l->pack.row_src.get()};
-  stage_experts(l, src, l->pack, A, T, l->last_tensor_min, l->y.get(), st);
+  const bool y16 = results_f16(l, l->last_tensor_min);
+  stage_experts(l, src, l->pack, A, T, l->last_tensor_min, l->y.get(), y16, st);
   if (beside)
     CUDA_OK(cudaStreamWaitEvent(st, l->join_ev->get(), 0));
   else
     stage_shared(l, T, st);
-  stage_combine<float>(l, l->y.get(), T, out, st);
+  if (y16)
+    stage_combine<__half>(l, (const __half *)l->y.get(), T, out, st);
+  else
+    stage_combine<float>(l, l->y.get(), T, out, st);
   l->stats.calls++, l->stats.rows += T, l->stats.assignments += A;
 }
 
@@ -763,11 +857,15 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
       src.h = l->wire_h.get();
     }
     l->last_pack = &pk;
-    stage_experts(l, src, pk, R, R, tm, l->y.get(), st);
-    if (y_f16)
-      k_unpermute<__half><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (__half *)y_dev);
+    // The results stay f16 in between only when they also leave as f16 (f32 results are the bit-exact mode).
+    const bool y16 = y_f16 && results_f16(l, tm);
+    stage_experts(l, src, pk, R, R, tm, l->y.get(), y16, st);
+    if (y16)
+      k_unpermute<__half, __half><<<R, 256, 0, st>>>((const __half *)l->y.get(), pk.inv.get(), E, (__half *)y_dev);
+    else if (y_f16)
+      k_unpermute<float, __half><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (__half *)y_dev);
     else
-      k_unpermute<float><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (float *)y_dev);
+      k_unpermute<float, float><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (float *)y_dev);
     launched(l, cudaGetLastError(), "rows back in arrival order");
   });
 }

@@ -39,14 +39,41 @@ __device__ __forceinline__ void gate_part(const float4 &a, const float4 &b, cons
   if (lane == 0) gate_parts[blk] = s;
 }
 
+// What the tensor-core router product takes of a row (steps of many rows): x as the sum of two f16 numbers, hi = f16(x)
+// and lo = f16(x - hi), 22 bits of x between them, and the block's sum of squares, from which the top-k kernel bounds
+// that product's error for the row.
+struct RouterSplit {
+  __half *hi, *lo;     // [rows][K] each; null: not wanted
+  float *norm2_parts;  // [rows][K / 256]
+};
+__device__ __forceinline__ uint32_t split_pair(float x0, float x1, uint32_t &lo) {
+  const __half2 h = __floats2half2_rn(x0, x1);
+  const float2 hf = __half22float2(h);
+  const __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+  lo = *(const uint32_t *)&l;
+  return *(const uint32_t *)&h;
+}
+__device__ __forceinline__ void router_split(const float4 &a, const float4 &b, uint64_t blk, uint32_t lane, const RouterSplit &rs) {
+  uint4 hi, lo;
+  hi.x = split_pair(a.x, a.y, lo.x), hi.y = split_pair(a.z, a.w, lo.y);
+  hi.z = split_pair(b.x, b.y, lo.z), hi.w = split_pair(b.z, b.w, lo.w);
+  ((uint4 *)(rs.hi + blk * 256))[lane] = hi;
+  ((uint4 *)(rs.lo + blk * 256))[lane] = lo;
+  float s = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) rs.norm2_parts[blk] = s;
+}
+
 static __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
                                                    float *__restrict__ d, __half *__restrict__ deq, const float *__restrict__ gate,
-                                                   uint32_t per_row, float *__restrict__ gate_parts) {
+                                                   uint32_t per_row, float *__restrict__ gate_parts, RouterSplit rs) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
   const float4 a = ((const float4 *)(x + blk * 256))[2 * lane], b = ((const float4 *)(x + blk * 256))[2 * lane + 1];
   if (gate) gate_part(a, b, gate, per_row, blk, lane, gate_parts);
+  if (rs.hi) router_split(a, b, blk, lane, rs);
   float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
                      fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -74,12 +101,14 @@ static __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restri
 // q = min(127, nearest-even(iscale * x)), d = 1 / iscale, and the sums of each 16 codes (QUANT_FORMATS.md:528-535).
 static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
                                                    float *__restrict__ d, int16_t *__restrict__ bs, __half *__restrict__ deq,
-                                                   const float *__restrict__ gate, uint32_t per_row, float *__restrict__ gate_parts) {
+                                                   const float *__restrict__ gate, uint32_t per_row, float *__restrict__ gate_parts,
+                                                   RouterSplit rs) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
   const float4 a = ((const float4 *)(x + blk * 256))[2 * lane], b = ((const float4 *)(x + blk * 256))[2 * lane + 1];
   if (gate) gate_part(a, b, gate, per_row, blk, lane, gate_parts);
+  if (rs.hi) router_split(a, b, blk, lane, rs);
   const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
   float amax = 0.0f, mx = 0.0f;
   uint32_t at = 8 * lane;
@@ -184,104 +213,6 @@ static __global__ void __launch_bounds__(256) k_router_logits_rows(const float *
   }
 }
 
-// Many rows: the product piece by piece. A CTA takes a 128 x 128 (or 96 x 128) tile of (rows, experts) and one of the kRouterPieces
-// pieces of the hidden size, 8 x 8 outputs a thread, 16 values of the piece a step, each output one chain of fused
-// multiply-adds in index order; it leaves the piece's partial sums in P[piece][row][expert]. The top-k kernel adds a
-// row's pieces in order. Splitting by piece gives eight times the CTAs, which keeps every SM busy at a few thousand
-// rows, and frees the registers the running totals would take. The shared expert's gate logit does not come from
-// here: the activation quantiser sums it (k_quant_*'s gate argument).
-template <int RM>
-static __global__ void __launch_bounds__(256, 2) k_router_pieces(const float *__restrict__ x, uint32_t T, uint32_t E,
-                                                                const float *__restrict__ W, uint32_t NE, float *__restrict__ P) {
-  constexpr int BM = RM == 8 ? 128 : 96, BN = 128, BK = 16, LD = 128 + 4;
-  static_assert(RM == 8 || RM == 6, "tiles of 128 or 96 rows");
-  __shared__ __align__(16) float As[2][BK][LD], Bs[2][BK][LD];
-  const uint32_t tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
-  const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, piece = E / kRouterPieces, kbeg = blockIdx.z * piece;
-  float acc[RM][8];
-#pragma unroll
-  for (int i = 0; i < RM; i++)
-#pragma unroll
-    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
-  // A thread's loads per step: two float4 of x and two of W, rows lr and the quarter lq of the step's 16 values and the
-  // one two on. A warp's lanes hold consecutive rows, so the transposed stores fill consecutive banks.
-  const uint32_t lr = tid % 128, lq = tid / 128;
-  float4 ra[2], rb[2];
-  auto fetch = [&](uint32_t k0) {
-    const uint32_t r = m0 + lr, e = n0 + lr;
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-      ra[i] = (lr < BM && r < T) ? __ldg((const float4 *)(x + (uint64_t)r * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
-      rb[i] = e < NE ? __ldg((const float4 *)(W + (uint64_t)e * E + k0 + 4 * (lq + 2 * i))) : make_float4(0, 0, 0, 0);
-    }
-  };
-  auto stash = [&](int buf) {
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-      const uint32_t k = 4 * (lq + 2 * i);
-      As[buf][k + 0][lr] = ra[i].x, As[buf][k + 1][lr] = ra[i].y, As[buf][k + 2][lr] = ra[i].z, As[buf][k + 3][lr] = ra[i].w;
-      Bs[buf][k + 0][lr] = rb[i].x, Bs[buf][k + 1][lr] = rb[i].y, Bs[buf][k + 2][lr] = rb[i].z, Bs[buf][k + 3][lr] = rb[i].w;
-    }
-  };
-  fetch(kbeg);
-  stash(0);
-  __syncthreads();
-  const uint32_t steps = piece / BK;
-  for (uint32_t s = 0; s < steps; s++) {
-    const int buf = s & 1;
-    if (s + 1 < steps) fetch(kbeg + (s + 1) * BK);
-#pragma unroll
-    for (int k = 0; k < BK; k++) {
-      // A thread's rows: ty * 4 .. + 3 and, past row 64, ty * 4 .. + 3 again (128-row tiles) or ty * 2, ty * 2 + 1 (96).
-      const float4 a0 = *(const float4 *)&As[buf][k][ty * 4];
-      float av[RM] = {a0.x, a0.y, a0.z, a0.w};
-      if constexpr (RM == 8) {
-        const float4 a1 = *(const float4 *)&As[buf][k][64 + ty * 4];
-        av[4] = a1.x, av[5] = a1.y, av[6] = a1.z, av[7] = a1.w;
-      } else {
-        const float2 a1 = *(const float2 *)&As[buf][k][64 + ty * 2];
-        av[4] = a1.x, av[5] = a1.y;
-      }
-      const float4 b0 = *(const float4 *)&Bs[buf][k][tx * 4], b1 = *(const float4 *)&Bs[buf][k][64 + tx * 4];
-      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-      for (int i = 0; i < RM; i++)
-#pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-    }
-    if (s + 1 < steps) stash(buf ^ 1);
-    __syncthreads();
-  }
-  float *out = P + (uint64_t)blockIdx.z * T * NE;
-#pragma unroll
-  for (int i = 0; i < RM; i++) {
-    const uint32_t t = m0 + (i < 4 ? ty * 4 + i : 64 + ty * (RM - 4) + i - 4);
-    if (t >= T) continue;
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-      const uint32_t e = n0 + 64 * h + tx * 4;
-      if (e + 3 < NE)
-        *(float4 *)(out + (uint64_t)t * NE + e) = make_float4(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3]);
-      else
-        for (int j = 0; j < 4; j++)
-          if (e + j < NE) out[(uint64_t)t * NE + e + j] = acc[i][4 * h + j];
-    }
-  }
-}
-
-// Rows a thread of k_router_pieces takes (8: tiles of 128 rows, 6: of 96) for T rows on a GPU that holds `slots` of its
-// CTAs at once: the height whose whole waves cost less. 3,521 rows in tiles of 128 are 896 CTAs, three waves of 296 and
-// eight CTAs of a fourth; in tiles of 96, 1,184 CTAs, four waves three quarters as long.
-inline int router_rows_per_thread(uint32_t T, uint32_t NE, uint32_t slots) {
-  auto cost = [&](int rm) {
-    const uint64_t ctas = (uint64_t)((T + 16 * rm - 1) / (16 * rm)) * ((NE + 127) / 128) * kRouterPieces;
-    return ((ctas + slots - 1) / slots) * rm;
-  };
-  // A 96-row tile does 48 multiply-adds for the shared-memory loads that feed 64 in a 128-row tile: measured, a row
-  // costs it about a fifth more (3,521 rows: 0.257 -> 0.236 ms; 32,768 rows: 1.90 -> 2.03 ms when it was chosen there).
-  return cost(6) * 6 < cost(8) * 5 ? 6 : 8;
-}
-
 // ---------------------------------------------------------------------------------------------------------------
 // Top-k. One warp per row, lane holding experts lane + 32 j. Keys order the logits as floats do (the reference's
 // topk_key, kernels/include/topk.h:12-15), -0 taken as +0; winners come out largest first, ties to the lower expert
@@ -297,12 +228,58 @@ __device__ __forceinline__ float key_value(uint32_t key) {
 
 constexpr int kMaxPerLane = 16;  // experts a lane holds at most: 512 / 32
 
-// The logits come as rows rl[t][NE + 1] (the gate's logit last), or, with pieces set, as the partial sums
-// pieces[p][t][e] of k_router_pieces, added here in order with the bias, and the gate's logit as gate_parts[t][nparts].
+// Steps of many rows: the logits come from the tensor-core product (router_mma.cuh) and are approximate. For row t
+// every one is within eps_t of the logit the exact order gives, eps_t = eps_rel * |x_t| * (largest |w_e|) + eps_abs,
+// with |x_t|^2 summed from norm2_parts. The top-k below then recomputes, in the exact order, only what that bound
+// cannot decide.
+struct RouterApprox {
+  const float *logits;       // [T][NE]; null: the logits are exact rows rl[t][NE + 1]
+  const float *x;            // [T][E]
+  const float *W;            // [NE][E]
+  const float *norm2_parts;  // [T][nparts]
+  const float *gate_parts;   // [T][nparts]: the parts of the shared expert's gate logit
+  uint32_t E, nparts;
+  float eps_rel, eps_abs;
+};
+
+// The logits of up to four experts for row x, each exactly as k_router_logits_rows and the CPU oracle sum it: eight
+// pieces of the row, each a chain of fused multiply-adds from 0 in index order, the pieces added in order, the bias
+// last. Lane 8 j + s takes piece s of expert ex[j]; lanes 8 j .. 8 j + 7 return expert ex[j]'s logit.
+__device__ __forceinline__ float exact_logits4(const float *__restrict__ x, const float *__restrict__ W, const float *__restrict__ bias,
+                                               uint32_t E, uint32_t e, uint32_t lane) {
+  const uint32_t piece = E / kRouterPieces, s = lane % 8;
+  const float4 *xp = (const float4 *)(x + s * piece), *wp = (const float4 *)(W + (uint64_t)e * E + s * piece);
+  float p = 0.0f;
+  for (uint32_t i = 0; i < piece / 4; i += 4) {
+    float4 xv[4], wv[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) xv[j] = __ldg(xp + i + j), wv[j] = __ldg(wp + i + j);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      p = fmaf(xv[j].x, wv[j].x, p);
+      p = fmaf(xv[j].y, wv[j].y, p);
+      p = fmaf(xv[j].z, wv[j].z, p);
+      p = fmaf(xv[j].w, wv[j].w, p);
+    }
+  }
+  float tot = __shfl_sync(0xffffffffu, p, lane & ~7u);
+#pragma unroll
+  for (int j = 1; j < (int)kRouterPieces; j++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, p, (lane & ~7u) + j));
+  if (bias) tot = __fadd_rn(tot, bias[e]);
+  return tot;
+}
+
 // The block's part: its rows' ids, weights and gates written, the chunk's count of every expert left in hist (shared,
 // 512 words) and, when s_ids is not null, the chunk's ids there too (shared, kChunkTokens * K words).
-__device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, const float *__restrict__ pieces,
-                                                  const float *__restrict__ bias, const float *__restrict__ gate_parts, uint32_t nparts,
+//
+// With approximate logits a row's candidates are the experts whose approximate logit is within 2 eps of the K-th
+// largest: the true top K is among them (an expert outside is below K others by more than the two errors can
+// bridge). Sorted by approximate logit, two neighbours less than 2 eps apart cannot be ordered by it, and both get
+// their exact logit; any other pair's order is certain. The candidates are then ranked by (logit, lower expert first)
+// with exact logits where they were needed, and the first K are the row's experts, in rank order. A row with more
+// than 32 candidates (all logits equal, as for a row of zeros) or a logit that is not finite (an x beyond f16's range)
+// has every logit recomputed exactly instead.
+__device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, const RouterApprox ap, const float *__restrict__ bias,
                                                   uint32_t T, uint32_t NE, uint32_t K, int32_t *__restrict__ ids, float *__restrict__ w,
                                                   float *__restrict__ gs, uint32_t *hist, int32_t *s_ids) {
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
@@ -310,18 +287,18 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
   const uint32_t lane = threadIdx.x % 32, t = blockIdx.x * kChunkTokens + threadIdx.x / 32, per = NE / 32;
   if (t < T) {
     uint32_t key[kMaxPerLane];
-    float mx = -INFINITY;
+    float mx = -INFINITY, eps2 = 0.0f;  // eps2: twice the row's error bound; 0 with exact logits
+    bool finite = true;
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; j++) {
       key[j] = 0;
       if ((uint32_t)j < per) {
         const uint32_t e = lane + 32 * j;
         float f;
-        if (pieces) {
-          f = pieces[(uint64_t)t * NE + e];
-#pragma unroll
-          for (uint32_t p = 1; p < kRouterPieces; p++) f = __fadd_rn(f, pieces[((uint64_t)p * T + t) * NE + e]);
+        if (ap.logits) {
+          f = ap.logits[(uint64_t)t * NE + e];
           if (bias) f = __fadd_rn(f, bias[e]);
+          finite = finite && isfinite(f);
         } else {
           f = rl[(uint64_t)t * (NE + 1) + e];
         }
@@ -329,53 +306,129 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
         mx = fmaxf(mx, f);
       }
     }
+    if (ap.logits) {
+      float n2 = 0.0f;
+      for (uint32_t p = lane; p < ap.nparts; p += 32) n2 += ap.norm2_parts[(uint64_t)t * ap.nparts + p];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    float sum = 0.0f;
+      for (int off = 16; off > 0; off >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
+      eps2 = 2.0f * (ap.eps_rel * sqrtf(n2) + ap.eps_abs);
+      finite = __all_sync(0xffffffffu, finite) && isfinite(eps2);
+    }
+    // Lane k keeps the k-th winner of the rounds below.
+    float my_v = 0.0f, sum = 0.0f;
+    uint32_t my_id = 0, ncand = 0;
+    for (bool exact_all = ap.logits && !finite;;) {
+      if (exact_all) {
+        // Every logit exactly, four experts a pass: for rows the approximate ones cannot serve.
+        mx = -INFINITY;
+        for (uint32_t e0 = 0; e0 < NE; e0 += 4) {
+          const float v = exact_logits4(ap.x + (uint64_t)t * ap.E, ap.W, bias, ap.E, e0 + lane / 8, lane);
 #pragma unroll
-    for (int j = 0; j < kMaxPerLane; j++)
-      if ((uint32_t)j < per) sum += expf(key_value(key[j]) - mx);
+          for (int q = 0; q < 4; q++) {
+            const float vq = __shfl_sync(0xffffffffu, v, 8 * q);
+            const uint32_t e = e0 + q;
+            if (e % 32 == lane) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    // K rounds of arg-max over (key, lower expert first).
-    float pk = 0.0f;
-    uint32_t my_id = 0;
-    for (uint32_t k = 0; k < K; k++) {
-      unsigned long long best = 0;
-#pragma unroll
-      for (int j = 0; j < kMaxPerLane; j++) {
-        const unsigned long long c = ((unsigned long long)key[j] << 32) | (uint32_t)~(lane + 32 * j);
-        if ((uint32_t)j < per && c > best) best = c;
+              for (int j = 0; j < kMaxPerLane; j++)
+                if ((uint32_t)j == e / 32) key[j] = order_key(vq);
+            }
+            mx = fmaxf(mx, vq);
+          }
+        }
+        eps2 = 0.0f;
       }
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
-        if (o > best) best = o;
-      }
-      const uint32_t e = ~(uint32_t)best, bkey = (uint32_t)(best >> 32);
-      if (e % 32 == lane) {
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kMaxPerLane; j++)
-          if ((uint32_t)j == e / 32) key[j] = 0;
+      for (int j = 0; j < kMaxPerLane; j++)
+        if ((uint32_t)j < per) sum += expf(key_value(key[j]) - mx);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      // Rounds of arg-max over (key, lower expert first), which use the keys up. K rounds with exact logits; with
+      // approximate ones, on until the next is more than 2 eps below the K-th (at most 32 in all).
+      float vK = 0.0f;
+      bool overflow = false;
+      ncand = 0;
+      for (uint32_t k = 0; k < 32; k++) {
+        unsigned long long best = 0;
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; j++) {
+          const unsigned long long c = ((unsigned long long)key[j] << 32) | (uint32_t)~(lane + 32 * j);
+          if ((uint32_t)j < per && c > best) best = c;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
+          if (o > best) best = o;
+        }
+        const uint32_t e = ~(uint32_t)best, bkey = (uint32_t)(best >> 32);
+        if (bkey == 0) break;  // nothing left (fewer than 32 experts in all)
+        const float v = key_value(bkey);
+        if (k == K - 1) vK = v;
+        if (k >= K && !(eps2 > 0.0f && v >= vK - eps2)) break;
+        if (e % 32 == lane) {
+#pragma unroll
+          for (int j = 0; j < kMaxPerLane; j++)
+            if ((uint32_t)j == e / 32) key[j] = 0;
+        }
+        if (lane == k) my_id = e, my_v = v;
+        ncand = k + 1;
+        if (k == 31 && eps2 > 0.0f && NE > 32) overflow = true;  // there may be more within reach than a warp holds
       }
-      if (lane == k) {
-        my_id = e;
-        pk = expf(key_value(bkey) - mx) / sum;
+      if (!overflow) break;
+      exact_all = true;
+    }
+    if (eps2 > 0.0f) {
+      // Neighbours too close to order: both get their exact logit, four candidates a pass.
+      const float up = __shfl_up_sync(0xffffffffu, my_v, 1), down = __shfl_down_sync(0xffffffffu, my_v, 1);
+      const bool need = lane < ncand && ((lane > 0 && up - my_v <= eps2) || (lane + 1 < ncand && my_v - down <= eps2));
+      uint32_t todo = __ballot_sync(0xffffffffu, need);
+      while (todo) {
+        uint32_t c[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          c[q] = todo ? (uint32_t)__ffs(todo) - 1 : 0xFFFFFFFFu;
+          if (todo) todo &= todo - 1;
+        }
+        const uint32_t g8 = lane / 8, mine = g8 == 0 ? c[0] : g8 == 1 ? c[1] : g8 == 2 ? c[2] : c[3];
+        const uint32_t e = __shfl_sync(0xffffffffu, my_id, mine == 0xFFFFFFFFu ? 0 : mine);
+        const float v = exact_logits4(ap.x + (uint64_t)t * ap.E, ap.W, bias, ap.E, e, lane);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const float vq = __shfl_sync(0xffffffffu, v, 8 * q);
+          if (lane == c[q]) my_v = vq + 0.0f;
+        }
       }
     }
+    // Rank among the candidates by (logit, lower expert first); with exact logits this is the order they came in.
+    uint32_t rank = 0;
+    {
+      const unsigned long long me = ((unsigned long long)order_key(my_v) << 32) | (uint32_t)~my_id;
+      for (uint32_t j = 0; j < ncand; j++) {
+        const unsigned long long o = __shfl_sync(0xffffffffu, me, j);
+        rank += o > me;
+      }
+    }
+    const bool winner = lane < ncand && rank < K;
+    const float pk = winner ? expf(my_v - mx) / sum : 0.0f;
+    // The K winners' p added in rank order.
     float tot = 0.0f;
-    for (uint32_t k = 0; k < K; k++) tot += __shfl_sync(0xffffffffu, pk, k);
-    if (lane < K) {
-      ids[(uint64_t)t * K + lane] = (int32_t)my_id;
-      w[(uint64_t)t * K + lane] = pk / fmaxf(tot, 6.1035e-5f);
+    for (uint32_t k = 0; k < K; k++) {
+      const uint32_t src = __ffs(__ballot_sync(0xffffffffu, winner && rank == k)) - 1;
+      tot += __shfl_sync(0xffffffffu, pk, src & 31);
+    }
+    if (winner) {
+      ids[(uint64_t)t * K + rank] = (int32_t)my_id;
+      w[(uint64_t)t * K + rank] = pk / fmaxf(tot, 6.1035e-5f);
       atomicAdd(&hist[my_id], 1u);
-      if (s_ids) s_ids[(threadIdx.x / 32) * K + lane] = (int32_t)my_id;
+      if (s_ids) s_ids[(threadIdx.x / 32) * K + rank] = (int32_t)my_id;
     }
     if (lane == 0) {
       float g;
-      if (pieces) {
+      if (ap.logits) {
         g = 0.0f;
-        for (uint32_t p = 0; p < nparts; p++) g += gate_parts[(uint64_t)t * nparts + p];
+        for (uint32_t p = 0; p < ap.nparts; p++) g += ap.gate_parts[(uint64_t)t * ap.nparts + p];
       } else {
         g = rl[(uint64_t)t * (NE + 1) + NE];
       }
@@ -385,14 +438,13 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
   __syncthreads();
 }
 
-static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const float *__restrict__ pieces,
-                                                                  const float *__restrict__ bias, const float *__restrict__ gate_parts,
-                                                                  uint32_t nparts, uint32_t T, uint32_t NE,
+static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const RouterApprox ap,
+                                                                  const float *__restrict__ bias, uint32_t T, uint32_t NE,
                                                                   uint32_t K, int32_t *__restrict__ ids,
                                                                   float *__restrict__ w, float *__restrict__ gs,
                                                                   uint32_t *__restrict__ chunk_hist) {
   __shared__ uint32_t hist[512];
-  router_topk_block(rl, pieces, bias, gate_parts, nparts, T, NE, K, ids, w, gs, hist, nullptr);
+  router_topk_block(rl, ap, bias, T, NE, K, ids, w, gs, hist, nullptr);
   for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) chunk_hist[(uint64_t)blockIdx.x * NE + i] = hist[i];
 }
 
@@ -597,7 +649,7 @@ static __global__ void __launch_bounds__(32 * kChunkTokens, 1) k_router_topk_pac
                                                                        uint32_t *__restrict__ row_src) {
   __shared__ uint32_t hist[512];
   extern __shared__ int32_t s_chunk_ids[];
-  router_topk_block(rl, nullptr, bias, nullptr, 0, T, NE, K, ids, w, gs, hist, s_chunk_ids);
+  router_topk_block(rl, RouterApprox{}, bias, T, NE, K, ids, w, gs, hist, s_chunk_ids);
   const uint32_t e = threadIdx.x;
   const uint32_t run = e < NE ? hist[e] : 0;
   uint32_t row = pack_scan_block(e, run, NE, 0, tensor_min, tensor_budget, group_max, o);
@@ -692,21 +744,24 @@ static __global__ void __launch_bounds__(256) k_wire_to_f16(const uint8_t *__res
   ((uint4 *)(out + row * K + 256 * b))[lane] = o;
 }
 
-// out[r] = y[inv[r]]: the experts' rows back in the order they arrived, as f32 or f16. One CTA per row.
-template <class O>
-static __global__ void __launch_bounds__(256) k_unpermute(const float *__restrict__ y, const uint32_t *__restrict__ inv, uint32_t E,
+// out[r] = y[inv[r]]: the experts' rows back in the order they arrived, f32 or f16 on either side. One CTA per row.
+template <class Y, class O>
+static __global__ void __launch_bounds__(256) k_unpermute(const Y *__restrict__ y, const uint32_t *__restrict__ inv, uint32_t E,
                                                          O *__restrict__ out) {
-  const uint64_t r = blockIdx.x;
-  const float4 *src = (const float4 *)(y + (uint64_t)inv[r] * E);
+  const uint64_t r = blockIdx.x, src = inv[r];
   for (uint32_t i = threadIdx.x; i < E / 4; i += 256) {
-    const float4 v = src[i];
-    if constexpr (sizeof(O) == 4) {
-      ((float4 *)(out + r * E))[i] = v;
+    if constexpr (sizeof(Y) == 2 && sizeof(O) == 2) {
+      ((uint2 *)(out + r * E))[i] = ((const uint2 *)(y + src * E))[i];
     } else {
-      const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-      uint2 o;
-      o.x = *(const uint32_t *)&a, o.y = *(const uint32_t *)&b;
-      ((uint2 *)(out + r * E))[i] = o;
+      const float4 v = load_row4(y, src, E, i);
+      if constexpr (sizeof(O) == 4) {
+        ((float4 *)(out + r * E))[i] = v;
+      } else {
+        const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 o;
+        o.x = *(const uint32_t *)&a, o.y = *(const uint32_t *)&b;
+        ((uint2 *)(out + r * E))[i] = o;
+      }
     }
   }
 }

@@ -86,7 +86,7 @@ MOE_API moe_status moe_route_rows_static(const float *x_dev, uint32_t T, uint32_
   const size_t smem = (size_t)8 * kRouterPieces * (n_embd / kRouterPieces + 4) * sizeof(float);
   k_router_logits_rows<8><<<dim3((N + 3) / 4, (T + 7) / 8), 32, smem, st>>>(x_dev, T, n_embd, router_dev, N, bias_dev, n_experts, rl);
   const uint32_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
-  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(rl, nullptr, nullptr, nullptr, 0, T, n_experts, n_used, ids_dev, w_dev, gate_dev, hist);
+  k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(rl, RouterApprox{}, nullptr, T, n_experts, n_used, ids_dev, w_dev, gate_dev, hist);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(MOE_ERROR, std::string("launch failed: ") + cudaGetErrorString(e));
   return MOE_OK;

@@ -9,7 +9,7 @@
 
 namespace moe {
 
-CUtensorMap make_rows_map(const void *base, uint64_t rows, uint32_t K) {
+CUtensorMap make_rows_map(const void *base, uint64_t rows, uint32_t K, uint32_t box_rows) {
   // The encoder is a driver call; its address comes through the runtime, so the library does not link the driver.
   static PFN_cuTensorMapEncodeTiled_v12000 encode = [] {
     void *fn = nullptr;
@@ -21,7 +21,7 @@ CUtensorMap make_rows_map(const void *base, uint64_t rows, uint32_t K) {
   CUtensorMap m{};
   const cuuint64_t dims[2] = {K, rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {64, kMapBoxRows};
+  const cuuint32_t box[2] = {64, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

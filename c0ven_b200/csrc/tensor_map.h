@@ -12,6 +12,7 @@ constexpr uint32_t kMapBoxRows = 64;  // rows one copy brings: a tile of n rows 
 // A map over f16 rows [rows][K] in device memory (base 16-byte aligned, K a multiple of 64) whose copies bring a box of
 // 64 values x 64 rows into shared memory with the 128-byte swizzle, the layout the tensor core reads K-major operands
 // in. Rows past `rows` read as zero. Throws CudaFailure when the driver refuses the map.
-CUtensorMap make_rows_map(const void *base, uint64_t rows, uint32_t K);
+// box_rows: the rows one copy brings, at most 256 (the tensor must be at least that high).
+CUtensorMap make_rows_map(const void *base, uint64_t rows, uint32_t K, uint32_t box_rows = kMapBoxRows);
 
 }  // namespace moe

@@ -1,8 +1,9 @@
 """The expert-parallel stage calls of the C ABI on ONE GPU: two layers, each holding half the experts, play the two
 ranks one after the other, and the all-to-alls between them are plain tensor copies (no process group, no kernel waits
 for another). A rank's outputs must equal, bit for bit, what a layer holding every expert gives for the same rows when
-the results travel as f32 and every expert takes the tile kernels on both sides; and the ids the device derives from
-the gathered counts must be the host function's."""
+every expert takes the tile kernels on both sides and the results travel as f16, the form the one layer keeps them in
+between its down kernel and its combine; and the ids the device derives from the gathered counts must be the host
+function's."""
 import numpy as np
 import pytest
 
@@ -32,7 +33,7 @@ def test_two_ranges_on_one_gpu_match_the_whole_layer(wtype, rows):
     single = MoELayer(layer, max_tokens=512, tensor_min_rows=1)
     want = [single.forward(x) for x in xs]
     single.close()
-    stages = [ep.GpuStages(layer, r, world, max_tokens=512, device=0, y_f16=False, tensor_min_rows=1, profile=True) for r in range(world)]
+    stages = [ep.GpuStages(layer, r, world, max_tokens=512, device=0, y_f16=True, tensor_min_rows=1, profile=True) for r in range(world)]
     try:
         xd = [torch.from_numpy(x).cuda() for x in xs]
         cnts = [st.route(xd[r]) for r, st in enumerate(stages)]
