@@ -217,7 +217,8 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
     for i in range(nlayers):
         lw = base if i == 0 else dict(base, router=(np.random.default_rng(100 + i).standard_normal((NE, E)) * 0.02).astype(np.float32))
         if world == 1:
-            m = MoELayer(lw, max_tokens=T, device=local, profile=False, tensor_min_rows=args.tensor_min)
+            m = MoELayer(lw, max_tokens=T, device=local, profile=False, tensor_min_rows=args.tensor_min,
+                         host_chunk_rows=args.host_chunk if args.host_chunk >= 0 else (8192 if T >= 16384 else 0))
             layers.append(m), moes.append(None)
             main_sp = main_sp or m.stream
         else:
@@ -454,6 +455,8 @@ def main():
     ap.add_argument("--no-second", action="store_true", help="the default workload alone, without the ragged batch beside it")
     ap.add_argument("--layers", type=int, default=0, help="layers instead of the workload's")
     ap.add_argument("--tokens", type=int, default=0, help="rows instead of the workload's (the sweep's points)")
+    ap.add_argument("--host-chunk", type=int, default=-1,
+                    help="rows of a chunk of the host-buffer call, whose copies overlap its neighbours' computation (0: never cut; default: 8192 for batches of 16384 rows and more)")
     ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

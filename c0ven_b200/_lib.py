@@ -17,7 +17,7 @@ SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_la
            "moe_abi_layout", "moe_to_runs", "moe_from_runs",
            "moe_route_rows_static", "moe_route_rows_static_error", "moe_layer_route_device", "moe_layer_read_counts", "moe_layer_counts_device",
            "moe_layer_wire_row_bytes", "moe_layer_received_ids_device", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
-           "moe_layer_combine_device", "moe_layer_read_groups", "moe_layer_read_quantized")
+           "moe_layer_combine_device", "moe_layer_read_groups", "moe_layer_read_quantized", "moe_layer_read_logits")
 
 
 class Config(C.Structure):
@@ -25,7 +25,7 @@ class Config(C.Structure):
                 ("gate_type", C.c_uint32), ("down_type", C.c_uint32), ("shexp_gate_type", C.c_uint32),
                 ("shexp_down_type", C.c_uint32), ("expert_first", C.c_uint32), ("expert_count", C.c_uint32),
                 ("max_tokens", C.c_uint32), ("device", C.c_int32), ("swiglu_limit", C.c_float), ("flags", C.c_uint32),
-                ("tensor_min_rows", C.c_uint32), ("max_expert_rows", C.c_uint32)]
+                ("tensor_min_rows", C.c_uint32), ("max_expert_rows", C.c_uint32), ("host_chunk_rows", C.c_uint32)]
 
 
 class Weights(C.Structure):
@@ -79,6 +79,7 @@ def lib():
         L.moe_layer_read_stats.argtypes = [vp, C.POINTER(Stats)]
         L.moe_layer_read_groups.argtypes = [vp, vp, u32, C.POINTER(u32)]
         L.moe_layer_read_quantized.argtypes = [vp, u32, vp, vp, vp, C.POINTER(u32)]
+        L.moe_layer_read_logits.argtypes = [vp, vp, C.POINTER(u32), C.POINTER(C.c_float), C.POINTER(C.c_float)]
         L.moe_layer_stage_ms.argtypes = [vp, vp]
         L.moe_layer_set_profiling.argtypes = [vp, u32]
         L.moe_layer_stream.argtypes = [vp]

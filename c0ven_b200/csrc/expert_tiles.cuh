@@ -497,7 +497,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   auto is_wide = [&](uint32_t count) { return NMAT == 2 && count > kTileN / 2; };
 
   // Columns q (this warp's quarter of the weight rows: TMEM lanes 32 q ..) of chunks slot, slot + nslots, ... of 16 rows
-  // each, from the accumulators at column colg (and colu, the up product) to the result.
+  // each, from the accumulators at column colg (and colu, the up product) to the result. A lane holds one weight row's
+  // values for the chunk's 16 rows; for each row the warp's 32 lanes store 32 consecutive values. The address of a
+  // chunk is worked out once and stepped by the row stride: what the loop costs per value is a conversion and a store.
   auto drain = [&](const ItemTile &t, uint32_t r0, uint32_t colg, uint32_t colu, uint32_t slot, uint32_t nslots) {
     const uint32_t q = warp % 4, r = r0 + 32 * q + lane, N = (t.count + 15) & ~15u;
     for (uint32_t c = slot; c < N / 16; c += nslots) {
@@ -505,17 +507,33 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       tmem_ld16(tmem_base + ((32 * q) << 16) + colg + 16 * c, gv);
       if constexpr (NMAT == 2) tmem_ld16(tmem_base + ((32 * q) << 16) + colu + 16 * c, uv);
       tmem_ld_wait();
+      float v[16];
 #pragma unroll
       for (int j = 0; j < 16; j++) {
-        const uint32_t n = 16 * c + j;
-        if (n < t.count) {
-          float v = __uint_as_float(gv[j]);
-          if constexpr (NMAT == 2) v = swiglu_fast(v, __uint_as_float(uv[j]), a.limit);
-          const uint64_t at = (uint64_t)(t.start + n) * a.out_stride + r;
-          if (a.out_f16)
-            ((__half *)a.out)[at] = __float2half_rn(v);
-          else
-            ((float *)a.out)[at] = v;
+        v[j] = __uint_as_float(gv[j]);
+        if constexpr (NMAT == 2) v[j] = swiglu_fast(v[j], __uint_as_float(uv[j]), a.limit);
+      }
+      const uint32_t left = t.count - 16 * c;  // rows of the chunk that exist: at least one
+      const uint64_t at = (uint64_t)(t.start + 16 * c) * a.out_stride + r;
+      if (a.out_f16) {
+        __half *p = (__half *)a.out + at;
+        if (left >= 16) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) p[(uint64_t)j * a.out_stride] = __float2half_rn(v[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            if ((uint32_t)j < left) p[(uint64_t)j * a.out_stride] = __float2half_rn(v[j]);
+        }
+      } else {
+        float *p = (float *)a.out + at;
+        if (left >= 16) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) p[(uint64_t)j * a.out_stride] = v[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            if ((uint32_t)j < left) p[(uint64_t)j * a.out_stride] = v[j];
         }
       }
     }
@@ -536,40 +554,50 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       constexpr uint32_t kLineStages = 128 / Dec::kStageBytes;
       constexpr uint32_t kAhead = kLineStages > 6 ? kLineStages : 6 / kLineStages * kLineStages;  // a whole number of lines, about 6 stages
       Raw raw[2][2];  // [buffer][half]
-      // The block's scales: fetched with the first of this thread's stages in the block, used from that stage on.
-      typename Dec::Hdr hdr, hdr_next;
-      uint32_t blk_fetched = 0xFFFFFFFFu, blk_used = 0xFFFFFFFFu;
-      auto fetch = [&](Raw (&r)[2], uint32_t it) {
+      // The block's scales travel with the stage's quants: loaded when a stage is the thread's first in its block, kept
+      // for its later stages there.
+      typename Dec::Hdr hdr[2], hdr_last;
+      uint32_t blk_fetched = 0xFFFFFFFFu;
+      auto fetch = [&](uint32_t b, uint32_t it) {
         const uint32_t k0 = it * kTileK;
-        r[0] = Dec::fetch(wm, nblk, K, r0 + m, k0, 0);
-        r[1] = Dec::fetch(wm, nblk, K, r0 + m, k0, 1);
-        if (k0 / 256 != blk_fetched) hdr_next = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
+        raw[b][0] = Dec::fetch(wm, nblk, K, r0 + m, k0, 0);
+        raw[b][1] = Dec::fetch(wm, nblk, K, r0 + m, k0, 1);
+        if (k0 / 256 != blk_fetched) hdr_last = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
+        hdr[b] = hdr_last;
         // One request a 128-byte line, which holds kLineStages stages of the row.
         if (it % kLineStages == 0 && k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
       };
-      auto stage_step = [&](Raw (&r)[2], uint32_t it) {
+      auto stage_step = [&](uint32_t b, uint32_t it) {
         const uint32_t g = li * KT + it, s = g % S, use_s = g / S, k0 = it * kTileK;
         if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
         if (!ok) return;
         tc_fence_after();
-        if (k0 / 256 != blk_used) hdr = hdr_next, blk_used = k0 / 256;
         uint8_t *tile = smem + s * SM::kStageBytes + mat * SM::kWBytes;
-        Dec::store(hdr, r[0], tile, m, 0, k0, grid);
-        Dec::store(hdr, r[1], tile, m, 1, k0, grid);
+        Dec::store(hdr[b], raw[b][0], tile, m, 0, k0, grid);
+        Dec::store(hdr[b], raw[b][1], tile, m, 1, k0, grid);
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
       };
-      if (first == 0)
-        for (uint32_t p = kLineStages; p < kAhead && p < KT; p += kLineStages) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, p * kTileK, 0));
+      // The first lines of a row's quants are asked for an item ahead (below), so that an item does not begin by
+      // waiting for HBM; the CTA's first item asks for its own.
+      auto ask_ahead = [&](const uint8_t *w, uint32_t row) {
+        for (uint32_t p = 0; p < kAhead && p < KT; p += kLineStages) prefetch_l2(Dec::quants_at(w, nblk, K, row, p * kTileK, 0));
+      };
+      if (first == 0 && li == 0) ask_ahead(wm, r0 + m);
+      const uint32_t item_next = item_at(rnd + 1);
       // This thread's stages: first, first + kDecGroups, ...; the quants of one are loaded while the one before decodes.
-      if (first < KT) fetch(raw[0], first);
+      if (first < KT) fetch(0, first);
       for (uint32_t it = first; it < KT && ok; it += 2 * kDecGroups) {
-        if (it + kDecGroups < KT) fetch(raw[1], it + kDecGroups);
-        stage_step(raw[0], it);
+        if (it + kDecGroups < KT) fetch(1, it + kDecGroups);
+        stage_step(0, it);
+        if (it == 0 && item_next != kNoItem) {  // group 0, after its first stage: the next item's first lines
+          const ItemTile tn = item_tile(a, item_next / RT);
+          ask_ahead((mat == 0 ? a.w0 : a.w1) + (uint64_t)tn.slot * a.slice_bytes, (item_next % RT) * kTileM + m);
+        }
         if (!ok || it + kDecGroups >= KT) break;
-        if (it + 2 * kDecGroups < KT) fetch(raw[0], it + 2 * kDecGroups);
-        stage_step(raw[1], it + kDecGroups);
+        if (it + 2 * kDecGroups < KT) fetch(0, it + 2 * kDecGroups);
+        stage_step(1, it + kDecGroups);
       }
       if (is_wide(t.count)) {
         // Both buffers: the next item's MMAs wait for this epilogue, so these warps take four fifths of it.

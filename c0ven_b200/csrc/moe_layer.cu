@@ -129,6 +129,9 @@ struct moe_layer {
   LaunchCtx ctx;
   std::unique_ptr<Stream> stream, aux;  // aux: the shared expert runs beside the routed ones
   std::unique_ptr<Event> fork_ev, join_ev;
+  // Host-buffer calls cut into chunks: the copies in and out on streams of their own, an event per chunk and direction.
+  std::unique_ptr<Stream> copy_in, copy_out;
+  std::vector<std::unique_ptr<Event>> in_done, comp_done;
   // Steps of few rows are bound by launches, not work: the whole call is recorded once per (rows, buffers, stream)
   // as a CUDA graph and replayed (the reference records its per-width step lists once too: core/ze/ze.h:155-189).
   struct StepGraph {
@@ -501,8 +504,10 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   const uint32_t tm_low = tm && tensor_budget_for(l, R) ? 1 : tm;
   const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
   if (max_big) {
-    // The rows in expert order first: a tile's rows are then one box after another for the kernel's copies. Part of
-    // the pack stage: the gate/up stage times the product's own kernels.
+    // The rows in expert order first (the reference's p_moe_scatter, kernels/models/qwen4exp/prompt.cl:744-754): a tile's
+    // rows are then one box after another for the kernel's copies. Part of the pack stage: the gate/up stage times the
+    // product's own kernels. (Copies that gather four rows by index, cp.async.bulk.tensor's tile::gather4 form, were
+    // measured in its place: 64 copies a stage instead of 4 held the tile kernel to half its rate.)
     k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
     launched(l, cudaGetLastError(), "rows to expert order");
   }
@@ -729,6 +734,7 @@ MOE_API void moe_layer_destroy(moe_layer *l) {
   cudaSetDevice(l->cfg.device);
   if (l->stream) cudaStreamSynchronize(l->stream->get());
   if (l->aux) cudaStreamSynchronize(l->aux->get());
+  if (l->copy_out) cudaStreamSynchronize(l->copy_out->get());
   for (auto &g : l->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
   delete l;
@@ -741,6 +747,34 @@ MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, f
     if (!x || !out || T == 0 || T > l->Tmax) throw BadArgument("x and out are required, and 1 <= T <= max_tokens");
     cudaStream_t st = l->stream->get();
     const size_t bytes = (size_t)T * l->E * sizeof(float);
+    const uint32_t chunk = l->cfg.host_chunk_rows;
+    if (chunk && T >= 2 * chunk && !l->profile && l->local == l->NE) {
+      // Chunks of equal size, about host_chunk_rows each: chunk c's rows come in on one stream while chunk c - 1 is
+      // computed on the layer's and chunk c - 2's results leave on a third.
+      const uint32_t n = T / chunk, rows = (T + n - 1) / n;
+      if (!l->copy_in) l->copy_in = std::make_unique<Stream>(), l->copy_out = std::make_unique<Stream>();
+      while (l->in_done.size() < n) l->in_done.push_back(std::make_unique<Event>()), l->comp_done.push_back(std::make_unique<Event>());
+      for (uint32_t c = 0; c < n; c++) {
+        const uint32_t t0 = c * rows, tn = std::min(rows, T - t0);
+        CUDA_OK(cudaMemcpyAsync(l->x.get() + (size_t)t0 * l->E, x + (size_t)t0 * l->E, (size_t)tn * l->E * sizeof(float), cudaMemcpyHostToDevice,
+                                l->copy_in->get()));
+        l->in_done[c]->record(l->copy_in->get());
+      }
+      for (uint32_t c = 0; c < n; c++) {
+        const uint32_t t0 = c * rows, tn = std::min(rows, T - t0);
+        CUDA_OK(cudaStreamWaitEvent(st, l->in_done[c]->get(), 0));
+        forward_step(l, l->x.get() + (size_t)t0 * l->E, tn, l->out.get() + (size_t)t0 * l->E, st);
+        l->comp_done[c]->record(st);
+        CUDA_OK(cudaStreamWaitEvent(l->copy_out->get(), l->comp_done[c]->get(), 0));
+        CUDA_OK(cudaMemcpyAsync(out + (size_t)t0 * l->E, l->out.get() + (size_t)t0 * l->E, (size_t)tn * l->E * sizeof(float), cudaMemcpyDeviceToHost,
+                                l->copy_out->get()));
+      }
+      l->stats.h2d_bytes += bytes, l->stats.d2h_bytes += bytes;
+      l->copy_out->wait(0);
+      l->stream->wait(0);
+      check_device_error(l);
+      return;
+    }
     CUDA_OK(cudaMemcpyAsync(l->x.get(), x, bytes, cudaMemcpyHostToDevice, st));
     forward_step(l, l->x.get(), T, l->out.get(), st);
     CUDA_OK(cudaMemcpyAsync(out, l->out.get(), bytes, cudaMemcpyDeviceToHost, st));
@@ -958,6 +992,26 @@ MOE_API moe_status moe_layer_read_quantized(moe_layer *l, uint32_t which, int8_t
   });
 }
 
+MOE_API moe_status moe_layer_read_logits(moe_layer *l, float *logits, uint32_t *approximate, float *eps_rel, float *eps_abs) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T == 0) throw BadArgument("no call has run yet");
+    l->stream->wait(0);
+    const bool approx = l->router_tensor && l->last_T > kRouterExactRows;
+    if (logits) {
+      if (approx)
+        CUDA_OK(cudaMemcpy(logits, l->approx.get(), (size_t)l->last_T * l->NE * sizeof(float), cudaMemcpyDeviceToHost));
+      else
+        CUDA_OK(cudaMemcpy2D(logits, l->NE * sizeof(float), l->rl.get(), l->N * sizeof(float), l->NE * sizeof(float), l->last_T,
+                             cudaMemcpyDeviceToHost));
+    }
+    if (approximate) *approximate = approx;
+    if (eps_rel) *eps_rel = approx ? l->router_eps_rel : 0.0f;
+    if (eps_abs) *eps_abs = approx ? l->router_eps_abs : 0.0f;
+  });
+}
+
 MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out) {
   if (!l || !out) return MOE_BAD_ARGUMENT;
   std::lock_guard<std::mutex> lk(l->mu);
@@ -1012,7 +1066,7 @@ MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap) {
       ROW(moe_layer_config, gate_type), ROW(moe_layer_config, down_type), ROW(moe_layer_config, shexp_gate_type),
       ROW(moe_layer_config, shexp_down_type), ROW(moe_layer_config, expert_first), ROW(moe_layer_config, expert_count),
       ROW(moe_layer_config, max_tokens), ROW(moe_layer_config, device), ROW(moe_layer_config, swiglu_limit), ROW(moe_layer_config, flags),
-      ROW(moe_layer_config, tensor_min_rows), ROW(moe_layer_config, max_expert_rows),
+      ROW(moe_layer_config, tensor_min_rows), ROW(moe_layer_config, max_expert_rows), ROW(moe_layer_config, host_chunk_rows),
       ROW(moe_layer_weights, router), ROW(moe_layer_weights, shexp_gate_inp), ROW(moe_layer_weights, router_bias),
       ROW(moe_layer_weights, gate_exps), ROW(moe_layer_weights, up_exps), ROW(moe_layer_weights, down_exps),
       ROW(moe_layer_weights, gate_shexp), ROW(moe_layer_weights, up_shexp), ROW(moe_layer_weights, down_shexp),

@@ -31,7 +31,7 @@ class MoELayer:
 
     def __init__(self, layer: dict, max_tokens: int = 4352, device: int = 0, profile: bool = False,
                  expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0,
-                 max_expert_rows: int = 0):
+                 max_expert_rows: int = 0, host_chunk_rows: int = 0):
         self._h = None
         L = _lib.lib()
         self.n_embd, self.n_ff = layer["n_embd"], layer["n_ff"]
@@ -42,7 +42,7 @@ class MoELayer:
         cfg = _lib.Config(self.n_embd, self.n_ff, self.n_experts, self.n_used, layer["gate_type"], layer["down_type"],
                           layer["shexp_gate_type"] if has_shared else 0, layer["shexp_down_type"] if has_shared else 0,
                           expert_first, count, max_tokens, device, float(layer.get("swiglu_limit", 0.0)),
-                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, max_expert_rows)
+                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, max_expert_rows, host_chunk_rows)
         sl = slice(expert_first, expert_first + count)
         keep = [np.ascontiguousarray(layer["router"], dtype=np.float32),
                 np.ascontiguousarray(layer["shexp_gate_inp"], dtype=np.float32) if has_shared else None,
@@ -122,6 +122,14 @@ class MoELayer:
         bs = np.empty((rows, Kv // 16), dtype=np.int16) if k.value else None
         self._check(_lib.lib().moe_layer_read_quantized(self._h, int(inner), _ptr(q), _ptr(d), _ptr(bs), C.byref(k)))
         return q, d, bs
+
+    def logits(self, T: int):
+        """The last call's router logits [T][n_experts] without the bias, whether they are the tensor-core product's
+        approximate ones, and the bound on their error: eps_rel * |x_t| + eps_abs."""
+        lg = np.empty((T, self.n_experts), dtype=np.float32)
+        ap, er, ea = C.c_uint32(0), C.c_float(0), C.c_float(0)
+        self._check(_lib.lib().moe_layer_read_logits(self._h, _ptr(lg), C.byref(ap), C.byref(er), C.byref(ea)))
+        return lg, bool(ap.value), er.value, ea.value
 
     # Expert parallel, stage by stage (device addresses; queued on `stream`, the layer's own when None).
     def route_device(self, x_ptr: int, T: int, stream=None):

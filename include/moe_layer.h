@@ -23,7 +23,7 @@ extern "C" {
 #define MOE_API
 #endif
 
-#define MOE_API_VERSION 1
+#define MOE_API_VERSION 2
 
 /* engine_status's values (include/engine_api.h:28-34). */
 typedef enum {
@@ -62,6 +62,10 @@ typedef struct {
   uint32_t tensor_min_rows;   /* an expert with at least this many rows in a call goes to the tensor-core kernels, one
                                  with fewer to the integer-dot kernels; default 16 */
   uint32_t max_expert_rows;   /* expert parallel: rows moe_layer_experts_device may receive; default max_tokens * n_used */
+  uint32_t host_chunk_rows;   /* moe_layer_forward (host buffers): calls of at least twice this many rows are cut into
+                                 chunks of about this many, and a chunk's copies to and from the GPU run beside its
+                                 neighbours' computation; a row's output does not depend on the cut, but
+                                 moe_layer_read_route then describes the last chunk only. 0: never cut */
 } moe_layer_config;
 
 #define MOE_FLAG_PROFILE 1u     /* time every stage of a call with events (moe_layer_stage_ms) */
@@ -112,7 +116,8 @@ MOE_API void moe_layer_destroy(moe_layer *l);
 
 /* The block on T rows: out[t] = sum over k of w[t][k] * expert ids[t][k] (x[t]) + sigmoid(gate . x[t]) * shared(x[t]).
  * x and out are HOST buffers of T * n_embd floats; the call copies them to and from the GPU and returns when out is
- * written. */
+ * written. Page-locked buffers let the copies run at the bus's rate and, with host_chunk_rows set, beside the
+ * computation. */
 MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, float *out);
 
 /* The same on DEVICE buffers, queued on the layer's stream (or on stream, a cudaStream_t, when not null); returns
@@ -176,6 +181,15 @@ MOE_API moe_status moe_layer_read_groups(moe_layer *l, moe_group *groups, uint32
  * each 16 codes, untouched for q8_0. *is_q8k says which form. Any pointer may be null. Waits for the stream. */
 MOE_API moe_status moe_layer_read_quantized(moe_layer *l, uint32_t which, int8_t *codes, float *scales, int16_t *sums,
                                             uint32_t *is_q8k);
+
+/* The last call's router logits as its top-k read them, [T][n_experts]. Steps of more than 64 rows
+ * take the router's product (the reference's kernels/gemm.cl:51-115 at prompt.cpp:608) on the tensor cores: then
+ * *approximate is 1, and every logit is within eps_rel * |x_t| + eps_abs of the fp32 logit summed in the fixed order
+ * (|x_t| the row's Euclidean norm); the top-k recomputes in that order whatever the bound leaves undecided, so the
+ * expert ids are those of the fixed order all the same; these logits are without the router's bias. Else *approximate
+ * is 0, the bounds are 0 and the logits are the fixed order's own, bias included. Any pointer may be null. Waits for the
+ * stream. */
+MOE_API moe_status moe_layer_read_logits(moe_layer *l, float *logits, uint32_t *approximate, float *eps_rel, float *eps_abs);
 
 MOE_API moe_status moe_layer_read_stats(moe_layer *l, moe_layer_stats *out);
 /* With MOE_FLAG_PROFILE: the last call's time in each stage, milliseconds, MOE_STAGES floats. Waits for the stream. */

@@ -37,7 +37,7 @@ def test_struct_layouts_match_the_library():
         for (_, end), (start, _) in itertools.pairwise(spans):
             assert end <= start
     assert ctypes.sizeof(_lib.Tile) == 16  # shared/moe_tile.h:18
-    assert ctypes.sizeof(_lib.Config) == 64 and ctypes.sizeof(_lib.Weights) == 72 and ctypes.sizeof(_lib.Stats) == 72
+    assert ctypes.sizeof(_lib.Config) == 68 and ctypes.sizeof(_lib.Weights) == 72 and ctypes.sizeof(_lib.Stats) == 72
 
 
 @pytest.mark.parametrize("t", [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S])
