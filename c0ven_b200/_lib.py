@@ -17,7 +17,8 @@ SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_la
            "moe_abi_layout", "moe_to_runs", "moe_from_runs",
            "moe_route_rows_static", "moe_route_rows_static_error", "moe_layer_route_device", "moe_layer_read_counts", "moe_layer_counts_device",
            "moe_layer_wire_row_bytes", "moe_layer_received_ids_device", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
-           "moe_layer_combine_device", "moe_layer_read_groups", "moe_layer_read_quantized", "moe_layer_read_logits")
+           "moe_layer_combine_device", "moe_layer_read_groups", "moe_layer_read_quantized", "moe_layer_read_logits",
+           "moe_layer_read_config", "moe_gguf_open", "moe_gguf_close", "moe_gguf_layers", "moe_gguf_tensors", "moe_layer_create_from_gguf")
 
 
 class Config(C.Structure):
@@ -42,6 +43,11 @@ class Group(C.Structure):
     _fields_ = [("slot", C.c_uint32), ("start", C.c_uint32), ("n", C.c_uint32)]
 
 
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("type", C.c_uint32), ("n_dims", C.c_uint32), ("shape", C.c_uint64 * 4),
+                ("offset", C.c_uint64), ("bytes", C.c_uint64)]
+
+
 class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("calls", "rows", "assignments", "kernels", "h2d_bytes", "d2h_bytes",
                                           "last_tiles", "last_experts_hit", "last_tensor_rows")]
@@ -51,7 +57,7 @@ class AbiRow(C.Structure):
     _fields_ = [("name", C.c_char_p), ("offset", C.c_uint32), ("size", C.c_uint32)]
 
 
-STRUCTS = {"moe_layer_config": Config, "moe_layer_weights": Weights, "moe_tile": Tile, "moe_group": Group, "moe_layer_stats": Stats,
+STRUCTS = {"moe_gguf_tensor": GgufTensor, "moe_layer_config": Config, "moe_layer_weights": Weights, "moe_tile": Tile, "moe_group": Group, "moe_layer_stats": Stats,
            "moe_abi_row": AbiRow}
 
 _lib = None
@@ -79,6 +85,15 @@ def lib():
         L.moe_layer_read_stats.argtypes = [vp, C.POINTER(Stats)]
         L.moe_layer_read_groups.argtypes = [vp, vp, u32, C.POINTER(u32)]
         L.moe_layer_read_quantized.argtypes = [vp, u32, vp, vp, vp, C.POINTER(u32)]
+        L.moe_layer_read_config.argtypes = [vp, C.POINTER(Config)]
+        L.moe_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+        L.moe_gguf_close.argtypes = [vp]
+        L.moe_gguf_close.restype = None
+        L.moe_gguf_layers.argtypes = [vp]
+        L.moe_gguf_layers.restype = u32
+        L.moe_gguf_tensors.argtypes = [vp, C.POINTER(GgufTensor), u32]
+        L.moe_gguf_tensors.restype = u32
+        L.moe_layer_create_from_gguf.argtypes = [vp, u32, C.POINTER(Config), C.POINTER(vp)]
         L.moe_layer_read_logits.argtypes = [vp, vp, C.POINTER(u32), C.POINTER(C.c_float), C.POINTER(C.c_float)]
         L.moe_layer_stage_ms.argtypes = [vp, vp]
         L.moe_layer_set_profiling.argtypes = [vp, u32]

@@ -18,6 +18,7 @@
 #include "expert_rows.cuh"
 #include "expert_tiles.cuh"
 #include "formats.h"
+#include "internal.h"
 #include "iq3s_grid.h"
 #include "moe_layer.h"
 #include "route_kernels.cuh"
@@ -178,6 +179,10 @@ struct moe_layer {
 };
 
 static thread_local std::string g_create_error;
+
+namespace moe {
+void set_create_error(const std::string &message) { g_create_error = message; }
+}  // namespace moe
 
 namespace {
 
@@ -928,6 +933,13 @@ MOE_API moe_status moe_layer_combine_device(moe_layer *l, const void *y_dev, uin
   });
 }
 
+MOE_API moe_status moe_layer_read_config(const moe_layer *l, moe_layer_config *out) {
+  if (!l || !out) return MOE_BAD_ARGUMENT;
+  *out = l->cfg;
+  out->expert_count = l->local, out->max_tokens = l->Tmax, out->max_expert_rows = (uint32_t)std::min<uint64_t>(l->Rmax, 0xFFFFFFFFu);
+  return MOE_OK;
+}
+
 MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms) {
   if (!l) return MOE_BAD_ARGUMENT;
   return guarded(l, [&] {
@@ -1075,12 +1087,15 @@ MOE_API uint32_t moe_abi_layout(moe_abi_row *table, uint32_t cap) {
       ROW(moe_layer_stats, h2d_bytes), ROW(moe_layer_stats, d2h_bytes), ROW(moe_layer_stats, last_tiles),
       ROW(moe_layer_stats, last_experts_hit), ROW(moe_layer_stats, last_tensor_rows),
       ROW(moe_group, slot), ROW(moe_group, start), ROW(moe_group, n),
+      ROW(moe_gguf_tensor, name), ROW(moe_gguf_tensor, type), ROW(moe_gguf_tensor, n_dims), ROW(moe_gguf_tensor, shape),
+      ROW(moe_gguf_tensor, offset), ROW(moe_gguf_tensor, bytes),
       ROW(moe_abi_row, name), ROW(moe_abi_row, offset), ROW(moe_abi_row, size),
 #undef ROW
       {"moe_layer_config", 0, (uint32_t)sizeof(moe_layer_config)},
       {"moe_layer_weights", 0, (uint32_t)sizeof(moe_layer_weights)},
       {"moe_tile", 0, (uint32_t)sizeof(moe_tile)},
       {"moe_group", 0, (uint32_t)sizeof(moe_group)},
+      {"moe_gguf_tensor", 0, (uint32_t)sizeof(moe_gguf_tensor)},
       {"moe_layer_stats", 0, (uint32_t)sizeof(moe_layer_stats)},
       {"moe_abi_row", 0, (uint32_t)sizeof(moe_abi_row)},
   };

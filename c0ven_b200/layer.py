@@ -20,6 +20,41 @@ def _ptr(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
 
+class GgufFile:
+    """A GGUF file's tensor table, through the library's reader (moe_gguf_*)."""
+
+    def __init__(self, path: str):
+        self._h = None
+        h = C.c_void_p()
+        st = _lib.lib().moe_gguf_open(str(path).encode(), C.byref(h))
+        if st != _lib.MOE_OK:
+            raise MoEError(st, _lib.lib().moe_last_error(None).decode())
+        self._h = h
+
+    @property
+    def layers(self) -> int:
+        return _lib.lib().moe_gguf_layers(self._h)
+
+    def tensors(self) -> dict:
+        """name -> (ggml type, shape in ggml order, offset in the file, bytes)."""
+        L = _lib.lib()
+        n = L.moe_gguf_tensors(self._h, None, 0)
+        rows = (_lib.GgufTensor * n)()
+        L.moe_gguf_tensors(self._h, rows, n)
+        return {r.name.decode(): (r.type, tuple(r.shape[:r.n_dims]), r.offset, r.bytes) for r in rows}
+
+    def close(self):
+        if self._h is not None:
+            _lib.lib().moe_gguf_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class MoELayer:
     """One layer's router, experts and shared expert on one GPU.
 
@@ -58,6 +93,27 @@ class MoELayer:
         if st != _lib.MOE_OK:
             raise MoEError(st, L.moe_last_error(None).decode())
         self._h = h
+
+    @classmethod
+    def from_gguf(cls, gguf: GgufFile, layer: int, n_used: int = 0, max_tokens: int = 4352, device: int = 0, profile: bool = False,
+                  expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0,
+                  max_expert_rows: int = 0, host_chunk_rows: int = 0, swiglu_limit: float = 0.0):
+        """Layer `layer` of an open GGUF file: sizes and types come from its tensors (moe_layer_create_from_gguf)."""
+        L = _lib.lib()
+        cfg = _lib.Config(0, 0, 0, n_used, 0, 0, 0, 0, expert_first, expert_count, max_tokens, device, float(swiglu_limit),
+                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows,
+                          max_expert_rows, host_chunk_rows)
+        h = C.c_void_p()
+        st = L.moe_layer_create_from_gguf(gguf._h, layer, C.byref(cfg), C.byref(h))
+        if st != _lib.MOE_OK:
+            raise MoEError(st, L.moe_last_error(None).decode())
+        self = cls.__new__(cls)
+        self._h = h
+        got = _lib.Config()
+        L.moe_layer_read_config(h, C.byref(got))
+        self.n_embd, self.n_ff, self.n_experts, self.n_used = got.n_embd, got.n_ff, got.n_experts, got.n_used
+        self.max_tokens = got.max_tokens
+        return self
 
     def _check(self, st: int):
         if st != _lib.MOE_OK:

@@ -97,3 +97,46 @@ CONFIGS = {
 def expert_bytes(gate_type: int, down_type: int, n_embd=2048, n_ff=512) -> int:
     """Bytes of one expert's three matrices."""
     return 2 * n_ff * row_bytes(gate_type, n_embd) + n_embd * row_bytes(down_type, n_ff)
+
+
+def write_gguf(path: str, layers: list, arch: str = "qwen4exp", router_type: str = "f32") -> None:
+    """Writes layers (dicts as make_layer returns) as a GGUF version 3 file with the reference's tensor names
+    (blk.N.ffn_gate_inp.weight, ffn_gate_inp_shexp.weight, ffn_{gate,up,down}_exps.weight, ffn_{gate,up,down}_shexp.weight:
+    docs/spec/MODEL_LAYER.md 4.1) and the metadata a reader needs (block_count, expert_count, expert_used_count,
+    embedding_length, expert_feed_forward_length). Needs gguf-py. router_type: "f32", "f16" or "bf16"."""
+    import gguf
+
+    w = gguf.GGUFWriter(str(path), arch)
+    L0 = layers[0]
+    w.add_block_count(len(layers))
+    w.add_embedding_length(L0["n_embd"])
+    w.add_expert_count(L0["n_experts"])
+    w.add_expert_used_count(L0["n_used"])
+    w.add_expert_feed_forward_length(L0["n_ff"])
+    qt = gguf.GGMLQuantizationType
+
+    def plain(a):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        if router_type == "f16":
+            return a.astype(np.float16), None
+        if router_type == "bf16":
+            u = a.view(np.uint32)
+            return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16).view(np.uint8).reshape(a.shape[:-1] + (a.shape[-1] * 2,)), qt.BF16
+        return a, None
+
+    for i, L in enumerate(layers):
+        r, rt = plain(L["router"])
+        w.add_tensor(f"blk.{i}.ffn_gate_inp.weight", r, raw_dtype=rt)
+        for name, key, t in (("ffn_gate_exps", "gate_exps", L["gate_type"]), ("ffn_up_exps", "up_exps", L["gate_type"]),
+                             ("ffn_down_exps", "down_exps", L["down_type"])):
+            w.add_tensor(f"blk.{i}.{name}.weight", np.ascontiguousarray(L[key]), raw_dtype=qt(t))
+        if L.get("gate_shexp") is not None:
+            g, gt = plain(L["shexp_gate_inp"])
+            w.add_tensor(f"blk.{i}.ffn_gate_inp_shexp.weight", g, raw_dtype=gt)
+            for name, key, t in (("ffn_gate_shexp", "gate_shexp", L["shexp_gate_type"]), ("ffn_up_shexp", "up_shexp", L["shexp_gate_type"]),
+                                 ("ffn_down_shexp", "down_shexp", L["shexp_down_type"])):
+                w.add_tensor(f"blk.{i}.{name}.weight", np.ascontiguousarray(L[key]), raw_dtype=qt(t))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()

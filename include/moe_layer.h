@@ -154,6 +154,38 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
 MOE_API moe_status moe_layer_shared_device(moe_layer *l, void *stream);
 MOE_API moe_status moe_layer_combine_device(moe_layer *l, const void *y_dev, uint32_t y_f16, float *out_dev, void *stream);
 
+/* A layer straight from a GGUF file (version 3, one file): the reference reads its layers' tensors through GgufModel
+ * (core/load/gguf.h:13-71) and addresses expert e of blk.N.ffn_{gate,up,down}_exps.weight at the tensor's offset plus
+ * e times the expert's bytes (core/models/qwen4exp/model.cpp:1045-1057); so does this. The file is mapped, not read:
+ * moe_layer_create_from_gguf takes the weights from the mapping and keeps nothing of it.
+ *   moe_gguf_open / _close: the file's header and tensor table. Failures' text: moe_last_error(NULL).
+ *   moe_gguf_layers: "<general.architecture>.block_count", or 0 if the file does not say.
+ *   moe_gguf_tensors: the table, up to cap rows into table (which may be null); returns how many tensors there are.
+ *     name points into the handle and lives as long as it; shape is in ggml's order (shape[0] the contiguous axis);
+ *     offset is from the file's start; bytes is 0 for a type this library does not read.
+ *   moe_layer_create_from_gguf: layer N's blk.N.ffn_gate_inp.weight [n_embd][n_experts] (F32, F16 or BF16),
+ *     ffn_gate_exps, ffn_up_exps [n_embd][n_ff][n_experts], ffn_down_exps [n_ff][n_embd][n_experts] and, when the file
+ *     has them, ffn_gate_inp_shexp [n_embd] with ffn_{gate,up,down}_shexp. The sizes and types come from the tensors;
+ *     of *config the call takes n_used (0: "<architecture>.expert_used_count"), expert_first, expert_count, max_tokens,
+ *     device, swiglu_limit, flags, tensor_min_rows, max_expert_rows and host_chunk_rows. */
+typedef struct moe_gguf moe_gguf;
+typedef struct {
+  const char *name;
+  uint32_t type;    /* ggml type id */
+  uint32_t n_dims;
+  uint64_t shape[4];
+  uint64_t offset;
+  uint64_t bytes;
+} moe_gguf_tensor;
+MOE_API moe_status moe_gguf_open(const char *path, moe_gguf **out);
+MOE_API void moe_gguf_close(moe_gguf *f);
+MOE_API uint32_t moe_gguf_layers(const moe_gguf *f);
+MOE_API uint32_t moe_gguf_tensors(const moe_gguf *f, moe_gguf_tensor *table, uint32_t cap);
+MOE_API moe_status moe_layer_create_from_gguf(const moe_gguf *f, uint32_t layer, const moe_layer_config *config, moe_layer **out);
+
+/* The configuration the layer runs with: the sizes and types it was created with or read from a file, defaults filled in. */
+MOE_API moe_status moe_layer_read_config(const moe_layer *l, moe_layer_config *out);
+
 /* Waits for the layer's stream. MOE_TIMEOUT after timeout_ms (0: 60 s), never an unbounded wait. */
 MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms);
 
