@@ -57,6 +57,7 @@ class DeviceBuffer {
   DeviceBuffer() = default;
   DeviceBuffer(const DeviceBuffer &) = delete;
   DeviceBuffer &operator=(const DeviceBuffer &) = delete;
+  DeviceBuffer(DeviceBuffer &&o) noexcept : p_(o.p_), n_(o.n_) { o.p_ = nullptr, o.n_ = 0; }
   ~DeviceBuffer() { release(); }
   void alloc(size_t n) {
     release();

@@ -137,7 +137,7 @@ struct moe_layer {
   // as a CUDA graph and replayed (the reference records its per-width step lists once too: core/ze/ze.h:155-189).
   struct StepGraph {
     uint32_t T;
-    const float *x;
+    const float *x, *res;
     float *out;
     cudaStream_t st;
     cudaGraphExec_t exec;
@@ -169,6 +169,7 @@ struct moe_layer {
   ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
   bool shared_x_same = true, rows_attr_set = false, shared_on_tensor = false;
   uint32_t last_T = 0, last_tensor_min = 0;
+  const float *residual = nullptr;  // of the call being queued: rows the combine adds last (moe_layer_forward_residual_device)
   PackBuffers *last_pack = nullptr;
   // Profiling: one event before each stage and one after the last.
   std::vector<std::unique_ptr<Event>> ev;
@@ -591,7 +592,8 @@ void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
 template <class Y>
 void stage_combine(moe_layer *l, const Y *y, uint32_t T, float *out, cudaStream_t st) {
   mark(l, ST_COMBINE, st);
-  k_combine<Y><<<T, 256, 0, st>>>(y, l->pack.inv.get(), l->w.get(), l->gs.get(), l->has_shared ? l->s.get() : nullptr, l->K, l->E, out);
+  k_combine<Y><<<T, 256, 0, st>>>(y, l->pack.inv.get(), l->w.get(), l->gs.get(), l->has_shared ? l->s.get() : nullptr, l->K, l->E, out,
+                                  l->residual);
   launched(l, cudaGetLastError(), "combine");
   mark(l, ST_COPIES, st);
 }
@@ -631,7 +633,7 @@ void forward_step(moe_layer *l, const float *x, uint32_t T, float *out, cudaStre
   if (l->profile || !l->graphs_ok || T > kGraphMaxRows || l->local != l->NE) return forward_device(l, x, T, out, st);
   moe_layer::StepGraph *g = nullptr;
   for (auto &c : l->graphs)
-    if (c.T == T && c.x == x && c.out == out && c.st == st) g = &c;
+    if (c.T == T && c.x == x && c.res == l->residual && c.out == out && c.st == st) g = &c;
   if (g && g->exec) {
     CUDA_OK(cudaGraphLaunch(g->exec, st));
     l->stats.kernels += g->kernels, l->stats.calls++, l->stats.rows += T, l->stats.assignments += (uint64_t)T * l->K;
@@ -643,7 +645,7 @@ void forward_step(moe_layer *l, const float *x, uint32_t T, float *out, cudaStre
       if (l->graphs.front().exec) cudaGraphExecDestroy(l->graphs.front().exec);
       l->graphs.erase(l->graphs.begin());
     }
-    l->graphs.push_back(moe_layer::StepGraph{T, x, out, st, nullptr, 0, 1});
+    l->graphs.push_back(moe_layer::StepGraph{T, x, l->residual, out, st, nullptr, 0, 1});
     return forward_device(l, x, T, out, st);
   }
   const moe_layer_stats before = l->stats;
@@ -798,6 +800,26 @@ MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, ui
     need_aligned16({x_dev, out_dev});
     cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
     forward_step(l, x_dev, T, out_dev, st);
+    if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
+  });
+}
+
+MOE_API moe_status moe_layer_forward_residual_device(moe_layer *l, const float *x_dev, uint32_t T, const float *residual_dev,
+                                                     float *out_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!x_dev || !out_dev || !residual_dev || T == 0 || T > l->Tmax) throw BadArgument("x, residual and out are required, and 1 <= T <= max_tokens");
+    need_aligned16({x_dev, residual_dev, out_dev});
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    l->residual = residual_dev;
+    try {
+      forward_step(l, x_dev, T, out_dev, st);
+    } catch (...) {
+      l->residual = nullptr;
+      throw;
+    }
+    l->residual = nullptr;
     if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
   });
 }

@@ -666,7 +666,8 @@ static __global__ void __launch_bounds__(32 * kChunkTokens, 1) k_router_topk_pac
 
 // ---------------------------------------------------------------------------------------------------------------
 // Combine: out[t] = sum over k, in rank order, of w[t][k] * y[inv[t K + k]] + gs[t] * s[t], in f32 (layer.cl:874-877).
-// One CTA per row. y is f32, or f16 when it came back from other GPUs in that form.
+// One CTA per row. y is f32, or f16 when the tile kernels or other GPUs left it in that form. With res set, the row's
+// residual res[t] is added last: a stack's x <- x + block(x) without a kernel of its own.
 __device__ __forceinline__ float4 load_row4(const float *y, uint64_t row, uint32_t E, uint32_t i) { return ((const float4 *)(y + row * E))[i]; }
 __device__ __forceinline__ float4 load_row4(const __half *y, uint64_t row, uint32_t E, uint32_t i) {
   const uint2 u = ((const uint2 *)(y + row * E))[i];
@@ -676,7 +677,8 @@ __device__ __forceinline__ float4 load_row4(const __half *y, uint64_t row, uint3
 template <class Y>
 static __global__ void __launch_bounds__(256) k_combine(const Y *__restrict__ y, const uint32_t *__restrict__ inv,
                                                        const float *__restrict__ w, const float *__restrict__ gs,
-                                                       const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out) {
+                                                       const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out,
+                                                       const float *__restrict__ res) {
   const uint32_t t = blockIdx.x;
   __shared__ uint32_t rows[16];
   __shared__ float wk[16];
@@ -693,6 +695,10 @@ static __global__ void __launch_bounds__(256) k_combine(const Y *__restrict__ y,
     if (s) {
       const float4 v = ((const float4 *)(s + (uint64_t)t * E))[i];
       acc.x = fmaf(g, v.x, acc.x), acc.y = fmaf(g, v.y, acc.y), acc.z = fmaf(g, v.z, acc.z), acc.w = fmaf(g, v.w, acc.w);
+    }
+    if (res) {
+      const float4 v = ((const float4 *)(res + (uint64_t)t * E))[i];
+      acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
     }
     ((float4 *)(out + (uint64_t)t * E))[i] = acc;
   }

@@ -20,6 +20,13 @@ def _ptr(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
 
+def rmsnorm_rows_device(x_ptr: int, weight_ptr: int | None, T: int, n_embd: int, eps: float, out_ptr: int, stream: int | None = None):
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight on device rows (addresses), queued on stream."""
+    st = _lib.lib().moe_rmsnorm_rows_device(x_ptr, weight_ptr, T, n_embd, eps, out_ptr, stream)
+    if st != _lib.MOE_OK:
+        raise MoEError(st, "moe_rmsnorm_rows_device refused its arguments or could not launch")
+
+
 class GgufFile:
     """A GGUF file's tensor table, through the library's reader (moe_gguf_*)."""
 
@@ -143,6 +150,10 @@ class MoELayer:
     def forward_device(self, x_ptr: int, T: int, out_ptr: int, stream: int | None = None):
         """The block on device buffers (addresses), queued without waiting."""
         self._check(_lib.lib().moe_layer_forward_device(self._h, x_ptr, T, out_ptr, stream))
+
+    def forward_residual_device(self, x_ptr: int, T: int, residual_ptr: int, out_ptr: int, stream: int | None = None):
+        """out = residual + block(x) on device buffers (addresses), queued without waiting."""
+        self._check(_lib.lib().moe_layer_forward_residual_device(self._h, x_ptr, T, residual_ptr, out_ptr, stream))
 
     def sync(self, timeout_ms: int = 0):
         self._check(_lib.lib().moe_layer_sync(self._h, timeout_ms))

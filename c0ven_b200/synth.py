@@ -99,11 +99,14 @@ def expert_bytes(gate_type: int, down_type: int, n_embd=2048, n_ff=512) -> int:
     return 2 * n_ff * row_bytes(gate_type, n_embd) + n_embd * row_bytes(down_type, n_ff)
 
 
-def write_gguf(path: str, layers: list, arch: str = "qwen4exp", router_type: str = "f32") -> None:
+def write_gguf(path: str, layers: list, arch: str = "qwen4exp", router_type: str = "f32", token_embd=None, ffn_norms=None,
+               output_norm=None, output=None) -> None:
     """Writes layers (dicts as make_layer returns) as a GGUF version 3 file with the reference's tensor names
     (blk.N.ffn_gate_inp.weight, ffn_gate_inp_shexp.weight, ffn_{gate,up,down}_exps.weight, ffn_{gate,up,down}_shexp.weight:
     docs/spec/MODEL_LAYER.md 4.1) and the metadata a reader needs (block_count, expert_count, expert_used_count,
-    embedding_length, expert_feed_forward_length). Needs gguf-py. router_type: "f32", "f16" or "bf16"."""
+    embedding_length, expert_feed_forward_length). Needs gguf-py. router_type: "f32", "f16" or "bf16". For a whole model
+    (what engine_open reads): token_embd [vocab][n_embd] f32, and optionally ffn_norms (one [n_embd] vector a layer, as
+    blk.N.ffn_norm.weight), output_norm [n_embd] and output [vocab][n_embd] (absent: the embedding is tied)."""
     import gguf
 
     w = gguf.GGUFWriter(str(path), arch)
@@ -124,7 +127,15 @@ def write_gguf(path: str, layers: list, arch: str = "qwen4exp", router_type: str
             return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16).view(np.uint8).reshape(a.shape[:-1] + (a.shape[-1] * 2,)), qt.BF16
         return a, None
 
+    if token_embd is not None:
+        w.add_tensor("token_embd.weight", np.ascontiguousarray(token_embd, dtype=np.float32))
+    if output_norm is not None:
+        w.add_tensor("output_norm.weight", np.ascontiguousarray(output_norm, dtype=np.float32))
+    if output is not None:
+        w.add_tensor("output.weight", np.ascontiguousarray(output, dtype=np.float32))
     for i, L in enumerate(layers):
+        if ffn_norms is not None:
+            w.add_tensor(f"blk.{i}.ffn_norm.weight", np.ascontiguousarray(ffn_norms[i], dtype=np.float32))
         r, rt = plain(L["router"])
         w.add_tensor(f"blk.{i}.ffn_gate_inp.weight", r, raw_dtype=rt)
         for name, key, t in (("ffn_gate_exps", "gate_exps", L["gate_type"]), ("ffn_up_exps", "up_exps", L["gate_type"]),

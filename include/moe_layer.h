@@ -125,6 +125,11 @@ MOE_API moe_status moe_layer_forward(moe_layer *l, const float *x, uint32_t T, f
  * allocations are: the kernels read rows through 16-byte loads, and a pointer that is not is refused with
  * MOE_BAD_ARGUMENT. */
 MOE_API moe_status moe_layer_forward_device(moe_layer *l, const float *x_dev, uint32_t T, float *out_dev, void *stream);
+/* out = residual + block(x): a stack of layers steps x <- x + block(norm(x)) with no kernel between the layers but the
+ * norm (the reference's layers add their block's result into the residual stream likewise,
+ * docs/spec/MODEL_LAYER.md 4.4). out_dev may be residual_dev. */
+MOE_API moe_status moe_layer_forward_residual_device(moe_layer *l, const float *x_dev, uint32_t T, const float *residual_dev,
+                                                     float *out_dev, void *stream);
 
 /* Expert parallel: a layer created with fewer than n_experts experts runs stage by stage, and the caller moves rows
  * between GPUs in between (one process per GPU, an all-to-all for the rows out and one for the results back). The
@@ -182,6 +187,13 @@ MOE_API void moe_gguf_close(moe_gguf *f);
 MOE_API uint32_t moe_gguf_layers(const moe_gguf *f);
 MOE_API uint32_t moe_gguf_tensors(const moe_gguf *f, moe_gguf_tensor *table, uint32_t cap);
 MOE_API moe_status moe_layer_create_from_gguf(const moe_gguf *f, uint32_t layer, const moe_layer_config *config, moe_layer **out);
+
+/* The norm a stack puts in front of each layer's block: out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight (weight null:
+ * ones), rows of n_embd floats (a multiple of 4), DEVICE pointers 16-byte aligned, queued on stream. It is what the
+ * engine behind include/engine_abi.h runs between its layers, exported so that a caller's own stack needs no other
+ * library for it. */
+MOE_API moe_status moe_rmsnorm_rows_device(const float *x_dev, const float *weight_dev, uint32_t T, uint32_t n_embd, float eps, float *out_dev,
+                                           void *stream);
 
 /* The configuration the layer runs with: the sizes and types it was created with or read from a file, defaults filled in. */
 MOE_API moe_status moe_layer_read_config(const moe_layer *l, moe_layer_config *out);
