@@ -18,7 +18,8 @@ SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_la
            "moe_route_rows_static", "moe_route_rows_static_error", "moe_layer_route_device", "moe_layer_read_counts", "moe_layer_counts_device",
            "moe_layer_wire_row_bytes", "moe_layer_received_ids_device", "moe_layer_gather_rows_device", "moe_layer_experts_device", "moe_layer_shared_device",
            "moe_layer_combine_device", "moe_layer_read_groups", "moe_layer_read_quantized", "moe_layer_read_logits",
-           "moe_layer_read_config", "moe_layer_forward_residual_device", "moe_rmsnorm_rows_device", "moe_gguf_open", "moe_gguf_close", "moe_gguf_layers", "moe_gguf_tensors", "moe_layer_create_from_gguf")
+           "moe_layer_read_config", "moe_layer_forward_residual_device", "moe_rmsnorm_rows_device", "moe_layer_dispatch_row_bytes", "moe_layer_dispatch_plan_device", "moe_layer_dispatch_rows_device",
+           "moe_layer_experts_partial_device", "moe_layer_combine_partials_device", "moe_gguf_open", "moe_gguf_close", "moe_gguf_layers", "moe_gguf_tensors", "moe_layer_create_from_gguf")
 
 
 class Config(C.Structure):
@@ -88,6 +89,12 @@ def lib():
         L.moe_layer_read_groups.argtypes = [vp, vp, u32, C.POINTER(u32)]
         L.moe_layer_read_quantized.argtypes = [vp, u32, vp, vp, vp, C.POINTER(u32)]
         L.moe_layer_read_config.argtypes = [vp, C.POINTER(Config)]
+        L.moe_layer_dispatch_row_bytes.argtypes = [vp]
+        L.moe_layer_dispatch_row_bytes.restype = u32
+        L.moe_layer_dispatch_plan_device.argtypes = [vp, vp, vp]
+        L.moe_layer_dispatch_rows_device.argtypes = [vp, vp, vp]
+        L.moe_layer_experts_partial_device.argtypes = [vp, vp, u32, u32, vp, vp]
+        L.moe_layer_combine_partials_device.argtypes = [vp, vp, vp, vp]
         L.moe_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
         L.moe_gguf_close.argtypes = [vp]
         L.moe_gguf_close.restype = None

@@ -166,6 +166,10 @@ struct moe_layer {
   DeviceBuffer<__half> xg;      // the routed experts' activation rows in expert order, f16: what their tile kernel copies from
   CUtensorMap xg_map{};
   PackBuffers pack, pack_local;  // the step's own rows over every expert; the rows received, over this GPU's experts
+  // Expert parallel with one row per (token, GPU): where each token's row goes, and the received rows' lists.
+  DeviceBuffer<uint32_t> dest_pos, dest_chunk_cnt, dest_chunk_asg, dest_totals;
+  DeviceBuffer<float> w_local;
+  uint32_t dest_world = 0;
   ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
   bool shared_x_same = true, rows_attr_set = false, shared_on_tensor = false;
   uint32_t last_T = 0, last_tensor_min = 0;
@@ -928,6 +932,116 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
     else
       k_unpermute<float, float><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), E, (float *)y_dev);
     launched(l, cudaGetLastError(), "rows back in arrival order");
+  });
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Expert parallel with one row per (token, GPU) on the way out and one weighted partial sum per (token, GPU) back.
+
+MOE_API uint32_t moe_layer_dispatch_row_bytes(const moe_layer *l) { return l ? dispatch_row_bytes(act_is_q8k(l->cfg.gate_type), l->E) : 0; }
+
+MOE_API moe_status moe_layer_dispatch_plan_device(moe_layer *l, uint32_t *totals_dev, void *stream) {
+  if (!l || !totals_dev) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->last_T == 0) throw BadArgument("after moe_layer_route_device");
+    const uint32_t world = l->NE / l->local;
+    if (l->local * world != l->NE || world > kMaxWorld || l->cfg.expert_first % l->local)
+      throw BadArgument("the GPUs must hold equal contiguous ranges of the experts, eight GPUs at most");
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    const uint32_t T = l->last_T, nchunks = (T + kDestChunk - 1) / kDestChunk;
+    if (!l->dest_pos.get()) {
+      const uint32_t most = (l->Tmax + kDestChunk - 1) / kDestChunk;
+      l->dest_pos.alloc((size_t)l->Tmax * kMaxWorld), l->dest_chunk_cnt.alloc(most * kMaxWorld), l->dest_chunk_asg.alloc(most * kMaxWorld);
+      l->dest_totals.alloc(2 * kMaxWorld);
+    }
+    l->dest_world = world;
+    k_dest_count<<<nchunks, kDestChunk, 0, st>>>(l->ids.get(), T, l->K, l->local, l->dest_chunk_cnt.get(), l->dest_chunk_asg.get());
+    launched(l, cudaGetLastError(), "destination counts");
+    k_dest_fill<<<nchunks, kDestChunk, 0, st>>>(l->ids.get(), T, l->K, l->local, l->dest_chunk_cnt.get(), l->dest_chunk_asg.get(), nchunks,
+                                                l->dest_pos.get(), l->dest_totals.get());
+    launched(l, cudaGetLastError(), "destination places");
+    CUDA_OK(cudaMemcpyAsync(totals_dev, l->dest_totals.get(), 2 * kMaxWorld * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
+  });
+}
+
+MOE_API moe_status moe_layer_dispatch_rows_device(moe_layer *l, void *rows_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!rows_dev || l->last_T == 0 || !l->dest_world) throw BadArgument("rows are required, after moe_layer_dispatch_plan_device");
+    need_aligned16({rows_dev});
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    const uint64_t pairs = (uint64_t)l->last_T * l->dest_world;
+    k_dispatch_rows<<<(unsigned)((pairs + 7) / 8), 256, 0, st>>>(l->xq_routed.view(), l->E, l->xq_routed.q8k, l->ids.get(), l->w.get(),
+                                                                l->dest_pos.get(), l->dest_totals.get(), l->last_T, l->K, l->local, l->dest_world,
+                                                                (uint8_t *)rows_dev);
+    launched(l, cudaGetLastError(), "rows by destination");
+  });
+}
+
+MOE_API moe_status moe_layer_experts_partial_device(moe_layer *l, const void *rows_dev, uint32_t R, uint32_t assignments, void *y_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (l->local == l->NE) throw BadArgument("this layer holds every expert: use moe_layer_forward_device");
+    if (R == 0) return;
+    if (!rows_dev || !y_dev) throw BadArgument("rows and y are required");
+    need_aligned16({rows_dev, y_dev});
+    const uint64_t entries = (uint64_t)R * l->K;
+    const uint64_t A = std::min<uint64_t>(assignments ? assignments : entries, entries);  // the rows' assignments: an upper bound will do
+    if (entries > l->Rmax) throw BadArgument("more rows than max_expert_rows allows (rows x n_used entries)");
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    const uint32_t E = l->E, K = l->K, nexp = l->local;
+    const bool q8k = l->xq_routed.q8k;
+    const uint32_t wb = wire_row_bytes(q8k, E), wb2 = wb + kMetaBytes, tm = tensor_min_for(l, A);
+    if (!l->w_local.get()) l->w_local.alloc(l->Rmax);
+    const uint8_t *wire = (const uint8_t *)rows_dev;
+    k_meta_unpack<<<(unsigned)((entries + 255) / 256), 256, 0, st>>>(wire, R, wb, K, l->cfg.expert_first, l->ids_local.get(), l->w_local.get());
+    launched(l, cudaGetLastError(), "received lists");
+    // Sort the entries by expert among this GPU's experts (entries with no expert fall out): row_src = the entry's row.
+    PackBuffers &pk = l->pack_local;
+    const uint32_t nchunks = (uint32_t)((entries + kLocalChunk - 1) / kLocalChunk);
+    k_chunk_hist<<<nchunks, 256, 0, st>>>(l->ids_local.get(), (uint32_t)entries, kLocalChunk, nexp, l->cfg.expert_first, pk.chunk_hist.get());
+    launched(l, cudaGetLastError(), "local counts");
+    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, tensor_budget_for(l, A), group_cap(A, nexp), pk.out());
+    launched(l, cudaGetLastError(), "local pack scan");
+    k_pack_fill<<<nchunks, 512, kLocalChunk * sizeof(int32_t), st>>>(l->ids_local.get(), (uint32_t)entries, kLocalChunk, nexp, pk.base.get(),
+                                                                 pk.chunk_off.get(), K, pk.inv.get(), pk.row_src.get(), l->cfg.expert_first);
+    launched(l, cudaGetLastError(), "local pack fill");
+    const uint32_t dbytes = q8k ? E / 64 : E / 8;
+    ActSource src{ActView{(const int8_t *)wire, (const float *)(wire + E), (const int16_t *)(wire + E + dbytes), wb2, wb2, wb2}, nullptr,
+                  pk.row_src.get()};
+    if (tm) {
+      const uint64_t nblk = (uint64_t)R * (E / 256);
+      k_wire_to_f16<<<(unsigned)((nblk + 7) / 8), 256, 0, st>>>(wire, E, q8k, nblk, l->wire_h.get(), wb2);
+      launched(l, cudaGetLastError(), "wire rows to f16");
+      src.h = l->wire_h.get();
+    }
+    l->last_pack = &pk;
+    const bool y16 = results_f16(l, tm);
+    stage_experts(l, src, pk, A, A, tm, l->y.get(), y16, st);
+    if (y16)
+      k_combine_partial<__half><<<R, 256, 0, st>>>((const __half *)l->y.get(), pk.inv.get(), l->ids_local.get(), l->w_local.get(), K, E, (__half *)y_dev);
+    else
+      k_combine_partial<float><<<R, 256, 0, st>>>(l->y.get(), pk.inv.get(), l->ids_local.get(), l->w_local.get(), K, E, (__half *)y_dev);
+    launched(l, cudaGetLastError(), "partial sums");
+  });
+}
+
+MOE_API moe_status moe_layer_combine_partials_device(moe_layer *l, const void *back_dev, float *out_dev, void *stream) {
+  if (!l) return MOE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lk(l->mu);
+  return guarded(l, [&] {
+    if (!back_dev || !out_dev || l->last_T == 0 || !l->dest_world) throw BadArgument("the returned rows and out are required, after moe_layer_dispatch_plan_device");
+    need_aligned16({back_dev, out_dev});
+    cudaStream_t st = stream ? (cudaStream_t)stream : l->stream->get();
+    mark(l, ST_COMBINE, st);
+    k_combine_home<<<l->last_T, 256, 0, st>>>((const __half *)back_dev, l->dest_pos.get(), l->dest_totals.get(), l->gs.get(),
+                                             l->has_shared ? l->s.get() : nullptr, l->residual, l->dest_world, l->E, out_dev);
+    launched(l, cudaGetLastError(), "combine of the GPUs' sums");
+    mark(l, ST_COPIES, st);
+    if (l->profile) l->ev[MOE_STAGES]->record(st), l->ev_valid = true;
   });
 }
 

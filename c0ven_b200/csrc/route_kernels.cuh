@@ -250,12 +250,14 @@ __device__ __forceinline__ float exact_logits4(const float *__restrict__ x, cons
   const uint32_t piece = E / kRouterPieces, s = lane % 8;
   const float4 *xp = (const float4 *)(x + s * piece), *wp = (const float4 *)(W + (uint64_t)e * E + s * piece);
   float p = 0.0f;
-  for (uint32_t i = 0; i < piece / 4; i += 4) {
-    float4 xv[4], wv[4];
+  // Eight loads of each operand in flight a lane: the chain of multiply-adds is short beside a trip to memory, so the
+  // pass costs about piece / 32 such trips.
+  for (uint32_t i = 0; i < piece / 4; i += 8) {
+    float4 xv[8], wv[8];
 #pragma unroll
-    for (int j = 0; j < 4; j++) xv[j] = __ldg(xp + i + j), wv[j] = __ldg(wp + i + j);
+    for (int j = 0; j < 8; j++) xv[j] = __ldg(xp + i + j), wv[j] = __ldg(wp + i + j);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < 8; j++) {
       p = fmaf(xv[j].x, wv[j].x, p);
       p = fmaf(xv[j].y, wv[j].y, p);
       p = fmaf(xv[j].z, wv[j].z, p);
@@ -289,6 +291,11 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
     uint32_t key[kMaxPerLane];
     float mx = -INFINITY, eps2 = 0.0f;  // eps2: twice the row's error bound; 0 with exact logits
     bool finite = true;
+    if (ap.logits) {
+      // The row itself is wanted only if some logits have to be recomputed, but then at once: ask for it now.
+      const char *row = (const char *)(ap.x + (uint64_t)t * ap.E);
+      for (uint32_t b = lane * 128; b < ap.E * 4; b += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + b));
+    }
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; j++) {
       key[j] = 0;
@@ -732,12 +739,12 @@ static __global__ void __launch_bounds__(256) k_gather_wire(const ActView act, u
 }
 
 // The f16 operand of the tensor-core kernels from wire rows: code * scale, as the quantisers write it. One warp per
-// 256 values.
+// 256 values. row_stride: bytes from a row to the next when they carry more than the row itself (0: none).
 static __global__ void __launch_bounds__(256) k_wire_to_f16(const uint8_t *__restrict__ wire, uint32_t K, bool q8k, uint64_t nblk256,
-                                                           __half *__restrict__ out) {
+                                                           __half *__restrict__ out, uint32_t row_stride = 0) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
-  const uint32_t lane = threadIdx.x % 32, per_row = K / 256, wb = wire_row_bytes(q8k, K);
+  const uint32_t lane = threadIdx.x % 32, per_row = K / 256, wb = row_stride ? row_stride : wire_row_bytes(q8k, K);
   const uint64_t row = blk / per_row;
   const uint32_t b = (uint32_t)(blk % per_row);
   const uint8_t *src = wire + row * wb;
@@ -748,6 +755,195 @@ static __global__ void __launch_bounds__(256) k_wire_to_f16(const uint8_t *__res
   uint4 o;
   o.x = *(const uint32_t *)&h0, o.y = *(const uint32_t *)&h1, o.z = *(const uint32_t *)&h2, o.w = *(const uint32_t *)&h3;
   ((uint4 *)(out + row * K + 256 * b))[lane] = o;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Expert parallel with one row per (token, GPU). A token's K experts live on a few GPUs (about 5.9 of 8, 2.0 of 2 for
+// K = 10 and even routing), so a token's quantised row travels once to each GPU that holds any of its experts, with the
+// list of those experts and their routing weights beside it; the GPU returns one row, the weighted sum of its experts'
+// results for the token. GPUs own contiguous ranges of `per` experts.
+constexpr uint32_t kMaxWorld = 8;
+constexpr uint32_t kDestChunk = 256;                   // tokens a CTA plans
+constexpr uint32_t kMetaBytes = 2 * 16 + 4 * 16;       // a travelling row's list: 16 u16 local expert ids, 16 f32 weights
+__host__ __device__ constexpr uint32_t dispatch_row_bytes(bool q8k, uint32_t K) { return wire_row_bytes(q8k, K) + kMetaBytes; }
+
+// Per chunk of tokens: how many of them go to each GPU, and how many assignments go with them.
+static __global__ void __launch_bounds__(kDestChunk) k_dest_count(const int32_t *__restrict__ ids, uint32_t T, uint32_t K, uint32_t per,
+                                                                uint32_t *__restrict__ chunk_cnt, uint32_t *__restrict__ chunk_asg) {
+  __shared__ uint32_t rows[kMaxWorld], asg[kMaxWorld];
+  if (threadIdx.x < kMaxWorld) rows[threadIdx.x] = 0, asg[threadIdx.x] = 0;
+  __syncthreads();
+  const uint32_t t = blockIdx.x * kDestChunk + threadIdx.x;
+  if (t < T) {
+    uint32_t mask = 0;
+    for (uint32_t k = 0; k < K; k++) {
+      const uint32_t g = (uint32_t)ids[(uint64_t)t * K + k] / per;
+      atomicAdd(&asg[g], 1u);
+      mask |= 1u << g;
+    }
+    for (uint32_t g = 0; g < kMaxWorld; g++)
+      if (mask >> g & 1) atomicAdd(&rows[g], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x < kMaxWorld) {
+    chunk_cnt[blockIdx.x * kMaxWorld + threadIdx.x] = rows[threadIdx.x];
+    chunk_asg[blockIdx.x * kMaxWorld + threadIdx.x] = asg[threadIdx.x];
+  }
+}
+
+// pos[t][g] = the place of token t's row among those this GPU sends to GPU g, in token order, or 0xFFFFFFFF when none
+// of its experts lives there. totals[g] = rows for GPU g, totals[kMaxWorld + g] = assignments for it (written by CTA 0).
+static __global__ void __launch_bounds__(kDestChunk) k_dest_fill(const int32_t *__restrict__ ids, uint32_t T, uint32_t K, uint32_t per,
+                                                               const uint32_t *__restrict__ chunk_cnt, const uint32_t *__restrict__ chunk_asg,
+                                                               uint32_t nchunks, uint32_t *__restrict__ pos, uint32_t *__restrict__ totals) {
+  __shared__ uint32_t base[kMaxWorld], warp_cnt[kDestChunk / 32][kMaxWorld], tot[2 * kMaxWorld];
+  if (threadIdx.x < kMaxWorld) base[threadIdx.x] = 0;
+  if (threadIdx.x < 2 * kMaxWorld) tot[threadIdx.x] = 0;
+  __syncthreads();
+  // The chunks before this one (and, for CTA 0, all of them for the totals).
+  for (uint32_t i = threadIdx.x; i < nchunks * kMaxWorld; i += kDestChunk) {
+    const uint32_t c = i / kMaxWorld, g = i % kMaxWorld;
+    if (c < blockIdx.x && chunk_cnt[i]) atomicAdd(&base[g], chunk_cnt[i]);
+    if (blockIdx.x == 0) atomicAdd(&tot[g], chunk_cnt[i]), atomicAdd(&tot[kMaxWorld + g], chunk_asg[i]);
+  }
+  const uint32_t t = blockIdx.x * kDestChunk + threadIdx.x, lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  uint32_t mask = 0;
+  if (t < T)
+    for (uint32_t k = 0; k < K; k++) mask |= 1u << ((uint32_t)ids[(uint64_t)t * K + k] / per);
+  uint32_t rank[kMaxWorld];
+#pragma unroll
+  for (uint32_t g = 0; g < kMaxWorld; g++) {
+    const uint32_t b = __ballot_sync(0xffffffffu, mask >> g & 1);
+    rank[g] = __popc(b & ((1u << lane) - 1));
+    if (lane == 0) warp_cnt[warp][g] = __popc(b);
+  }
+  __syncthreads();
+  if (t < T) {
+#pragma unroll
+    for (uint32_t g = 0; g < kMaxWorld; g++) {
+      uint32_t before = base[g];
+      for (uint32_t w = 0; w < warp; w++) before += warp_cnt[w][g];
+      pos[(uint64_t)t * kMaxWorld + g] = (mask >> g & 1) ? before + rank[g] : 0xFFFFFFFFu;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < 2 * kMaxWorld) totals[threadIdx.x] = tot[threadIdx.x];
+}
+
+// The travelling rows, destination by destination (GPU 0's first), each destination's in token order: the token's
+// quantised row as k_gather_wire lays it, then its experts on that GPU as local indices (0xFFFF: none) in rank order,
+// then their routing weights. One warp per (token, GPU).
+static __global__ void __launch_bounds__(256) k_dispatch_rows(const ActView act, uint32_t E, bool q8k, const int32_t *__restrict__ ids,
+                                                             const float *__restrict__ w, const uint32_t *__restrict__ pos,
+                                                             const uint32_t *__restrict__ totals, uint32_t T, uint32_t K, uint32_t per,
+                                                             uint32_t world, uint8_t *__restrict__ out) {
+  const uint32_t lane = threadIdx.x % 32;
+  const uint64_t pair = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
+  if (pair >= (uint64_t)T * world) return;
+  const uint32_t t = (uint32_t)(pair / world), g = (uint32_t)(pair % world), p = pos[(uint64_t)t * kMaxWorld + g];
+  if (p == 0xFFFFFFFFu) return;
+  uint32_t first = 0;
+  for (uint32_t i = 0; i < g; i++) first += totals[i];
+  const uint32_t wb = wire_row_bytes(q8k, E), dbytes = q8k ? E / 64 : E / 8;
+  uint8_t *dst = out + (uint64_t)(first + p) * (wb + kMetaBytes);
+  const int4 *q = (const int4 *)(act.q + (uint64_t)t * act.q_stride);
+  for (uint32_t i = lane; i < E / 16; i += 32) ((int4 *)dst)[i] = q[i];
+  const uint32_t *d = (const uint32_t *)((const uint8_t *)act.d + (uint64_t)t * act.d_stride);
+  for (uint32_t i = lane; i < dbytes / 4; i += 32) ((uint32_t *)(dst + E))[i] = d[i];
+  if (q8k) {
+    const uint32_t *b = (const uint32_t *)((const uint8_t *)act.bs + (uint64_t)t * act.bs_stride);
+    for (uint32_t i = lane; i < E / 32; i += 32) ((uint32_t *)(dst + E + dbytes))[i] = b[i];
+  }
+  if (lane < 16) {
+    uint32_t local = 0xFFFFu;
+    float wk = 0.0f;
+    if (lane < K) {
+      const uint32_t e = (uint32_t)ids[(uint64_t)t * K + lane];
+      if (e / per == g) local = e % per, wk = w[(uint64_t)t * K + lane];
+    }
+    ((uint16_t *)(dst + wb))[lane] = (uint16_t)local;
+    ((float *)(dst + wb + 32))[lane] = wk;
+  }
+}
+
+// The lists of the rows received, flattened: ids[r * K + k] = first_expert + the local index, or -1 for no expert;
+// w[r * K + k] its weight. One thread per entry.
+static __global__ void __launch_bounds__(256) k_meta_unpack(const uint8_t *__restrict__ rows, uint64_t R, uint32_t wb, uint32_t K,
+                                                           uint32_t first_expert, int32_t *__restrict__ ids, float *__restrict__ w) {
+  const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= R * K) return;
+  const uint8_t *meta = rows + (i / K) * (wb + kMetaBytes) + wb;
+  const uint32_t local = ((const uint16_t *)meta)[i % K];
+  ids[i] = local == 0xFFFFu ? -1 : (int32_t)(first_expert + local);
+  w[i] = ((const float *)(meta + 32))[i % K];
+}
+
+// What a GPU returns for a received row: the weighted sum of its experts' results for the row, in the row's rank
+// order, f32 accumulate, as f16. One CTA per row.
+template <class Y>
+static __global__ void __launch_bounds__(256) k_combine_partial(const Y *__restrict__ y, const uint32_t *__restrict__ inv,
+                                                               const int32_t *__restrict__ ids, const float *__restrict__ w, uint32_t K,
+                                                               uint32_t E, __half *__restrict__ out) {
+  const uint64_t r = blockIdx.x;
+  __shared__ uint32_t rows[16];
+  __shared__ float wk[16];
+  __shared__ uint32_t n;
+  if (threadIdx.x == 0) {
+    uint32_t m = 0;
+    for (uint32_t k = 0; k < K; k++)
+      if (ids[r * K + k] >= 0) rows[m] = inv[r * K + k], wk[m] = w[r * K + k], m++;
+    n = m;
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < E / 4; i += 256) {
+    float4 acc = make_float4(0, 0, 0, 0);
+    for (uint32_t k = 0; k < n; k++) {
+      const float4 v = load_row4(y, rows[k], E, i);
+      acc.x = fmaf(wk[k], v.x, acc.x), acc.y = fmaf(wk[k], v.y, acc.y);
+      acc.z = fmaf(wk[k], v.z, acc.z), acc.w = fmaf(wk[k], v.w, acc.w);
+    }
+    const __half2 a = __floats2half2_rn(acc.x, acc.y), b = __floats2half2_rn(acc.z, acc.w);
+    uint2 o;
+    o.x = *(const uint32_t *)&a, o.y = *(const uint32_t *)&b;
+    ((uint2 *)(out + r * E))[i] = o;
+  }
+}
+
+// At home: out[t] = the GPUs' partial sums for token t added in GPU order, + gs[t] * s[t] (+ res[t]). back holds the
+// rows as they were sent: destination by destination. One CTA per token.
+static __global__ void __launch_bounds__(256) k_combine_home(const __half *__restrict__ back, const uint32_t *__restrict__ pos,
+                                                            const uint32_t *__restrict__ totals, const float *__restrict__ gs,
+                                                            const float *__restrict__ s, const float *__restrict__ res, uint32_t world,
+                                                            uint32_t E, float *__restrict__ out) {
+  const uint32_t t = blockIdx.x;
+  __shared__ uint32_t rows[kMaxWorld];
+  __shared__ uint32_t n;
+  if (threadIdx.x == 0) {
+    uint32_t m = 0, first = 0;
+    for (uint32_t g = 0; g < world; g++) {
+      const uint32_t p = pos[(uint64_t)t * kMaxWorld + g];
+      if (p != 0xFFFFFFFFu) rows[m++] = first + p;
+      first += totals[g];
+    }
+    n = m;
+  }
+  __syncthreads();
+  const float g = s ? gs[t] : 0.0f;
+  for (uint32_t i = threadIdx.x; i < E / 4; i += 256) {
+    float4 acc = make_float4(0, 0, 0, 0);
+    for (uint32_t k = 0; k < n; k++) {
+      const float4 v = load_row4(back, rows[k], E, i);
+      acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+    }
+    if (s) {
+      const float4 v = ((const float4 *)(s + (uint64_t)t * E))[i];
+      acc.x = fmaf(g, v.x, acc.x), acc.y = fmaf(g, v.y, acc.y), acc.z = fmaf(g, v.z, acc.z), acc.w = fmaf(g, v.w, acc.w);
+    }
+    if (res) {
+      const float4 v = ((const float4 *)(res + (uint64_t)t * E))[i];
+      acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+    }
+    ((float4 *)(out + (uint64_t)t * E))[i] = acc;
+  }
 }
 
 // out[r] = y[inv[r]]: the experts' rows back in the order they arrived, f32 or f16 on either side. One CTA per row.

@@ -73,7 +73,9 @@ class MoELayer:
 
     def __init__(self, layer: dict, max_tokens: int = 4352, device: int = 0, profile: bool = False,
                  expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0,
-                 max_expert_rows: int = 0, host_chunk_rows: int = 0):
+                 max_expert_rows: int = 0, host_chunk_rows: int = 0, own_experts=None):
+        """own_experts: this GPU's experts' (gate, up, down) arrays, [expert_count][rows][row bytes] each, when they are
+        not the slice [expert_first, expert_first + expert_count) of the layer's own arrays."""
         self._h = None
         L = _lib.lib()
         self.n_embd, self.n_ff = layer["n_embd"], layer["n_ff"]
@@ -86,11 +88,13 @@ class MoELayer:
                           expert_first, count, max_tokens, device, float(layer.get("swiglu_limit", 0.0)),
                           (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, max_expert_rows, host_chunk_rows)
         sl = slice(expert_first, expert_first + count)
+        ge, ue, de = own_experts if own_experts is not None else (layer["gate_exps"][sl], layer["up_exps"][sl], layer["down_exps"][sl])
+        if len(ge) != count or len(ue) != count or len(de) != count:
+            raise ValueError("the experts' arrays must hold expert_count experts")
         keep = [np.ascontiguousarray(layer["router"], dtype=np.float32),
                 np.ascontiguousarray(layer["shexp_gate_inp"], dtype=np.float32) if has_shared else None,
                 np.ascontiguousarray(layer["router_bias"], dtype=np.float32) if layer.get("router_bias") is not None else None,
-                np.ascontiguousarray(layer["gate_exps"][sl]), np.ascontiguousarray(layer["up_exps"][sl]),
-                np.ascontiguousarray(layer["down_exps"][sl]),
+                np.ascontiguousarray(ge), np.ascontiguousarray(ue), np.ascontiguousarray(de),
                 np.ascontiguousarray(layer["gate_shexp"]) if has_shared else None,
                 np.ascontiguousarray(layer["up_shexp"]) if has_shared else None,
                 np.ascontiguousarray(layer["down_shexp"]) if has_shared else None]
@@ -228,6 +232,23 @@ class MoELayer:
 
     def combine_device(self, y_ptr: int, y_f16: bool, out_ptr: int, stream=None):
         self._check(_lib.lib().moe_layer_combine_device(self._h, y_ptr, int(y_f16), out_ptr, stream))
+
+    # Expert parallel with one row per (token, GPU).
+    @property
+    def dispatch_row_bytes(self) -> int:
+        return _lib.lib().moe_layer_dispatch_row_bytes(self._h)
+
+    def dispatch_plan_device(self, totals_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_dispatch_plan_device(self._h, totals_ptr, stream))
+
+    def dispatch_rows_device(self, rows_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_dispatch_rows_device(self._h, rows_ptr, stream))
+
+    def experts_partial_device(self, rows_ptr: int, R: int, assignments: int, y_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_experts_partial_device(self._h, rows_ptr, R, assignments, y_ptr, stream))
+
+    def combine_partials_device(self, back_ptr: int, out_ptr: int, stream=None):
+        self._check(_lib.lib().moe_layer_combine_partials_device(self._h, back_ptr, out_ptr, stream))
 
     def stats(self) -> dict:
         s = _lib.Stats()

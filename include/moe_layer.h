@@ -198,6 +198,29 @@ MOE_API moe_status moe_rmsnorm_rows_device(const float *x_dev, const float *weig
 /* The configuration the layer runs with: the sizes and types it was created with or read from a file, defaults filled in. */
 MOE_API moe_status moe_layer_read_config(const moe_layer *l, moe_layer_config *out);
 
+/* Expert parallel with fewer bytes on the wire: one row per (token, GPU) instead of one per assignment. A token's
+ * n_used experts live on a few GPUs (for 10 of 512: all of 2, 3.8 of 4, 5.9 of 8 on average), so its quantised row
+ * travels once to each GPU that holds any of them, with the list of those experts and their routing weights beside it,
+ * and each GPU returns one row: the weighted sum of its experts' results for the token, in the token's rank order, as
+ * f16. At home the GPUs' sums are added in GPU order, then the shared expert's gated result. The sum over a token's
+ * experts is thus taken GPU by GPU, not in one pass over its ranks: outputs agree with one GPU's within the layer's
+ * tolerance, not bit for bit (the per-assignment calls above keep that). GPUs hold equal contiguous expert ranges.
+ *   dispatch_plan:  after route. For every token the GPUs its experts live on; totals_dev (DEVICE, 16 words) receives
+ *                   the rows this GPU sends to GPUs 0 .. 7 and then the assignments that go with them: what the
+ *                   all-to-all's split sizes are made of.
+ *   dispatch_rows:  rows_dev (DEVICE) receives the travelling rows, moe_layer_dispatch_row_bytes each, destination by
+ *                   destination, each destination's in token order.
+ *   experts_partial: R rows received (any order), `assignments` experts listed in them in all (0: unknown; an upper
+ *                   bound will do); y_dev [R][n_embd] f16 receives the weighted sums, in the order received.
+ *   combine_partials: back_dev holds the sums for the rows this GPU sent, in the order it sent them;
+ *                   out[t] = the GPUs' sums for t + gate[t] * shared[t]. */
+MOE_API uint32_t moe_layer_dispatch_row_bytes(const moe_layer *l);
+MOE_API moe_status moe_layer_dispatch_plan_device(moe_layer *l, uint32_t *totals_dev, void *stream);
+MOE_API moe_status moe_layer_dispatch_rows_device(moe_layer *l, void *rows_dev, void *stream);
+MOE_API moe_status moe_layer_experts_partial_device(moe_layer *l, const void *rows_dev, uint32_t R, uint32_t assignments, void *y_dev,
+                                                    void *stream);
+MOE_API moe_status moe_layer_combine_partials_device(moe_layer *l, const void *back_dev, float *out_dev, void *stream);
+
 /* Waits for the layer's stream. MOE_TIMEOUT after timeout_ms (0: 60 s), never an unbounded wait. */
 MOE_API moe_status moe_layer_sync(moe_layer *l, uint32_t timeout_ms);
 

@@ -40,6 +40,67 @@ class OracleStages:
         y = O.compute_many(L["gate_type"], L["down_type"], self.E, self.F, jobs, x) if R else np.zeros((0, self.E), np.float32)
         return torch.from_numpy(y)
 
+    # One row per (token, GPU): the same four stages on the CPU. A travelling row is the f32 row, then K int32 expert
+    # ids (-1: not on that GPU) and K f32 weights.
+    @property
+    def dispatch_bytes(self):
+        return self.E * 4 + self.K * 8
+
+    @property
+    def n_used(self):
+        return self.K
+
+    def plan(self):
+        per = self.L["n_experts"] // self.world
+        owner = self.ids // per                                   # [T][K]
+        self.goes = np.stack([(owner == g).any(1) for g in range(self.world)], 1)   # [T][world]
+        tot = np.zeros(16, dtype=np.int32)
+        tot[:self.world] = self.goes.sum(0)
+        tot[8:8 + self.world] = [(owner == g).sum() for g in range(self.world)]
+        self.owner = owner
+        return torch.from_numpy(tot)
+
+    def dispatch(self, nrows):
+        out = np.zeros((nrows, self.dispatch_bytes), dtype=np.uint8)
+        r = 0
+        self.sent_at = {}
+        for g in range(self.world):
+            for t in np.nonzero(self.goes[:, g])[0]:
+                on = self.owner[t] == g
+                out[r, :self.E * 4] = self.x[t].view(np.uint8)
+                out[r, self.E * 4:self.E * 4 + self.K * 4] = np.where(on, self.ids[t], -1).astype(np.int32).view(np.uint8)
+                out[r, self.E * 4 + self.K * 4:] = np.where(on, self.w[t], 0).astype(np.float32).view(np.uint8)
+                self.sent_at[(int(t), g)] = r
+                r += 1
+        assert r == nrows
+        return torch.from_numpy(out)
+
+    def experts_partial(self, rows, assignments):
+        L, R = self.L, rows.shape[0]
+        b = rows.numpy()
+        x = np.ascontiguousarray(b[:, :self.E * 4]).view(np.float32).reshape(R, self.E)
+        ids = np.ascontiguousarray(b[:, self.E * 4:self.E * 4 + self.K * 4]).view(np.int32).reshape(R, self.K)
+        w = np.ascontiguousarray(b[:, self.E * 4 + self.K * 4:]).view(np.float32).reshape(R, self.K)
+        # Rows from a rank whose own stage failed are whatever its buffer held: as the GPU stage does, take what is a
+        # valid list entry and ignore the rest, rather than fail here too.
+        ids = np.where((ids >= self.first) & (ids < self.first + self.count), ids, -1)
+        w = np.nan_to_num(w, nan=0.0, posinf=0.0, neginf=0.0)
+        x = np.nan_to_num(x, nan=0.0, posinf=0.0, neginf=0.0)
+        jobs = [(L["gate_exps"][e], L["up_exps"][e], L["down_exps"][e], r, float(w[r, k]))
+                for r in range(R) for k, e in enumerate(ids[r]) if e >= 0]   # a row's jobs in rank order, as compute_many sums them
+        y = O.compute_many(L["gate_type"], L["down_type"], self.E, self.F, jobs, x) if jobs else np.zeros((R, self.E), np.float32)
+        return torch.from_numpy(y)
+
+    def combine_partials(self, back, out):
+        back = back.numpy()
+        T = self.x.shape[0]
+        o = np.zeros((T, self.E), dtype=np.float32)
+        for g in range(self.world):                               # the GPUs' sums in GPU order
+            for t in np.nonzero(self.goes[:, g])[0]:
+                o[t] += back[self.sent_at[(int(t), g)]]
+        o += self.gs[:, None] * self.s
+        out.copy_(torch.from_numpy(o))
+
     def shared(self):
         L = self.L
         T = self.x.shape[0]

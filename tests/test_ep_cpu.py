@@ -26,7 +26,7 @@ def _layer():
     return synth.make_layer(n_embd=256, n_ff=256, n_experts=32, n_used=4, gate_type=synth.Q4_K, zipf_s=1.1, seed=3)
 
 
-def _worker(rank, world, port, q, T):
+def _worker(rank, world, port, q, T, by_token):
     from ep_common import OracleStages
     from oracle import oracle as O
 
@@ -34,23 +34,35 @@ def _worker(rank, world, port, q, T):
     try:
         layer = _layer()
         x = synth.make_input(T[rank], 256, seed=10 + rank)
-        moe = ep.ExpertParallelMoE(OracleStages(layer, rank, world))
+        moe = ep.ExpertParallelMoE(OracleStages(layer, rank, world), by_token=by_token)
         out = moe.forward(torch.from_numpy(x)).numpy()
         ref = O.moe_forward(layer, x)[0]
-        q.put((rank, bool(np.array_equal(out, ref)), moe.sent_rows, moe.received_rows))
+        rel = float(np.abs(out - ref).max() / np.abs(ref).max())
+        q.put((rank, bool(np.array_equal(out, ref)), moe.sent_rows, moe.received_rows, rel))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("T", [(37, 5), (1, 64)])
 def test_two_ranks_give_the_single_process_bits(T):
-    res = run_ranks(_worker, 2, (T,))
-    assert all(ok for _, ok, _, _ in res)
+    """One row per assignment: each rank's outputs are the single process's bits."""
+    res = run_ranks(_worker, 2, (T, False))
+    assert all(r[1] for r in res)
     # What one rank sent to the other is what the other received from it.
     assert res[0][2] == res[1][3] and res[1][2] == res[0][3]
 
 
-def _worker_stage_fails(rank, world, port, q, where):
+@pytest.mark.parametrize("world,T", [(2, (37, 5)), (4, (9, 1, 30, 2))])
+def test_one_row_per_token_and_gpu(world, T):
+    """One row per (token, GPU) out and one partial sum back: the outputs agree with the single process's to f32
+    rounding (the sum over a token's experts is taken GPU by GPU), and fewer rows cross than there are assignments."""
+    res = run_ranks(_worker, world, (T, True))
+    assert all(r[4] <= 1e-5 for r in res), [r[4] for r in res]
+    assert sum(r[2] for r in res) == sum(r[3] for r in res)          # rows sent = rows received, over all ranks
+    assert sum(r[2] for r in res) < sum(T) * 4                        # fewer than one a (token, expert)
+
+
+def _worker_stage_fails(rank, world, port, q, where, by_token):
     """Rank 1's stage raises in the middle of a step. Rank 0 must still leave the step (its collectives are all
     entered by rank 1 too, which raises only after them), and the step after that must work on both."""
     from ep_common import OracleStages
@@ -68,7 +80,7 @@ def _worker_stage_fails(rank, world, port, q, where):
             return real(*a)
 
         setattr(st, where, failing)
-        moe = ep.ExpertParallelMoE(st)
+        moe = ep.ExpertParallelMoE(st, by_token=by_token)
         x = torch.from_numpy(synth.make_input(9, 256, seed=rank))
         first = "ok"
         try:
@@ -85,9 +97,9 @@ def _worker_stage_fails(rank, world, port, q, where):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("where", ["gather", "experts"])
-def test_a_stage_that_fails_on_one_rank_does_not_strand_the_other(where):
-    res = run_ranks(_worker_stage_fails, 2, (where,), timeout=90)
+@pytest.mark.parametrize("where,by_token", [("gather", False), ("experts", False), ("dispatch", True), ("experts_partial", True)])
+def test_a_stage_that_fails_on_one_rank_does_not_strand_the_other(where, by_token):
+    res = run_ranks(_worker_stage_fails, 2, (where, by_token), timeout=90)
     assert res[0][1] == "ok" and "injected" in res[1][1]
     assert res[0][2] == "ok" and res[1][2] == "ok"
 

@@ -39,7 +39,7 @@ def _worker(rank, world, port, q):
             ref = O.moe_forward(layer, x)[0]
             for f16 in (False, True):
                 st = ep.GpuStages(layer, rank, world, max_tokens=512, device=rank, y_f16=f16, tensor_min_rows=1)
-                moe = ep.ExpertParallelMoE(st)
+                moe = ep.ExpertParallelMoE(st, by_token=False)
                 xd = torch.from_numpy(x).cuda()
                 for _ in range(2):
                     out = moe.forward(xd)
@@ -48,6 +48,15 @@ def _worker(rank, world, port, q):
                 rel = float(np.abs(got - ref).max() / np.abs(ref).max())
                 res.append((t, f16, bool(np.array_equal(got, want)), rel, moe.sent_rows))
                 st.close()
+            # One row per (token, GPU), with the experts interleaved over the ranks: within the layer's bar of the oracle.
+            st = ep.GpuStages(layer, rank, world, max_tokens=512, device=rank, tensor_min_rows=1, interleave=True)
+            moe = ep.ExpertParallelMoE(st)
+            for _ in range(2):
+                out = moe.forward(torch.from_numpy(x).cuda())
+            st.sync()
+            got = out.cpu().numpy()
+            res.append((t, "by_token", True, float(np.abs(got - ref).max() / np.abs(ref).max()), moe.sent_rows))
+            st.close()
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -61,6 +70,6 @@ def test_two_gpus_match_one():
     for rank, res in run_ranks(_worker, 2, timeout=600):
         for t, f16, same_bits, rel, sent in res:
             assert rel <= 1e-2, (rank, t, f16, rel)
-            if f16:
+            if f16 is True:
                 assert same_bits, (rank, t)
             assert sent > 0

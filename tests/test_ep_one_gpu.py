@@ -76,3 +76,62 @@ def test_two_ranges_on_one_gpu_match_the_whole_layer(wtype, rows):
     finally:
         for st in stages:
             st.close()
+
+
+@pytest.mark.parametrize("wtype,rows,world", [("Q4_K", (300, 41), 2), ("IQ3_S", (7, 1, 30, 12), 4), ("Q8_0", (64, 33), 2)])
+def test_one_row_per_token_and_gpu_on_one_gpu(wtype, rows, world):
+    """The same on one GPU for the other form of the exchange: one row per (token, GPU) out, one weighted partial sum
+    back. Each rank's outputs are held to the oracle (and so to the whole layer's) within the layer's bar; the rows
+    that cross are counted against the plan's totals; the lists that travel with them name only the receiver's experts."""
+    import torch
+
+    from c0ven_b200 import ep, synth
+    from oracle import oracle as O
+
+    K = 4
+    layer = synth.make_layer(n_embd=512, n_ff=256, n_experts=32, n_used=K, gate_type=synth.TYPE_IDS[wtype], zipf_s=1.1, seed=71)
+    xs = [synth.make_input(rows[r], 512, seed=40 + r) for r in range(world)]
+    stages = [ep.GpuStages(layer, r, world, max_tokens=512, device=0, tensor_min_rows=1, profile=True) for r in range(world)]
+    try:
+        xd = [torch.from_numpy(x).cuda() for x in xs]
+        tots = []
+        for r, st in enumerate(stages):
+            st.route(xd[r])
+            tots.append(st.plan())
+            st.sync()
+        m = torch.stack(tots).cpu().numpy().reshape(world, 2, 8)
+        for r, st in enumerate(stages):   # the plan against the routing it came from
+            ids = st.moe.route(rows[r])[0]
+            owner = ids // (32 // world)
+            assert [int(v) for v in m[r, 0, :world]] == [int((owner == g).any(1).sum()) for g in range(world)]
+            assert [int(v) for v in m[r, 1, :world]] == [int((owner == g).sum()) for g in range(world)]
+        sent = []
+        for r, st in enumerate(stages):
+            d = st.dispatch(int(m[r, 0, :world].sum()))
+            st.sync()
+            sent.append(d.clone())
+        assert sum(s.shape[0] for s in sent) < sum(rows) * K or world == 1
+        rows_in = [t.contiguous() for t in _exchange(sent, [[int(v) for v in m[r, 0, :world]] for r in range(world)])]
+        torch.cuda.synchronize()
+        ys = []
+        for r, st in enumerate(stages):
+            wb = st.moe.wire_row_bytes
+            meta = rows_in[r][:, wb:wb + 32].cpu().numpy().view(np.uint16)[:, :K]
+            assert np.all((meta == 0xFFFF) | (meta < 32 // world)) and int((meta != 0xFFFF).sum()) == int(m[:, 1, r].sum())
+            y = st.experts_partial(rows_in[r], int(m[:, 1, r].sum()))
+            st.sync()
+            ys.append(y.clone())
+            torch.cuda.synchronize()
+        back = [t.contiguous() for t in _exchange(ys, [[int(v) for v in m[:, 0, r]] for r in range(world)])]
+        torch.cuda.synchronize()
+        for r, st in enumerate(stages):
+            st.shared()
+            out = torch.empty_like(xd[r])
+            st.combine_partials(back[r], out)
+            st.sync()
+            got = out.cpu().numpy()
+            ref = O.moe_forward(layer, xs[r])[0]
+            assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+    finally:
+        for st in stages:
+            st.close()
