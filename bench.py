@@ -222,9 +222,22 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
             layers.append(m), moes.append(None)
             main_sp = main_sp or m.stream
         else:
+            # Expert parallel: the experts dealt to the GPUs by the load one step of this batch shows (a layer with a
+            # routing bias), else interleaved; one row per (token, GPU) on the wire unless --per-assignment.
+            order = ep.interleaved_order(NE, world)
+            if w.get("zipf_s", 0.0) > 0 and not args.contiguous:
+                probe = ep.GpuStages(lw, rank, world, max_tokens=T, device=local, order=order)
+                ep.ExpertParallelMoE(probe, by_token=not args.per_assignment).forward(x_host.cuda())
+                probe.sync()
+                cnt = torch.from_numpy(probe.moe.read_counts().astype(np.int64)).cuda()
+                dist.all_reduce(cnt)
+                seen = np.zeros(NE, dtype=np.int64)
+                seen[order] = cnt.cpu().numpy()          # the probe counted in its own numbering
+                probe.close()
+                order = ep.balanced_order(seen, world)
             st = ep.GpuStages(lw, rank, world, max_tokens=T, device=local, y_f16=True, profile=False,
-                              tensor_min_rows=args.tensor_min, stream_ptr=main_sp)
-            stages.append(st), layers.append(st.moe), moes.append(ep.ExpertParallelMoE(st))
+                              tensor_min_rows=args.tensor_min, stream_ptr=main_sp, order=None if args.contiguous else order)
+            stages.append(st), layers.append(st.moe), moes.append(ep.ExpertParallelMoE(st, by_token=not args.per_assignment))
             main_sp = main_sp or st.moe.stream
     stream = torch.cuda.ExternalStream(main_sp, device=local)
     x_dev, out_dev = x_host.cuda(), torch.empty((T, E), device="cuda")
@@ -403,7 +416,9 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
         par = "1 GPU"
     else:
         par = (f"expert parallel x{world}: {NE // world} experts and {T} rows per GPU ({scaling} scaling), "
-               "all-to-all of q8 rows out and f16 results back")
+               + ("all-to-all of one q8 row per assignment out and one f16 result back" if args.per_assignment else
+                  "all-to-all of one q8 row per (token, GPU) out and one f16 partial sum back")
+               + (", contiguous expert ranges" if args.contiguous else ", experts dealt to the GPUs by load" if w.get("zipf_s", 0.0) > 0 else ", experts interleaved"))
     return dict(metric=METRIC, value=world * T / (ms * 1e-3), unit=UNIT, n_gpus=world, steps=steps, warmup=args.warmup,
                 ms_per_step=ms, timed_steps=len(times), ms_per_step_mean_of_steps=ms_asked, higher_is_better=True, scaling=scaling,
                 vs_baseline=None, dtype="f16" if tensor_rows > 0 else "i8", data="synthetic",
@@ -462,6 +477,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="rows instead of the workload's (the sweep's points)")
     ap.add_argument("--host-chunk", type=int, default=-1,
                     help="rows of a chunk of the host-buffer call, whose copies overlap its neighbours' computation (0: never cut; default: 8192 for batches of 16384 rows and more)")
+    ap.add_argument("--per-assignment", action="store_true", help="expert parallel: one row per assignment on the wire (one GPU's bits) instead of one per (token, GPU)")
+    ap.add_argument("--contiguous", action="store_true", help="expert parallel: GPU g holds experts [g * per, (g + 1) * per) of the layer as given")
     ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

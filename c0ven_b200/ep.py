@@ -49,12 +49,34 @@ def split_sizes(cnt_all: np.ndarray, rank: int):
     return [int(v) for v in by_owner[rank]], [int(v) for v in by_owner[:, rank]]
 
 
-def interleaved(layer: dict, world: int) -> dict:
-    """The layer with its experts renumbered so that new expert g * per + j is the caller's expert j * world + g: equal
-    contiguous ranges of the new numbering are then the residue classes of the old. (Copies the experts: for tests and
-    CPU stand-ins; GpuStages takes only its own rank's.)"""
-    ne = layer["n_experts"]
-    order = np.arange(ne).reshape(ne // world, world).T.reshape(-1)   # new index -> caller's index
+def interleaved_order(n_experts: int, world: int) -> np.ndarray:
+    """The renumbering (new index -> caller's index) under which equal contiguous ranges of the new numbering are the
+    residue classes of the old: new expert g * per + j is the caller's expert j * world + g."""
+    return np.arange(n_experts).reshape(n_experts // world, world).T.reshape(-1)
+
+
+def balanced_order(counts, world: int) -> np.ndarray:
+    """A renumbering (new index -> caller's index) that spreads the load the counts show: counts[e] = rows expert e got
+    over some steps (moe_layer_read_counts, summed by the caller). Experts are dealt, heaviest first, each to the GPU
+    with the least load so far that still has room (every GPU holds the same number of experts); inside a GPU they keep
+    the caller's order. The reference answers routing skew by swapping which experts its cards cache
+    (core/models/qwen4exp/swap.cpp); with every expert resident somewhere, the analogue is where."""
+    counts = np.asarray(counts, dtype=np.int64)
+    ne = counts.size
+    per = ne // world
+    load, room = np.zeros(world, dtype=np.int64), np.full(world, per)
+    owner = np.empty(ne, dtype=np.int64)
+    for e in np.argsort(-counts, kind="stable"):
+        open_ = np.nonzero(room > 0)[0]
+        g = open_[np.argmin(load[open_])]
+        owner[e], load[g], room[g] = g, load[g] + counts[e], room[g] - 1
+    return np.concatenate([np.nonzero(owner == g)[0] for g in range(world)])
+
+
+def reordered(layer: dict, order) -> dict:
+    """The layer with its experts renumbered by order (new index -> caller's index). Copies the experts: for tests and
+    CPU stand-ins; GpuStages takes only its own rank's."""
+    order = np.asarray(order)
     out = dict(layer)
     out["router"] = np.ascontiguousarray(layer["router"][order])
     if layer.get("router_bias") is not None:
@@ -62,6 +84,10 @@ def interleaved(layer: dict, world: int) -> dict:
     for k in ("gate_exps", "up_exps", "down_exps"):
         out[k] = layer[k][order]
     return out
+
+
+def interleaved(layer: dict, world: int) -> dict:
+    return reordered(layer, interleaved_order(layer["n_experts"], world))
 
 
 def received_ids(cnt_all: np.ndarray, rank: int) -> np.ndarray:
@@ -77,14 +103,20 @@ class GpuStages:
 
     def __init__(self, layer: dict, rank: int, world: int, max_tokens: int, device: int, max_expert_rows: int = 0,
                  y_f16: bool = True, profile: bool = False, tensor_min_rows: int = 0, stream_ptr: int | None = None,
-                 interleave: bool = False):
+                 interleave: bool = False, order=None):
+        """order: a renumbering of the experts (new index -> the caller's index, e.g. balanced_order's); rank g then holds
+        the caller's experts order[g * per : (g + 1) * per]. interleave: interleaved_order."""
         from .layer import MoELayer
 
         first, count = owner_ranges(layer["n_experts"], world)[rank]
         own = None
-        if interleave:
-            # The router renumbered; of the experts only this rank's are touched: the caller's rank, rank + world, ...
-            order = np.arange(layer["n_experts"]).reshape(count, world).T.reshape(-1)   # new index -> caller's index
+        if interleave and order is None:
+            order = interleaved_order(layer["n_experts"], world)
+        if order is not None:
+            # The router renumbered; of the experts only this rank's are touched.
+            order = np.asarray(order)
+            if sorted(order.tolist()) != list(range(layer["n_experts"])):
+                raise ValueError("order must be a permutation of the experts")
             mine = order[first:first + count]
             own = (layer["gate_exps"][mine], layer["up_exps"][mine], layer["down_exps"][mine])
             layer = dict(layer, router=np.ascontiguousarray(layer["router"][order]),
