@@ -51,6 +51,9 @@ struct ExpertTilesArgs {
   uint32_t out_f16;
   float limit;
   uint32_t *error;          // set non-zero when a wait ran out
+  // For types whose quants come by copy (quants_by_copy): maps over the quants runs of w0 and w1, (bytes of a row, rows,
+  // expert slots), their box (a quant slot's bytes a row, 128 rows, 1 slot) (tensor_map.h: make_quants_map).
+  CUtensorMap qmap[2];
 };
 
 namespace tc {
@@ -111,6 +114,13 @@ __device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes)
 __device__ __forceinline__ void tma_load_rows(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+// Box (x .. of the row's bytes, rows y .., expert slot z) of a weight matrix's quants run into shared memory at dst.
+// x is a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_quants(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t z, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(bar)
                : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -381,15 +391,31 @@ struct Decoder<QT_IQ3_S> {
 }  // namespace tc
 
 
-// Shared memory of a CTA: the stages (NMAT weight tiles of 16 KB and a row tile of 32 KB each), then the barriers.
-template <int NMAT>
+// Whether a type's quants reach the decode warps through a ring in shared memory filled by bulk-tensor copies, rather
+// than by the warps' own global loads (whose one-row-per-lane pattern costs the load pipe 32 wavefronts an
+// instruction). Q4_K, the benchmark's type: its quants are one run of K / 2 bytes a row, which a 3-D map (bytes of the
+// row, rows, expert slots) covers.
+__host__ __device__ constexpr bool quants_by_copy(uint32_t qt) { return qt == QT_Q4_K; }
+
+// Shared memory of a CTA: the stages (NMAT weight tiles of 16 KB and a row tile of 32 KB each), then (for types whose
+// quants come by copy) a ring of two quant slots, then the barriers, then IQ3_S's codebook.
+// A quant slot holds, for every weight row of the item, the quants of one stage per decode group: 32 bytes a stage for
+// Q4_K, so 64 bytes a row with two groups (64-byte swizzle) and 128 with four (128-byte swizzle).
+template <int QT, int NMAT>
 struct TileSmem {
   static constexpr uint32_t kStages = NMAT == 2 ? 3 : 4;
   static constexpr uint32_t kWBytes = kTileM * kTileK * 2, kXBytes = kTileN * kTileK * 2;
   static constexpr uint32_t kStageBytes = NMAT * kWBytes + kXBytes;
-  static constexpr uint32_t kBarriers = kStages * kStageBytes;  // full[kStages], empty[kStages], accumulators full[2], empty[2], empty after a two-buffer item; tmem address; abort
-  static constexpr uint32_t kGrid = kBarriers + 128;            // IQ3_S's codebook, 2 KB
-  static constexpr uint32_t kBytes = kGrid + 2048 + 1024;       // and room to align the base to 1024
+  static constexpr uint32_t kGroups = kTileDecoders / (NMAT * kTileM);                // decode groups: 2 or 4
+  static constexpr uint32_t kQRowBytes = kGroups * 32;                                // a row's bytes in a quant slot
+  static constexpr uint32_t kQMatBytes = kTileM * kQRowBytes, kQSlotBytes = NMAT * kQMatBytes, kQSlots = 2;
+  static constexpr uint32_t kQuants = kStages * kStageBytes;
+  static constexpr uint32_t kBarriers = kQuants + (quants_by_copy(QT) ? kQSlots * kQSlotBytes : 0);
+  // full[kStages], empty[kStages], accumulators full[2], empty[2], empty after a two-buffer item, quant slots full[2],
+  // empty[2]; tmem address; abort
+  static constexpr uint32_t kGrid = kBarriers + 256;                                  // IQ3_S's codebook, 2 KB
+  static constexpr uint32_t kBytes = kGrid + (QT == QT_IQ3_S ? 2048 : 0) + 1024;      // and room to align the base to 1024
+  static_assert(kBytes <= 227 * 1024, "a CTA's shared memory");
 };
 
 // SwiGLU with the fast exponential and division: the tensor-core path's results already differ from the CPU path's
@@ -428,10 +454,11 @@ __device__ __forceinline__ ItemTile item_tile(const ExpertTilesArgs &a, uint32_t
 // wait for its epilogue, and to keep that short the decode warps join the epilogue warps for it.
 // Dynamic shared memory TileSmem::kBytes.
 template <int QT, int NMAT>
-__global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTilesArgs a, const __grid_constant__ CUtensorMap act_map,
+__global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_constant__ ExpertTilesArgs a,
+                                                                  const __grid_constant__ CUtensorMap act_map,
                                                                   const uint32_t *__restrict__ grid_global) {
   using namespace tc;
-  using SM = TileSmem<NMAT>;
+  using SM = TileSmem<QT, NMAT>;
   using Dec = Decoder<QT>;
   using Raw = typename Dec::Raw;
   constexpr uint32_t S = SM::kStages, kCols = 512;
@@ -456,7 +483,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
   auto acc_full = [&](uint32_t b) { return bar0 + 8 * (2 * S + b); };
   auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (2 * S + 2 + b); };
   const uint32_t acc_empty_wide = bar0 + 8 * (2 * S + 4);
-  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 5);
+  auto q_full = [&](uint32_t b) { return bar0 + 8 * (2 * S + 5 + b); };
+  auto q_empty = [&](uint32_t b) { return bar0 + 8 * (2 * S + 7 + b); };
+  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S + 9);
   volatile uint32_t *abort = tmem_slot + 1;
   uint32_t *grid = (uint32_t *)(smem + SM::kGrid);
 
@@ -467,6 +496,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
     for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW / kDecGroups + 1), mbar_init(empty_bar(s), 1);
     for (uint32_t b = 0; b < 2; b++) mbar_init(acc_full(b), 1), mbar_init(acc_empty(b), kEW);
     mbar_init(acc_empty_wide, kDW);
+    for (uint32_t b = 0; b < 2; b++) mbar_init(q_full(b), 1), mbar_init(q_empty(b), kDW);
     *abort = 0;
     fence_barrier_init();
   }
@@ -560,12 +590,28 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       uint32_t blk_fetched = 0xFFFFFFFFu;
       auto fetch = [&](uint32_t b, uint32_t it) {
         const uint32_t k0 = it * kTileK;
-        raw[b][0] = Dec::fetch(wm, nblk, K, r0 + m, k0, 0);
-        raw[b][1] = Dec::fetch(wm, nblk, K, r0 + m, k0, 1);
         if (k0 / 256 != blk_fetched) hdr_last = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
         hdr[b] = hdr_last;
-        // One request a 128-byte line, which holds kLineStages stages of the row.
-        if (it % kLineStages == 0 && k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
+        if constexpr (quants_by_copy(QT)) {
+          // The stage's 32 bytes of this row from the quant ring: slot qn holds one stage per group, this group's at
+          // bytes 32 * first of the row, its 16-byte pieces swizzled by the row as the copy laid them.
+          const uint32_t qn = li * (KT / kDecGroups) + it / kDecGroups, qb = qn % SM::kQSlots;
+          if (!mbar_wait(q_full(qb), (qn / SM::kQSlots) & 1, abort, a.error)) {
+            ok = false;
+            return;
+          }
+          const uint8_t *row = smem + SM::kQuants + qb * SM::kQSlotBytes + mat * SM::kQMatBytes + m * SM::kQRowBytes;
+          const uint32_t sw = SM::kQRowBytes == 64 ? (m >> 1) & 3 : m & 7;
+          raw[b][0].q = *(const uint4 *)(row + 16 * ((2 * first) ^ sw));
+          raw[b][1].q = *(const uint4 *)(row + 16 * ((2 * first + 1) ^ sw));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(q_empty(qb));
+        } else {
+          raw[b][0] = Dec::fetch(wm, nblk, K, r0 + m, k0, 0);
+          raw[b][1] = Dec::fetch(wm, nblk, K, r0 + m, k0, 1);
+          // One request a 128-byte line, which holds kLineStages stages of the row.
+          if (it % kLineStages == 0 && k0 + kAhead * kTileK < K) prefetch_l2(Dec::quants_at(wm, nblk, K, r0 + m, k0 + kAhead * kTileK, 0));
+        }
       };
       auto stage_step = [&](uint32_t b, uint32_t it) {
         const uint32_t g = li * KT + it, s = g % S, use_s = g / S, k0 = it * kTileK;
@@ -584,9 +630,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       auto ask_ahead = [&](const uint8_t *w, uint32_t row) {
         for (uint32_t p = 0; p < kAhead && p < KT; p += kLineStages) prefetch_l2(Dec::quants_at(w, nblk, K, row, p * kTileK, 0));
       };
-      if (first == 0 && li == 0) ask_ahead(wm, r0 + m);
-      const uint32_t item_next = item_at(rnd + 1);
+      if (!quants_by_copy(QT) && first == 0 && li == 0) ask_ahead(wm, r0 + m);
+      const uint32_t item_next = quants_by_copy(QT) ? kNoItem : item_at(rnd + 1);
       // This thread's stages: first, first + kDecGroups, ...; the quants of one are loaded while the one before decodes.
+      if constexpr (quants_by_copy(QT)) {
+        // The quants wait in shared memory: nothing to load ahead; a stage is read and decoded in one go.
+        for (uint32_t it = first; it < KT && ok; it += kDecGroups) {
+          fetch(0, it);
+          if (ok) stage_step(0, it);
+        }
+      } else {
       if (first < KT) fetch(0, first);
       for (uint32_t it = first; it < KT && ok; it += 2 * kDecGroups) {
         if (it + kDecGroups < KT) fetch(1, it + kDecGroups);
@@ -598,6 +651,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
         if (!ok || it + kDecGroups >= KT) break;
         if (it + 2 * kDecGroups < KT) fetch(0, it + 2 * kDecGroups);
         stage_step(1, it + kDecGroups);
+      }
       }
       if (is_wide(t.count)) {
         // Both buffers: the next item's MMAs wait for this epilogue, so these warps take four fifths of it.
@@ -663,6 +717,27 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const ExpertTi
       }
       if (!ok) {
         // Copies already issued may still be on their way: give them time to land before the CTA leaves.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000) {
+        }
+      }
+    } else if (quants_by_copy(QT) && lane == 1) {
+      // The quants' copy thread: a quant slot, one stage per decode group for every weight row of the item, as soon
+      // as the decode warps have read the slot's last contents; it runs ahead of the stages by the ring's two slots.
+      uint32_t li = 0;
+      for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
+        const ItemTile t = item_tile(a, item / RT);
+        for (uint32_t j = 0; j < KT / kDecGroups && ok; j++) {
+          const uint32_t qn = li * (KT / kDecGroups) + j, qb = qn % SM::kQSlots, use_q = qn / SM::kQSlots;
+          if (use_q > 0) ok = mbar_wait(q_empty(qb), (use_q - 1) & 1, abort, a.error);
+          if (!ok) break;
+          const uint32_t dst = smem_u32(smem + SM::kQuants + qb * SM::kQSlotBytes);
+          mbar_arrive_expect(q_full(qb), SM::kQSlotBytes);
+          for (uint32_t mt = 0; mt < (uint32_t)NMAT; mt++)
+            tma_load_quants(dst + mt * SM::kQMatBytes, &a.qmap[mt], j * SM::kQRowBytes, (item % RT) * kTileM, t.slot, q_full(qb));
+        }
+      }
+      if (!ok) {
         const long long t0 = clock64();
         while (clock64() - t0 < 400000) {
         }

@@ -14,7 +14,7 @@ cudaError_t launch_expert_tiles(const ExpertTilesArgs &a, const CUtensorMap &act
                                 const LaunchCtx &ctx, cudaStream_t st) {
   if (a.K % kTileK || a.R % kTileM || max_tiles == 0) return cudaErrorInvalidValue;
   auto kernel = k_expert_tiles<QT, NMAT>;
-  const size_t smem = TileSmem<NMAT>::kBytes;
+  const size_t smem = TileSmem<QT, NMAT>::kBytes;
   static std::atomic<uint32_t> attr_done{0};
   const cudaError_t e = ensure_dynamic_smem(kernel, smem, attr_done, ctx.device);
   if (e != cudaSuccess) return e;

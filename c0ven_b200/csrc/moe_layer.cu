@@ -151,6 +151,8 @@ struct moe_layer {
   DeviceBuffer<uint8_t> wg, wu, wd, sg, su, sd;
   DeviceBuffer<uint32_t> grid;
   uint64_t gate_slice = 0, down_slice = 0;
+  // Maps over the quants runs, for the matrices whose type's quants reach the tile kernels by copy (tensor_map.h).
+  CUtensorMap wg_q{}, wu_q{}, wd_q{}, sg_q{}, su_q{}, sd_q{};
   // A call's buffers.
   DeviceBuffer<float> x, out, rl, gate_parts, w, gs, h, y, s;
   // The router's product on the tensor cores (steps of more than 64 rows): the router's rows and the step's rows as
@@ -291,6 +293,19 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
     upload_matrix(l->sd, c.shexp_down_type, w.down_shexp, (uint64_t)E * (F / block_values(c.shexp_down_type)), 1, st);
   }
 
+  if (l->can_tensor) {
+    // A quant slot's row is 32 bytes a decode group: 2 groups for gate and up (two matrices a stage), 4 for down.
+    if (quants_by_copy(c.gate_type)) {
+      l->wg_q = make_quants_map(l->wg.get(), E / 2, F, l->local, l->gate_slice, 64);
+      l->wu_q = make_quants_map(l->wu.get(), E / 2, F, l->local, l->gate_slice, 64);
+    }
+    if (quants_by_copy(c.down_type)) l->wd_q = make_quants_map(l->wd.get(), F / 2, E, l->local, l->down_slice, 128);
+    if (l->has_shared && quants_by_copy(c.shexp_gate_type)) {
+      l->sg_q = make_quants_map(l->sg.get(), E / 2, F, 1, l->sg.bytes(), 64);
+      l->su_q = make_quants_map(l->su.get(), E / 2, F, 1, l->su.bytes(), 64);
+    }
+    if (l->has_shared && quants_by_copy(c.shexp_down_type)) l->sd_q = make_quants_map(l->sd.get(), F / 2, E, 1, l->sd.bytes(), 128);
+  }
   l->x.alloc((size_t)T * E), l->out.alloc((size_t)T * E);
   l->router_tensor = l->can_tensor && T > kRouterExactRows;
   l->rl.alloc((size_t)(l->router_tensor ? kRouterExactRows : T) * l->N), l->gate_parts.alloc((size_t)T * (E / 256));
@@ -480,13 +495,19 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
     launched(l, cudaGetLastError(), "router top-k and pack");
     mark(l, ST_PACK, st);
   } else {
-    RouterApprox ap{};
-    if (approx)
-      ap = RouterApprox{l->approx.get(), x, l->router.get(), l->norm2_parts.get(), l->gate_parts.get(), E, E / 256,
-                        l->router_eps_rel, l->router_eps_abs};
-    k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), ap, l->bias.get(), T, NE, K, l->ids.get(), l->w.get(), l->gs.get(),
-                                                        l->pack.chunk_hist.get());
-    launched(l, cudaGetLastError(), "router top-k");
+    if (approx) {
+      const RouterApprox ap{l->approx.get(), x, l->router.get(), l->norm2_parts.get(), l->gate_parts.get(), E, E / 256,
+                            l->router_eps_rel, l->router_eps_abs};
+      k_router_topk_rows<<<(T + kTopkRowsPerCta - 1) / kTopkRowsPerCta, 32 * kTopkRowsPerCta, 0, st>>>(ap, l->bias.get(), T, NE, K, l->ids.get(),
+                                                                                                  l->w.get(), l->gs.get());
+      launched(l, cudaGetLastError(), "router top-k");
+      k_chunk_hist<<<nchunks, 256, 0, st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, 0, l->pack.chunk_hist.get());
+      launched(l, cudaGetLastError(), "chunk counts");
+    } else {
+      k_router_topk<<<nchunks, 32 * kChunkTokens, 0, st>>>(l->rl.get(), RouterApprox{}, l->bias.get(), T, NE, K, l->ids.get(), l->w.get(),
+                                                          l->gs.get(), l->pack.chunk_hist.get());
+      launched(l, cudaGetLastError(), "router top-k");
+    }
     mark(l, ST_PACK, st);
     k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, budget, group_cap(A, NE), l->pack.out());
     launched(l, cudaGetLastError(), "pack scan");
@@ -525,6 +546,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   if (max_big) {
     ExpertTilesArgs a{};
     a.w0 = l->wg.get(), a.w1 = l->wu.get(), a.slice_bytes = l->gate_slice, a.K = E, a.R = F;
+    a.qmap[0] = l->wg_q, a.qmap[1] = l->wu_q;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
     launched(l, launch_tiles(c.gate_type, 2, a, l->xg_map, max_big, l->grid.get(), l->ctx, st), "experts gate/up tiles");
@@ -542,6 +564,7 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   if (max_big) {
     ExpertTilesArgs a{};
     a.w0 = l->wd.get(), a.slice_bytes = l->down_slice, a.K = F, a.R = E;
+    a.qmap[0] = l->wd_q;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = y, a.out_stride = E, a.out_f16 = y16, a.error = l->error.get();
     launched(l, launch_tiles(c.down_type, 1, a, l->hq_routed.h_map, max_big, l->grid.get(), l->ctx, st), "experts down tiles");
@@ -569,11 +592,13 @@ void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
     const uint32_t dense_tiles = (T + kTileN - 1) / kTileN;
     ExpertTilesArgs a{};
     a.w0 = l->sg.get(), a.w1 = l->su.get(), a.K = E, a.R = F, a.dense_rows = T;
+    a.qmap[0] = l->sg_q, a.qmap[1] = l->su_q;
     a.out = hs, a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
     launched(l, launch_tiles(c.shexp_gate_type, 2, a, xs.h_map, dense_tiles, l->grid.get(), l->ctx, st), "shared gate/up tiles");
     quantize_rows(l, hs, T, F, l->hq_shared, st);
     ExpertTilesArgs b{};
     b.w0 = l->sd.get(), b.K = F, b.R = E, b.dense_rows = T;
+    b.qmap[0] = l->sd_q;
     b.out = l->s.get(), b.out_stride = E, b.error = l->error.get();
     launched(l, launch_tiles(c.shexp_down_type, 1, b, l->hq_shared.h_map, dense_tiles, l->grid.get(), l->ctx, st), "shared down tiles");
     l->shared_on_tensor = true;

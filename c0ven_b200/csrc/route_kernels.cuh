@@ -284,9 +284,12 @@ __device__ __forceinline__ float exact_logits4(const float *__restrict__ x, cons
 __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, const RouterApprox ap, const float *__restrict__ bias,
                                                   uint32_t T, uint32_t NE, uint32_t K, int32_t *__restrict__ ids, float *__restrict__ w,
                                                   float *__restrict__ gs, uint32_t *hist, int32_t *s_ids) {
-  for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
-  __syncthreads();
-  const uint32_t lane = threadIdx.x % 32, t = blockIdx.x * kChunkTokens + threadIdx.x / 32, per = NE / 32;
+  // hist null: the caller counts the chunks' experts itself (k_chunk_hist), and the block may be of any number of warps.
+  if (hist) {
+    for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+  }
+  const uint32_t lane = threadIdx.x % 32, t = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, per = NE / 32;
   if (t < T) {
     uint32_t key[kMaxPerLane];
     float mx = -INFINITY, eps2 = 0.0f;  // eps2: twice the row's error bound; 0 with exact logits
@@ -428,7 +431,7 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
     if (winner) {
       ids[(uint64_t)t * K + rank] = (int32_t)my_id;
       w[(uint64_t)t * K + rank] = pk / fmaxf(tot, 6.1035e-5f);
-      atomicAdd(&hist[my_id], 1u);
+      if (hist) atomicAdd(&hist[my_id], 1u);
       if (s_ids) s_ids[(threadIdx.x / 32) * K + rank] = (int32_t)my_id;
     }
     if (lane == 0) {
@@ -442,7 +445,17 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
       gs[t] = 1.0f / (1.0f + expf(-g));
     }
   }
-  __syncthreads();
+  if (hist) __syncthreads();
+}
+
+// The top-k alone, a few rows a CTA and no barrier in it: for long steps, whose rows wait on memory for their exact
+// recomputations; with many small CTAs an SM always has rows that are not waiting, and no row waits for the slowest of
+// its chunk. The chunks' counts then come from k_chunk_hist.
+constexpr uint32_t kTopkRowsPerCta = 4;
+static __global__ void __launch_bounds__(32 * kTopkRowsPerCta) k_router_topk_rows(const RouterApprox ap, const float *__restrict__ bias, uint32_t T,
+                                                                                 uint32_t NE, uint32_t K, int32_t *__restrict__ ids,
+                                                                                 float *__restrict__ w, float *__restrict__ gs) {
+  router_topk_block(nullptr, ap, bias, T, NE, K, ids, w, gs, nullptr, nullptr);
 }
 
 static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const RouterApprox ap,
