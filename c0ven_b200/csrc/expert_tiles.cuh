@@ -575,10 +575,26 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
     const uint64_t nblk = (uint64_t)a.R * (K / block_values(QT));
     const uint32_t first = tid / kGroupThreads, mat = (tid % kGroupThreads) / kTileM, m = tid % kTileM;
     uint32_t li = 0;
+    // For types whose quants come by copy, the one thing a decode thread still loads itself is a block's header, and it
+    // asks for it a block ahead (across items too), so that no stage begins by waiting for it: hdr_ahead holds the
+    // header of the next block the thread will decode.
+    typename Dec::Hdr hdr_ahead;
+    if constexpr (quants_by_copy(QT)) {
+      const uint32_t i0 = item_at(0);
+      if (i0 != kNoItem && first < KT) {
+        const ItemTile t0 = item_tile(a, i0 / RT);
+        hdr_ahead = Dec::fetch_hdr((mat == 0 ? a.w0 : a.w1) + (uint64_t)t0.slot * a.slice_bytes, nblk, K, (i0 % RT) * kTileM + m,
+                                   (first * kTileK) & ~255u);
+      }
+    }
     for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
       const ItemTile t = item_tile(a, item / RT);
       const uint32_t r0 = (item % RT) * kTileM;
       const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
+      // The next item's weights and rows, known early: its first header is asked for at this item's last stage.
+      const uint32_t item_after = quants_by_copy(QT) ? item_at(rnd + 1) : kNoItem;
+      ItemTile t_after{0, 0, 0};
+      if (item_after != kNoItem) t_after = item_tile(a, item_after / RT);
       // Quants come from HBM the first time an expert is touched; a request for the L2 goes out kAhead stages before
       // the load into registers, which itself goes a stage of this thread's before the decode.
       constexpr uint32_t kLineStages = 128 / Dec::kStageBytes;
@@ -590,7 +606,19 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
       uint32_t blk_fetched = 0xFFFFFFFFu;
       auto fetch = [&](uint32_t b, uint32_t it) {
         const uint32_t k0 = it * kTileK;
-        if (k0 / 256 != blk_fetched) hdr_last = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
+        if constexpr (quants_by_copy(QT)) {
+          // The header asked for a block ago is this block's; the one after it is asked for now.
+          if (it == first || k0 / 256 != blk_fetched) hdr_last = hdr_ahead, blk_fetched = k0 / 256;
+          const uint32_t it2 = it + kDecGroups;
+          if (it2 < KT) {
+            if (it2 * kTileK / 256 != blk_fetched) hdr_ahead = Dec::fetch_hdr(wm, nblk, K, r0 + m, (it2 * kTileK) & ~255u);
+          } else if (item_after != kNoItem) {
+            hdr_ahead = Dec::fetch_hdr((mat == 0 ? a.w0 : a.w1) + (uint64_t)t_after.slot * a.slice_bytes, nblk, K,
+                                       (item_after % RT) * kTileM + m, (first * kTileK) & ~255u);
+          }
+        } else {
+          if (k0 / 256 != blk_fetched) hdr_last = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
+        }
         hdr[b] = hdr_last;
         if constexpr (quants_by_copy(QT)) {
           // The stage's 32 bytes of this row from the quant ring: slot qn holds one stage per group, this group's at

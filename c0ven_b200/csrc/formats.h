@@ -1,3 +1,6 @@
+// IQ4_NL (y = d * table[nibble], blocks of 32) and IQ4_XS (y = d * (ls - 32) * table[nibble], 256 values with a 6-bit
+// scale per 32) share ggml's 16-entry table of signed bytes (docs/spec/QUANT_FORMATS.md:213-247); they are the types of
+// the reference file's down and (in one layer) gate/up experts.
 // The GGUF block formats the layer reads and the "runs" layout the GPU holds them in: a slice of n blocks is one run
 // per field, the quants first and the f16 scales last, field f of block k at run_offset(f, n) + k * field_size(f).
 // The formats and the run order are the reference's (shared/quant.h:36-176; docs/spec/QUANT_FORMATS.md, "Wide loads"),
@@ -15,22 +18,26 @@
 
 namespace moe {
 
-enum : uint32_t { QT_Q8_0 = 8, QT_Q4_K = 12, QT_Q6_K = 14, QT_IQ3_S = 21 };
+enum : uint32_t { QT_Q8_0 = 8, QT_Q4_K = 12, QT_Q6_K = 14, QT_IQ4_NL = 20, QT_IQ3_S = 21, QT_IQ4_XS = 23 };
 
-FMT_HD constexpr uint32_t block_values(uint32_t t) { return t == QT_Q8_0 ? 32u : (t == QT_Q4_K || t == QT_Q6_K || t == QT_IQ3_S) ? 256u : 0u; }
+FMT_HD constexpr uint32_t block_values(uint32_t t) {
+  return (t == QT_Q8_0 || t == QT_IQ4_NL) ? 32u : (t == QT_Q4_K || t == QT_Q6_K || t == QT_IQ3_S || t == QT_IQ4_XS) ? 256u : 0u;
+}
 FMT_HD constexpr uint32_t block_bytes(uint32_t t) {
-  return t == QT_Q8_0 ? 34u : t == QT_Q4_K ? 144u : t == QT_Q6_K ? 210u : t == QT_IQ3_S ? 110u : 0u;
+  return t == QT_Q8_0 ? 34u : t == QT_Q4_K ? 144u : t == QT_Q6_K ? 210u : t == QT_IQ3_S ? 110u : t == QT_IQ4_NL ? 18u : t == QT_IQ4_XS ? 136u : 0u;
 }
 FMT_HD constexpr bool type_known(uint32_t t) { return block_bytes(t) != 0; }
 // Whether the type's dot takes activations as q8_K (256 values, f32 scale, sums of 16) rather than q8_0 (32 values,
 // f16 scale): docs/spec/MODEL_LAYER.md, section 6.
-FMT_HD constexpr bool act_is_q8k(uint32_t t) { return t != QT_Q8_0; }
+FMT_HD constexpr bool act_is_q8k(uint32_t t) { return t != QT_Q8_0 && t != QT_IQ4_NL; }
 FMT_HD constexpr uint64_t row_bytes(uint32_t t, uint64_t n) { return n / block_values(t) * block_bytes(t); }
 
 struct Field {
   uint32_t offset, size;
 };
-FMT_HD constexpr uint32_t nfields(uint32_t t) { return t == QT_Q8_0 ? 2u : t == QT_Q4_K ? 2u : t == QT_Q6_K ? 4u : t == QT_IQ3_S ? 5u : 0u; }
+FMT_HD constexpr uint32_t nfields(uint32_t t) {
+  return t == QT_Q8_0 ? 2u : t == QT_Q4_K ? 2u : t == QT_Q6_K ? 4u : t == QT_IQ3_S ? 5u : t == QT_IQ4_NL ? 2u : t == QT_IQ4_XS ? 4u : 0u;
+}
 // Field f of type t, in run order.
 FMT_HD constexpr Field field(uint32_t t, uint32_t f) {
   switch (t) {
@@ -39,6 +46,8 @@ FMT_HD constexpr Field field(uint32_t t, uint32_t f) {
     case QT_Q6_K: return f == 0 ? Field{0, 128} : f == 1 ? Field{128, 64} : f == 2 ? Field{192, 16} : Field{208, 2};  // ql, qh, scales, d
     case QT_IQ3_S:
       return f == 0 ? Field{2, 64} : f == 1 ? Field{74, 32} : f == 2 ? Field{66, 8} : f == 3 ? Field{106, 4} : Field{0, 2};  // qs, signs, qh, scales, d
+    case QT_IQ4_NL: return f == 0 ? Field{2, 16} : Field{0, 2};                                                // qs, d
+    case QT_IQ4_XS: return f == 0 ? Field{8, 128} : f == 1 ? Field{4, 4} : f == 2 ? Field{2, 2} : Field{0, 2};   // qs, scales_l, scales_h, d
     default: return Field{0, 0};
   }
 }

@@ -330,7 +330,7 @@ class ExpertParallelMoE:
                 except Exception as e:  # noqa: BLE001
                     held = e
             if y_in is None:
-                y_in = st.empty((R, x.shape[1]), torch.float16, "y_part")
+                y_in = st.empty((R, x.shape[1]), getattr(st, "partial_dtype", torch.float16), "y_part")   # the type every rank sends
             back = st.empty((sum(send), y_in.shape[1]), y_in.dtype, "y_back")
             dist.all_to_all_single(back, y_in, send, recv, group=self.group)
             if held is not None:

@@ -49,8 +49,8 @@ void orc_set_threads(int n) {
 /* shared/quant.h:36-75 */
 uint32_t orc_block_values(uint32_t t) {
   switch (t) {
-    case ORC_Q8_0: return 32;
-    case ORC_Q4_K: case ORC_Q6_K: case ORC_Q8_K: case ORC_IQ3_S: return 256;
+    case ORC_Q8_0: case ORC_IQ4_NL: return 32;
+    case ORC_Q4_K: case ORC_Q6_K: case ORC_Q8_K: case ORC_IQ3_S: case ORC_IQ4_XS: return 256;
     default: return 0;
   }
 }
@@ -61,10 +61,12 @@ uint32_t orc_block_bytes(uint32_t t) {
     case ORC_Q6_K: return 210;
     case ORC_Q8_K: return 292;
     case ORC_IQ3_S: return 110;
+    case ORC_IQ4_NL: return 18;
+    case ORC_IQ4_XS: return 136;
     default: return 0;
   }
 }
-uint32_t orc_vec_dot_type(uint32_t t) { return t == ORC_Q8_0 ? ORC_Q8_0 : ORC_Q8_K; }
+uint32_t orc_vec_dot_type(uint32_t t) { return t == ORC_Q8_0 || t == ORC_IQ4_NL ? ORC_Q8_0 : ORC_Q8_K; }
 uint64_t orc_row_bytes(uint32_t t, uint64_t n) { return n / orc_block_values(t) * orc_block_bytes(t); }
 
 /* The fields of a block in run order, (offset, size): shared/quant.h:78-169. */
@@ -76,6 +78,8 @@ static uint32_t fields(uint32_t t, uint32_t off[5], uint32_t sz[5]) {
     case ORC_IQ3_S:
       off[0] = 2, sz[0] = 64, off[1] = 74, sz[1] = 32, off[2] = 66, sz[2] = 8, off[3] = 106, sz[3] = 4, off[4] = 0, sz[4] = 2;
       return 5;
+    case ORC_IQ4_NL: off[0] = 2, sz[0] = 16, off[1] = 0, sz[1] = 2; return 2;
+    case ORC_IQ4_XS: off[0] = 8, sz[0] = 128, off[1] = 4, sz[1] = 4, off[2] = 2, sz[2] = 2, off[3] = 0, sz[3] = 2; return 4;
     default: return 0;
   }
 }
@@ -165,6 +169,27 @@ void orc_dequantize_row(uint32_t t, const void *vb, float *y, int64_t n) {
             const int neg = (sg >> (4 * (k % 2) + v)) & 1;
             yy[32 * sb + 4 * k + v] = db * (float)((g >> (8 * v)) & 0xFF) * (neg ? -1.0f : 1.0f);
           }
+        }
+      }
+    } else if (t == ORC_IQ4_NL) {
+      /* y = d * kvalues[nibble]; byte j: low nibble value j, high nibble value j + 16 (QUANT_FORMATS.md:234-244). */
+      const float d = h2f(rd16(b));
+      for (int j = 0; j < 16; j++) {
+        y[i * 32 + j] = d * (float)kIq4nlValues[b[2 + j] & 0xF];
+        y[i * 32 + 16 + j] = d * (float)kIq4nlValues[b[2 + j] >> 4];
+      }
+    } else if (t == ORC_IQ4_XS) {
+      /* y = d * (ls - 32) * kvalues[nibble], ls the sub-block's 6-bit scale: low 4 bits in scales_l, high 2 in scales_h
+       * (QUANT_FORMATS.md:213-226). */
+      const float d = h2f(rd16(b));
+      const uint32_t sh = rd16(b + 2);
+      const uint8_t *sl = b + 4, *qs = b + 8;
+      for (int ib = 0; ib < 8; ib++) {
+        const int ls = (int)(((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+        const float dl = d * (float)ls;
+        for (int j = 0; j < 16; j++) {
+          y[i * QK_K + 32 * ib + j] = dl * (float)kIq4nlValues[qs[16 * ib + j] & 0xF];
+          y[i * QK_K + 32 * ib + 16 + j] = dl * (float)kIq4nlValues[qs[16 * ib + j] >> 4];
         }
       }
     }
@@ -321,12 +346,46 @@ static float dot_iq3_s(int64_t n, const uint8_t *w, const uint8_t *a) {
   return (r0 + r2) + (r1 + r3);
 }
 
+/* IQ4_NL against q8_0: per block the integer sum of table values times codes, times d_w * d_a (QUANT_FORMATS.md:246-247). */
+static float dot_iq4_nl(int64_t n, const uint8_t *w, const uint8_t *a) {
+  float sumf = 0.0f;
+  for (int64_t i = 0; i < n / 32; i++, w += 18, a += 34) {
+    const int8_t *p = (const int8_t *)(a + 2);
+    int sumi = 0;
+    for (int j = 0; j < 16; j++) sumi += (int)kIq4nlValues[w[2 + j] & 0xF] * p[j] + (int)kIq4nlValues[w[2 + j] >> 4] * p[16 + j];
+    sumf += (float)sumi * (h2f(rd16(w)) * h2f(rd16(a)));
+  }
+  return sumf;
+}
+
+/* IQ4_XS against q8_K: per block sum over sub-blocks of (ls - 32) * integer sum, times d_w * d_a (QUANT_FORMATS.md:228-232). */
+static float dot_iq4_xs(int64_t n, const uint8_t *w, const uint8_t *a) {
+  float sumf = 0.0f;
+  for (int64_t i = 0; i < n / QK_K; i++, w += 136, a += 292) {
+    const uint32_t sh = rd16(w + 2);
+    const uint8_t *sl = w + 4, *qs = w + 8;
+    const int8_t *p = (const int8_t *)(a + 4);
+    int isum = 0;
+    for (int ib = 0; ib < 8; ib++) {
+      const int ls = (int)(((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+      int s = 0;
+      for (int j = 0; j < 16; j++)
+        s += (int)kIq4nlValues[qs[16 * ib + j] & 0xF] * p[32 * ib + j] + (int)kIq4nlValues[qs[16 * ib + j] >> 4] * p[32 * ib + 16 + j];
+      isum += ls * s;
+    }
+    sumf += (h2f(rd16(w)) * rdf(a)) * (float)isum;
+  }
+  return sumf;
+}
+
 float orc_vec_dot(uint32_t t, int64_t n, const void *w, const void *a) {
   switch (t) {
     case ORC_Q8_0: return dot_q8_0(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_Q4_K: return dot_q4_K(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_Q6_K: return dot_q6_K(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_IQ3_S: return dot_iq3_s(n, (const uint8_t *)w, (const uint8_t *)a);
+    case ORC_IQ4_NL: return dot_iq4_nl(n, (const uint8_t *)w, (const uint8_t *)a);
+    case ORC_IQ4_XS: return dot_iq4_xs(n, (const uint8_t *)w, (const uint8_t *)a);
     default: return NAN;
   }
 }

@@ -29,7 +29,9 @@ extern "C" {
 #define ORC_Q4_K 12
 #define ORC_Q6_K 14
 #define ORC_Q8_K 15
+#define ORC_IQ4_NL 20
 #define ORC_IQ3_S 21
+#define ORC_IQ4_XS 23
 
 uint32_t orc_block_values(uint32_t type);
 uint32_t orc_block_bytes(uint32_t type);

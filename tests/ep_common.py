@@ -42,6 +42,8 @@ class OracleStages:
 
     # One row per (token, GPU): the same four stages on the CPU. A travelling row is the f32 row, then K int32 expert
     # ids (-1: not on that GPU) and K f32 weights.
+    partial_dtype = torch.float32   # what experts_partial returns here; the GPU stages send f16
+
     @property
     def dispatch_bytes(self):
         return self.E * 4 + self.K * 8

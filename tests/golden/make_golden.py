@@ -15,7 +15,8 @@ sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."
 from c0ven_b200 import synth  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-CLASSES = {synth.Q8_0: quants.Q8_0, synth.Q4_K: quants.Q4_K, synth.Q6_K: quants.Q6_K, synth.IQ3_S: quants.IQ3_S}
+CLASSES = {synth.Q8_0: quants.Q8_0, synth.Q4_K: quants.Q4_K, synth.Q6_K: quants.Q6_K, synth.IQ3_S: quants.IQ3_S,
+           synth.IQ4_NL: quants.IQ4_NL, synth.IQ4_XS: quants.IQ4_XS}
 
 
 def main():

@@ -7,14 +7,14 @@ import pytest
 from c0ven_b200 import synth
 from oracle import oracle as O
 
-TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S]
+TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS]
 
 
 @pytest.mark.parametrize("t", TYPES)
 def test_tables_match_shared_quant_h(t):
     assert O.block_values(t) == synth.BLOCK_VALUES[t]
     assert O.block_bytes(t) == synth.BLOCK_BYTES[t]
-    assert O.vec_dot_type(t) == (O.Q8_0 if t == synth.Q8_0 else O.Q8_K)
+    assert O.vec_dot_type(t) == (O.Q8_0 if t in (synth.Q8_0, synth.IQ4_NL) else O.Q8_K)
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -85,7 +85,8 @@ def test_runs_layout_is_a_permutation(t):
     assert np.array_equal(np.sort(runs.reshape(-1)), np.sort(blocks.reshape(-1)))
     assert np.array_equal(O.from_runs(t, runs).reshape(blocks.shape), blocks)
     # The first run holds every block's quants, block k's at k * size (shared/quant.h:172-176).
-    qoff, qsz = {synth.Q8_0: (2, 32), synth.Q4_K: (16, 128), synth.Q6_K: (0, 128), synth.IQ3_S: (2, 64)}[t]
+    qoff, qsz = {synth.Q8_0: (2, 32), synth.Q4_K: (16, 128), synth.Q6_K: (0, 128), synth.IQ3_S: (2, 64),
+                 synth.IQ4_NL: (2, 16), synth.IQ4_XS: (8, 128)}[t]
     assert np.array_equal(runs.reshape(-1)[:n * qsz].reshape(n, qsz), blocks[:, qoff:qoff + qsz])
 
 
