@@ -41,7 +41,8 @@ def _newer(target: str, deps: list[str]) -> bool:
 def _compile(src: str, force: bool, verbose: bool) -> str:
     obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
-    headers += [os.path.join(ROOT, "include", "moe_layer.h"), os.path.join(ROOT, "include", "engine_abi.h"), os.path.join(ROOT, "build", "iq3s_grid.h")]
+    headers += [os.path.join(ROOT, "include", "moe_layer.h"), os.path.join(ROOT, "include", "engine_abi.h"), os.path.join(ROOT, "build", "iq3s_grid.h"),
+                os.path.join(ROOT, "build", "iq4nl_values.h")]
     if force or _newer(obj, [os.path.join(CSRC, src)] + headers):
         cmd = [NVCC] + ARCH + COMMON + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -58,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     import gen_iq3s_grid
 
     grid_h = os.path.join(ROOT, "build", "iq3s_grid.h")
-    if not os.path.exists(grid_h):
+    if not os.path.exists(grid_h) or not os.path.exists(os.path.join(ROOT, "build", "iq4nl_values.h")):
         gen_iq3s_grid.main(grid_h)
     with cf.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, verbose), sources()))

@@ -12,6 +12,7 @@
 #include <cstdint>
 
 #include "formats.h"
+#include "iq4nl_values.h"
 
 namespace moe {
 
@@ -268,6 +269,91 @@ struct Unit<QT_IQ3_S> {
       s0 = __dp4a(g[6], a1.z, s0), s1 = __dp4a(g[14], a3.z, s1);
       s0 = __dp4a(g[7], a1.w, s0), s1 = __dp4a(g[15], a3.w, s1);
       acc[t] = fmaf(x.d * ((const float *)(a + K))[b], (float)(sc0 * s0 + sc1 * s1), acc[t]);
+    }
+  }
+};
+
+// The 16-entry table of IQ4_NL and IQ4_XS as four words of four signed bytes, entries 4 i .. 4 i + 3 in word i.
+__host__ __device__ constexpr uint32_t iq4_table_word(int i) {
+  return (uint32_t)(uint8_t)kIq4nlValues[4 * i] | (uint32_t)(uint8_t)kIq4nlValues[4 * i + 1] << 8 | (uint32_t)(uint8_t)kIq4nlValues[4 * i + 2] << 16 |
+         (uint32_t)(uint8_t)kIq4nlValues[4 * i + 3] << 24;
+}
+// Table values of the eight nibbles of q: lo = those of its four bytes' low nibbles (byte order kept), hi = of the
+// high ones. A byte permute looks four nibbles up at once: its selector's digits are the nibbles' low three bits
+// (entries 0 .. 7 from the table's first two words, 8 .. 15 from its last two), and a second permute takes each
+// byte from the one or the other by the nibble's fourth bit. A third pair of permutes parts even nibbles from odd.
+__device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t &lo, uint32_t &hi) {
+  constexpr uint32_t T0 = iq4_table_word(0), T1 = iq4_table_word(1), T2 = iq4_table_word(2), T3 = iq4_table_word(3);
+  const uint32_t qa = q & 0xFFFFu, qb = q >> 16;
+  const uint32_t sa = qa & 0x7777u, sb = qb & 0x7777u;
+  const uint32_t r0 = __byte_perm(__byte_perm(T0, T1, sa), __byte_perm(T2, T3, sa), 0x3210u | ((qa & 0x8888u) >> 1));
+  const uint32_t r1 = __byte_perm(__byte_perm(T0, T1, sb), __byte_perm(T2, T3, sb), 0x3210u | ((qb & 0x8888u) >> 1));
+  lo = __byte_perm(r0, r1, 0x6420u), hi = __byte_perm(r0, r1, 0x7531u);
+}
+
+// IQ4_NL: y = d * table[q], blocks of 32 with an f16 scale; a block's 16 bytes hold values 0 .. 15 in their low nibbles
+// and 16 .. 31 in their high ones (QUANT_FORMATS.md:236-247). A unit is one block. Activations are q8_0.
+template <>
+struct Unit<QT_IQ4_NL> {
+  static constexpr int kValues = 32;
+  struct Raw {
+    uint4 q;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.q = ldg_stream16(s + (uint64_t)r * (K / 2) + 16u * u);
+    x.d = __half2float(__ldg((const __half *)(s + 16 * nblk) + (uint64_t)r * (K / 32) + u));
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc, uint32_t n) {
+    uint4 lo, hi;
+    iq4_lookup8(x.q.x, lo.x, hi.x), iq4_lookup8(x.q.y, lo.y, hi.y), iq4_lookup8(x.q.z, lo.z, hi.z), iq4_lookup8(x.q.w, lo.w, hi.w);
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
+      const uint8_t *a = acts + t * stride;
+      const int4 *av = (const int4 *)(a + 32u * u);
+      const int s = dot4x4(lo, av[0]) + dot4x4(hi, av[1]);
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[u], (float)s, acc[t]);
+    }
+  }
+};
+
+// IQ4_XS: y = d * (ls - 32) * table[q], 256 values in eight sub-blocks of 32, each with a 6-bit ls: its low four bits
+// a nibble of scales_l, its high two a pair of bits of scales_h (QUANT_FORMATS.md:213-232). A unit is one sub-block,
+// 16 bytes of qs laid out as IQ4_NL's. Activations are q8_K (its sums are not needed: the table has no offset).
+template <>
+struct Unit<QT_IQ4_XS> {
+  static constexpr int kValues = 32;
+  struct Raw {
+    uint4 q;
+    uint32_t sl, sh;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.q = ldg_stream16(s + (uint64_t)r * (K / 2) + 16u * u);
+    const uint64_t blk = (uint64_t)r * (K / 256) + u / 8;
+    x.sl = __ldg((const uint32_t *)(s + 128 * nblk) + blk);
+    x.sh = __ldg((const uint16_t *)(s + 132 * nblk) + blk);
+    x.d = __half2float(__ldg((const __half *)(s + 134 * nblk) + blk));
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc, uint32_t n) {
+    const uint32_t b = u / 8, ib = u % 8;
+    const int ls = (int)(((x.sl >> (4 * ib)) & 0xF) | (((x.sh >> (2 * ib)) & 3) << 4)) - 32;
+    uint4 lo, hi;
+    iq4_lookup8(x.q.x, lo.x, hi.x), iq4_lookup8(x.q.y, lo.y, hi.y), iq4_lookup8(x.q.z, lo.z, hi.z), iq4_lookup8(x.q.w, lo.w, hi.w);
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
+      const uint8_t *a = acts + t * stride;
+      const int4 *av = (const int4 *)(a + 256 * b + 32 * ib);
+      const int s = dot4x4(lo, av[0]) + dot4x4(hi, av[1]);
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[b], (float)(ls * s), acc[t]);
     }
   }
 };

@@ -388,6 +388,80 @@ struct Decoder<QT_IQ3_S> {
   }
 };
 
+// Sixteen table values (four words of signed bytes) times d2 as f16, into o[0 .. 7].
+__device__ __forceinline__ void int8x16_to_f16(const uint32_t (&w)[4], __half2 d2, uint32_t *o) {
+  const __half2 off = as_h2(0x64806480u);  // 1152 = 1024 + 128
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const uint32_t u = w[j] ^ 0x80808080u;  // int8 + 128
+    o[2 * j] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(u, 0x4140)), off), d2));
+    o[2 * j + 1] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(u, 0x4342)), off), d2));
+  }
+}
+// A block or sub-block of 32 four-bit codes (16 bytes: values 0 .. 15 in the low nibbles, 16 .. 31 in the high ones)
+// through the table, times d2, into chunks 4 h .. 4 h + 3 of the row.
+__device__ __forceinline__ void iq4_store32(const uint4 &q, __half2 d2, uint8_t *tile, uint32_t m, uint32_t h) {
+  uint32_t lo[4], hi[4], o[16];
+  iq4_lookup8(q.x, lo[0], hi[0]), iq4_lookup8(q.y, lo[1], hi[1]), iq4_lookup8(q.z, lo[2], hi[2]), iq4_lookup8(q.w, lo[3], hi[3]);
+  int8x16_to_f16(lo, d2, o), int8x16_to_f16(hi, d2, o + 8);
+#pragma unroll
+  for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
+}
+
+// IQ4_NL: w = d * table[q]. A half is one block of 32.
+template <>
+struct Decoder<QT_IQ4_NL> {
+  static constexpr uint32_t kStageBytes = 32;  // bytes of a row's main quants run a 64-value stage reads
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
+  struct Raw {
+    uint4 q;
+    __half d;
+  };
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + (uint64_t)r * (K / 2) + k0 / 2 + 16 * h;
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    Raw x;
+    x.q = ldg16(quants_at(s, nblk, K, r, k0, h));
+    x.d = __ldg((const __half *)(s + 16 * nblk) + (uint64_t)r * (K / 32) + k0 / 32 + h);
+    return x;
+  }
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *) {
+    iq4_store32(x.q, __half2half2(x.d), tile, m, h);
+  }
+};
+
+// IQ4_XS: w = d * (ls - 32) * table[q]. A half is one sub-block of 32 with its 6-bit ls.
+template <>
+struct Decoder<QT_IQ4_XS> {
+  static constexpr uint32_t kStageBytes = 32;  // bytes of a row's main quants run a 64-value stage reads
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
+  struct Raw {
+    uint4 q;
+    uint32_t ls;
+    __half d;
+  };
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + (uint64_t)r * (K / 2) + k0 / 2 + 16 * h;
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    const uint32_t ib = (k0 % 256) / 32 + h;  // the sub-block within its block
+    const uint64_t blk = (uint64_t)r * (K / 256) + k0 / 256;
+    Raw x;
+    x.q = ldg16(quants_at(s, nblk, K, r, k0, h));
+    const uint32_t sl = __ldg((const uint32_t *)(s + 128 * nblk) + blk), sh = __ldg((const uint16_t *)(s + 132 * nblk) + blk);
+    x.ls = ((sl >> (4 * ib)) & 0xF) | (((sh >> (2 * ib)) & 3) << 4);
+    x.d = __ldg((const __half *)(s + 134 * nblk) + blk);
+    return x;
+  }
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *) {
+    // d * (ls - 32) rounded to f16 once; ls - 32 is in -32 .. 31, exact in f16.
+    iq4_store32(x.q, __float2half2_rn(__half2float(x.d) * (float)((int)x.ls - 32)), tile, m, h);
+  }
+};
+
 }  // namespace tc
 
 
@@ -632,6 +706,10 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
           const uint32_t sw = SM::kQRowBytes == 64 ? (m >> 1) & 3 : m & 7;
           raw[b][0].q = *(const uint4 *)(row + 16 * ((2 * first) ^ sw));
           raw[b][1].q = *(const uint4 *)(row + 16 * ((2 * first + 1) ^ sw));
+          // These reads are the generic proxy's and the copy that refills the slot is the async proxy's: without the
+          // fence the copy was seen to overtake them (a few 128-byte lines of a slot read as the next stage's quants,
+          // run to run different). The fence orders the reads before whatever the arrival below lets loose.
+          fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(q_empty(qb));
         } else {

@@ -40,6 +40,8 @@ static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, i
     ROWS_CASE(QT_Q4_K)
     ROWS_CASE(QT_Q6_K)
     ROWS_CASE(QT_IQ3_S)
+    ROWS_CASE(QT_IQ4_NL)
+    ROWS_CASE(QT_IQ4_XS)
     default: return cudaErrorInvalidValue;
   }
 #undef ROWS_CASE
@@ -55,6 +57,8 @@ static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a,
     TILES_CASE(QT_Q4_K)
     TILES_CASE(QT_Q6_K)
     TILES_CASE(QT_IQ3_S)
+    TILES_CASE(QT_IQ4_NL)
+    TILES_CASE(QT_IQ4_XS)
     default: return cudaErrorInvalidValue;
   }
 #undef TILES_CASE
@@ -217,7 +221,7 @@ void check_config(const moe_layer_config &c, const moe_layer_weights &w) {
   if (c.n_ff == 0 || c.n_ff % 256 || c.n_ff > kRowsMaxK) bad("n_ff must be a multiple of 256, at most 16384");
   if (c.n_experts == 0 || c.n_experts % 32 || c.n_experts > 512) bad("n_experts must be a multiple of 32, at most 512");
   if (c.n_used == 0 || c.n_used > 16 || c.n_used > c.n_experts) bad("n_used must be 1 .. 16 and at most n_experts");
-  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K or IQ3_S");
+  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K, IQ3_S, IQ4_NL or IQ4_XS");
   if (c.shexp_gate_type && (!type_known(c.shexp_gate_type) || !type_known(c.shexp_down_type)))
     bad("the shared expert's types must be Q8_0, Q4_K, Q6_K or IQ3_S");
   if (c.expert_first + (c.expert_count ? c.expert_count : c.n_experts - c.expert_first) > c.n_experts)

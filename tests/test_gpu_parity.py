@@ -9,7 +9,7 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S]
+TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS]
 MAX_REL, MIN_COS = 1e-2, 0.9999   # the bar the layer is held to
 # Routing weights: 1e-5 where the logits are the exactly ordered fp32 sums (steps of up to 64 rows). Longer steps take
 # their logits from the tensor-core product, a few 1e-6 from those sums; the weights follow, while the expert ids, which
@@ -81,6 +81,27 @@ def test_same_bits_twice_and_alone_or_batched():
     assert np.array_equal(a, b) and np.array_equal(ids_a, ids_b) and np.array_equal(inv_a, inv_b)
     gpu.forward(x[17:18])
     assert np.array_equal(gpu.route(1)[0][0], ids_a[17])
+    gpu.close()
+
+
+def test_tile_kernels_give_the_same_bits_every_run():
+    """The tensor-core path at the full shape, with types mixed so that kernels of different kinds follow one another
+    (Q4_K's quants come through a ring of bulk copies, the others' by the warps' own loads): six runs, the same bits of
+    the output and of every quantised inner row. (A copy that refilled a ring slot before the warps' reads of it were
+    done once showed here as a few wrong weight rows, different from run to run.)"""
+    layer = synth.make_layer(gate_type=synth.Q4_K, down_type=synth.Q6_K, shexp_gate_type=synth.Q8_0, shexp_down_type=synth.Q8_0,
+                             zipf_s=1.1, seed=5)
+    gpu = MoELayer(layer, max_tokens=2048)
+    x = synth.make_input(2048, 2048, seed=77)
+    first = None
+    for _ in range(6):
+        out = gpu.forward(x).copy()
+        q, d, _bs = gpu.quantized(2048, inner=True)
+        if first is None:
+            first = (out, q.copy(), d.copy())
+        else:
+            assert np.array_equal(q, first[1]) and np.array_equal(d, first[2])
+            assert np.array_equal(out, first[0])
     gpu.close()
 
 
@@ -258,9 +279,9 @@ def test_full_shape_sweep_q4k_q6k_q8_0():
     gpu.close()
 
 
-@pytest.mark.parametrize("t", [synth.Q8_0, synth.Q6_K])
+@pytest.mark.parametrize("t", [synth.Q8_0, synth.Q6_K, synth.IQ4_NL, synth.IQ4_XS])
 def test_tile_kernels_full_shape_other_types(t):
-    """The tile kernels' Q8_0 and Q6_K decoders at the full shape (rows of 2048 and of 512 values), every expert on them."""
+    """The tile kernels' Q8_0, Q6_K, IQ4_NL and IQ4_XS decoders at the full shape (rows of 2048 and of 512 values), every expert on them."""
     layer = synth.make_layer(gate_type=t, zipf_s=1.1, seed=300 + t)
     gpu = MoELayer(layer, max_tokens=700, tensor_min_rows=1)
     x = synth.make_input(700, 2048, seed=11)
