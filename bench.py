@@ -360,14 +360,17 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
         step_host()
     barrier()
     e2e_times = []
-    while len(e2e_times) < steps or (sum(e2e_times) < MIN_TIMED_S and len(e2e_times) < MAX_TIMED_STEPS):
+    while True:
         t0 = time.perf_counter()
         step_host()
         torch.cuda.synchronize()
         e2e_times.append(time.perf_counter() - t0)
-        if dist and len(e2e_times) >= steps:  # every rank stops after the same step
-            if agree(sum(e2e_times), torch.distributed.ReduceOp.MIN) >= MIN_TIMED_S:
-                break
+        if len(e2e_times) < steps:
+            continue
+        # Every rank stops after the same step: the decision rests on numbers every rank holds.
+        total = agree(sum(e2e_times), torch.distributed.ReduceOp.MIN) if dist else sum(e2e_times)
+        if total >= MIN_TIMED_S or len(e2e_times) >= MAX_TIMED_STEPS:
+            break
     e2e_s = agree(statistics.median(e2e_times), MAX)
 
     # Expert parallel: the rows each rank's experts ran in the last step (routing skew shows here: the busiest rank

@@ -123,6 +123,62 @@ __device__ __forceinline__ void tma_load_quants(uint32_t dst_smem, const CUtenso
                ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(bar)
                : "memory");
 }
+// --- A pair of CTAs (a cluster of two on the two SMs of a TPC) that share one product: tcgen05's cta_group::2. ---
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of the same place in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// Arrivals on a barrier that may be the other CTA's (a shared::cluster address). What the arriving thread wrote for the
+// tensor core to read has passed its own fence.proxy.async before; a release for the whole cluster on every arrival
+// was measured to cost the decode warps a third of their rate and is left out, as in CUTLASS's pipelines for a pair.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_cluster(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// All threads of both CTAs.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tma_load_rows by a CTA of a pair: the bytes land in this CTA's shared memory and are counted on the barrier `bar`,
+// which may be the other CTA's (a shared::cluster address).
+__device__ __forceinline__ void tma_load_rows_pair(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// The pair's commit: one arrival on the barrier at this place in each CTA of the mask.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint32_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)cta_mask)
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A[256 rows: 128 in each CTA's shared memory] * B[n rows: half in each CTA's]^T, issued by
+// one thread of the pair's first CTA; the descriptors name the same places in both.
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -155,7 +211,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *v) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The wait, naming the registers the loads fill: nothing that reads them can be scheduled before it.
+__device__ __forceinline__ void tmem_ld_wait8(uint32_t *v) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t *v) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                 "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
+}
 
 // A K-major operand tile without swizzle: core matrices of 8 rows x 16 bytes, contiguous (128 bytes); the next 8
 // values of the contraction 128 bytes on (the leading offset), the next 8 rows 1024 bytes on (the stride offset).
@@ -170,7 +246,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // kind::f16 instruction descriptor: f32 accumulator, f16 A and B, both K-major, M 128, N n.
-__device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((kTileM >> 4) << 24); }
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n, uint32_t m = kTileM) { return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24); }
 
 __device__ __forceinline__ void store_chunk(uint8_t *tile, uint32_t row, uint32_t kc, uint4 v) {
   *(uint4 *)(tile + (row >> 3) * kSbo + kc * kLbo + (row & 7) * 16) = v;
@@ -475,10 +551,12 @@ __host__ __device__ constexpr bool quants_by_copy(uint32_t qt) { return qt == QT
 // quants come by copy) a ring of two quant slots, then the barriers, then IQ3_S's codebook.
 // A quant slot holds, for every weight row of the item, the quants of one stage per decode group: 32 bytes a stage for
 // Q4_K, so 64 bytes a row with two groups (64-byte swizzle) and 128 with four (128-byte swizzle).
-template <int QT, int NMAT>
+template <int QT, int NMAT, bool PAIR = false>
 struct TileSmem {
-  static constexpr uint32_t kStages = NMAT == 2 ? 3 : 4;
-  static constexpr uint32_t kWBytes = kTileM * kTileK * 2, kXBytes = kTileN * kTileK * 2;
+  // A CTA of a pair holds half the rows' tile, which leaves room for more stages.
+  static constexpr uint32_t kStages = PAIR ? (NMAT == 2 ? 4 : 6) : (NMAT == 2 ? 3 : 4);
+  static constexpr uint32_t kXRows = PAIR ? kTileN / 2 : kTileN;
+  static constexpr uint32_t kWBytes = kTileM * kTileK * 2, kXBytes = kXRows * kTileK * 2;
   static constexpr uint32_t kStageBytes = NMAT * kWBytes + kXBytes;
   static constexpr uint32_t kGroups = kTileDecoders / (NMAT * kTileM);                // decode groups: 2 or 4
   static constexpr uint32_t kQRowBytes = kGroups * 32;                                // a row's bytes in a quant slot
@@ -501,6 +579,7 @@ __device__ __forceinline__ float swiglu_fast(float g, float u, float limit) {
   }
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
+
 
 // The tile a work item belongs to.
 struct ItemTile {
@@ -527,12 +606,12 @@ __device__ __forceinline__ ItemTile item_tile(const ExpertTilesArgs &a, uint32_t
 // gate/up item of more than 128 rows needs both buffers (gate in one, up in the other): the MMAs of the next item
 // wait for its epilogue, and to keep that short the decode warps join the epilogue warps for it.
 // Dynamic shared memory TileSmem::kBytes.
-template <int QT, int NMAT>
+template <int QT, int NMAT, bool PAIR>
 __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_constant__ ExpertTilesArgs a,
                                                                   const __grid_constant__ CUtensorMap act_map,
                                                                   const uint32_t *__restrict__ grid_global) {
   using namespace tc;
-  using SM = TileSmem<QT, NMAT>;
+  using SM = TileSmem<QT, NMAT, PAIR>;
   using Dec = Decoder<QT>;
   using Raw = typename Dec::Raw;
   constexpr uint32_t S = SM::kStages, kCols = 512;
@@ -547,8 +626,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
 
   const uint32_t K = a.K, KT = K / kTileK, RT = a.R / kTileM;
   const uint32_t ntiles = a.tiles ? *a.ntiles : (a.dense_rows + kTileN - 1) / kTileN;
-  const uint32_t nitems = ntiles * RT;
-  if (blockIdx.x >= nitems) return;
+  // PAIR: the CTAs come in clusters of two, on the two SMs of a TPC. A pair is one unit of work: its item is 256 weight
+  // rows (128 decoded by each CTA) times the tile's rows, of which each CTA brings half into its own shared memory;
+  // the first CTA's MMA thread issues one tcgen05.mma.cta_group::2 for both, which reads both halves and writes each
+  // CTA's 128 weight rows of the product into that CTA's tensor memory. What a CTA's shared memory carries per flop
+  // is the weights as before but only half the rows, and shared-memory bandwidth is what bounds the single-CTA form.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0;
+  const uint32_t unit = PAIR ? blockIdx.x / 2 : blockIdx.x, nunits = PAIR ? gridDim.x / 2 : gridDim.x;
+  const uint32_t RTU = PAIR ? RT / 2 : RT;  // a big tile's items
+  const uint32_t nitems = ntiles * RTU;
+  if (unit >= nitems) return;  // both CTAs of a pair alike
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   uint64_t *bars = (uint64_t *)(smem + SM::kBarriers);
   const uint32_t bar0 = smem_u32(bars);
@@ -567,29 +654,51 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
   // (the copy thread's arrival states their bytes; the copy unit counts them off). An accumulator buffer is empty again
   // when the epilogue warps have read it; after an item that took both buffers, also when the decode warps have.
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kDW / kDecGroups + 1), mbar_init(empty_bar(s), 1);
-    for (uint32_t b = 0; b < 2; b++) mbar_init(acc_full(b), 1), mbar_init(acc_empty(b), kEW);
-    mbar_init(acc_empty_wide, kDW);
+    // In a pair the first CTA's full, accumulator-empty barriers take both CTAs' arrivals.
+    constexpr uint32_t kCtas = PAIR ? 2 : 1;
+    for (uint32_t s = 0; s < S; s++) mbar_init(full_bar(s), kCtas * (kDW / kDecGroups + 1)), mbar_init(empty_bar(s), 1);
+    for (uint32_t b = 0; b < 2; b++) mbar_init(acc_full(b), 1), mbar_init(acc_empty(b), kCtas * kEW);
+    mbar_init(acc_empty_wide, kCtas * kDW);
     for (uint32_t b = 0; b < 2; b++) mbar_init(q_full(b), 1), mbar_init(q_empty(b), kDW);
     *abort = 0;
     fence_barrier_init();
   }
   if constexpr (QT == QT_IQ3_S)
     for (uint32_t i = tid; i < 512; i += blockDim.x) grid[i] = grid_global[i];
-  if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_slot), kCols);
+  if (warp == kMmaWarp) {
+    if constexpr (PAIR)
+      tmem_alloc_pair(smem_u32(tmem_slot), kCols);  // the same warp of both CTAs, the same place for the address
+    else
+      tmem_alloc(smem_u32(tmem_slot), kCols);
+  }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();  // the other CTA's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  // The first CTA's barriers, as the pair's other CTA names them (for the first CTA itself: its own).
+  const uint32_t bar0_lead = PAIR ? map_to_cta(bar0, 0) : bar0;
+  auto full_lead = [&](uint32_t s) { return bar0_lead + 8 * s; };
+  auto acc_empty_lead = [&](uint32_t b) { return bar0_lead + 8 * (2 * S + 2 + b); };
+  const uint32_t acc_empty_wide_lead = bar0_lead + 8 * (2 * S + 4);
+  // Arrivals that in a pair go to the first CTA's barrier.
+  auto arrive_lead = [&](uint32_t lead_bar, uint32_t own_bar) {
+    if constexpr (PAIR)
+      mbar_arrive_cluster(lead_bar);
+    else
+      mbar_arrive(own_bar);
+  };
+  // The weight rows of an item that this CTA decodes and drains.
+  auto item_rows0 = [&](uint32_t item) { return ((item % RTU) * (PAIR ? 2u : 1u) + rank) * kTileM; };
 
   // CTA b's item of round r: the items come sorted by size (full tiles first, then the others by falling row count), and
   // the rounds deal them boustrophedon (b, then G - 1 - b, ...), so that every CTA gets a like share of long and short
   // items. kNoItem past the end; a CTA's last round may have no item for it while others still have one.
   constexpr uint32_t kNoItem = 0xFFFFFFFFu;
   auto item_at = [&](uint32_t rnd) {
-    const uint32_t base = rnd * gridDim.x;
-    const uint32_t i = base + ((rnd & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+    const uint32_t base = rnd * nunits;
+    const uint32_t i = base + ((rnd & 1) ? nunits - 1 - unit : unit);
     return i < nitems ? i : kNoItem;
   };
 
@@ -600,46 +709,77 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
   auto use_inc = [&](uint32_t b) { use0 += b == 0, use1 += b == 1; };
   auto is_wide = [&](uint32_t count) { return NMAT == 2 && count > kTileN / 2; };
 
-  // Columns q (this warp's quarter of the weight rows: TMEM lanes 32 q ..) of chunks slot, slot + nslots, ... of 16 rows
+  // Columns q (this warp's quarter of the weight rows: TMEM lanes 32 q ..) of chunks slot, slot + nslots, ... of W rows
   // each, from the accumulators at column colg (and colu, the up product) to the result. A lane holds one weight row's
-  // values for the chunk's 16 rows; for each row the warp's 32 lanes store 32 consecutive values. The address of a
+  // values for the chunk's W rows; for each row the warp's 32 lanes store 32 consecutive values. The address of a
   // chunk is worked out once and stepped by the row stride: what the loop costs per value is a conversion and a store.
+  // The loads of a warp's next chunk are in flight while it converts and stores the one before (two sets of
+  // registers): what a chunk costs is then its instructions, not tensor memory's latency, which alone had the down
+  // product's four epilogue warps take longer over an item than its MMAs do.
   auto drain = [&](const ItemTile &t, uint32_t r0, uint32_t colg, uint32_t colu, uint32_t slot, uint32_t nslots) {
-    const uint32_t q = warp % 4, r = r0 + 32 * q + lane, N = (t.count + 15) & ~15u;
-    for (uint32_t c = slot; c < N / 16; c += nslots) {
-      uint32_t gv[16], uv[16];
-      tmem_ld16(tmem_base + ((32 * q) << 16) + colg + 16 * c, gv);
-      if constexpr (NMAT == 2) tmem_ld16(tmem_base + ((32 * q) << 16) + colu + 16 * c, uv);
-      tmem_ld_wait();
-      float v[16];
+    constexpr int W = NMAT == 2 ? 8 : 16;
+    const uint32_t q = warp % 4, r = r0 + 32 * q + lane, nch = ((t.count + 15) & ~15u) / W;
+    const uint32_t lanes = tmem_base + ((32 * q) << 16);
+    auto load = [&](uint32_t c, uint32_t *g, uint32_t *u) {
+      if constexpr (NMAT == 2)
+        tmem_ld8(lanes + colg + W * c, g), tmem_ld8(lanes + colu + W * c, u);
+      else
+        tmem_ld16(lanes + colg + W * c, g);
+    };
+    auto wait = [&](uint32_t *g, uint32_t *u) {
+      if constexpr (NMAT == 2)
+        tmem_ld_wait8(g), tmem_ld_wait8(u);
+      else
+        tmem_ld_wait16(g);
+    };
+    auto store = [&](uint32_t c, const uint32_t *g, const uint32_t *u) {
+      if (W * c >= t.count) return;           // a chunk of rows past the tile's (the rows are rounded up to 16)
+      const uint32_t left = t.count - W * c;  // rows of the chunk that exist
+      float v[W];
 #pragma unroll
-      for (int j = 0; j < 16; j++) {
-        v[j] = __uint_as_float(gv[j]);
-        if constexpr (NMAT == 2) v[j] = swiglu_fast(v[j], __uint_as_float(uv[j]), a.limit);
+      for (int j = 0; j < W; j++) {
+        v[j] = __uint_as_float(g[j]);
+        if constexpr (NMAT == 2) v[j] = swiglu_fast(v[j], __uint_as_float(u[j]), a.limit);
       }
-      const uint32_t left = t.count - 16 * c;  // rows of the chunk that exist: at least one
-      const uint64_t at = (uint64_t)(t.start + 16 * c) * a.out_stride + r;
+      const uint64_t at = (uint64_t)(t.start + W * c) * a.out_stride + r;
       if (a.out_f16) {
         __half *p = (__half *)a.out + at;
-        if (left >= 16) {
+        if (left >= (uint32_t)W) {
 #pragma unroll
-          for (int j = 0; j < 16; j++) p[(uint64_t)j * a.out_stride] = __float2half_rn(v[j]);
+          for (int j = 0; j < W; j++) p[(uint64_t)j * a.out_stride] = __float2half_rn(v[j]);
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; j++)
+          for (int j = 0; j < W; j++)
             if ((uint32_t)j < left) p[(uint64_t)j * a.out_stride] = __float2half_rn(v[j]);
         }
       } else {
         float *p = (float *)a.out + at;
-        if (left >= 16) {
+        if (left >= (uint32_t)W) {
 #pragma unroll
-          for (int j = 0; j < 16; j++) p[(uint64_t)j * a.out_stride] = v[j];
+          for (int j = 0; j < W; j++) p[(uint64_t)j * a.out_stride] = v[j];
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; j++)
+          for (int j = 0; j < W; j++)
             if ((uint32_t)j < left) p[(uint64_t)j * a.out_stride] = v[j];
         }
       }
+    };
+    uint32_t gA[W], gB[W], uA[NMAT == 2 ? W : 1], uB[NMAT == 2 ? W : 1];
+    uint32_t c = slot;
+    if (c >= nch) return;
+    load(c, gA, uA);
+    for (;;) {
+      wait(gA, uA);
+      uint32_t cn = c + nslots;
+      if (cn < nch) load(cn, gB, uB);
+      store(c, gA, uA);
+      if (cn >= nch) break;
+      c = cn, cn = c + nslots;
+      wait(gB, uB);
+      if (cn < nch) load(cn, gA, uA);
+      store(c, gB, uB);
+      if (cn >= nch) break;
+      c = cn;
     }
   };
 
@@ -656,19 +796,19 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
     if constexpr (quants_by_copy(QT)) {
       const uint32_t i0 = item_at(0);
       if (i0 != kNoItem && first < KT) {
-        const ItemTile t0 = item_tile(a, i0 / RT);
-        hdr_ahead = Dec::fetch_hdr((mat == 0 ? a.w0 : a.w1) + (uint64_t)t0.slot * a.slice_bytes, nblk, K, (i0 % RT) * kTileM + m,
+        const ItemTile t0 = item_tile(a, i0 / RTU);
+        hdr_ahead = Dec::fetch_hdr((mat == 0 ? a.w0 : a.w1) + (uint64_t)t0.slot * a.slice_bytes, nblk, K, item_rows0(i0) + m,
                                    (first * kTileK) & ~255u);
       }
     }
     for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
-      const ItemTile t = item_tile(a, item / RT);
-      const uint32_t r0 = (item % RT) * kTileM;
+      const ItemTile t = item_tile(a, item / RTU);
+      const uint32_t r0 = item_rows0(item);
       const uint8_t *wm = (mat == 0 ? a.w0 : a.w1) + (uint64_t)t.slot * a.slice_bytes;
       // The next item's weights and rows, known early: its first header is asked for at this item's last stage.
       const uint32_t item_after = quants_by_copy(QT) ? item_at(rnd + 1) : kNoItem;
       ItemTile t_after{0, 0, 0};
-      if (item_after != kNoItem) t_after = item_tile(a, item_after / RT);
+      if (item_after != kNoItem) t_after = item_tile(a, item_after / RTU);
       // Quants come from HBM the first time an expert is touched; a request for the L2 goes out kAhead stages before
       // the load into registers, which itself goes a stage of this thread's before the decode.
       constexpr uint32_t kLineStages = 128 / Dec::kStageBytes;
@@ -688,7 +828,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
             if (it2 * kTileK / 256 != blk_fetched) hdr_ahead = Dec::fetch_hdr(wm, nblk, K, r0 + m, (it2 * kTileK) & ~255u);
           } else if (item_after != kNoItem) {
             hdr_ahead = Dec::fetch_hdr((mat == 0 ? a.w0 : a.w1) + (uint64_t)t_after.slot * a.slice_bytes, nblk, K,
-                                       (item_after % RT) * kTileM + m, (first * kTileK) & ~255u);
+                                       item_rows0(item_after) + m, (first * kTileK) & ~255u);
           }
         } else {
           if (k0 / 256 != blk_fetched) hdr_last = Dec::fetch_hdr(wm, nblk, K, r0 + m, k0 & ~255u), blk_fetched = k0 / 256;
@@ -729,7 +869,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         Dec::store(hdr[b], raw[b][1], tile, m, 1, k0, grid);
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(s));
+        if (lane == 0) arrive_lead(full_lead(s), full_bar(s));
       };
       // The first lines of a row's quants are asked for an item ahead (below), so that an item does not begin by
       // waiting for HBM; the CTA's first item asks for its own.
@@ -751,8 +891,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         if (it + kDecGroups < KT) fetch(1, it + kDecGroups);
         stage_step(0, it);
         if (it == 0 && item_next != kNoItem) {  // group 0, after its first stage: the next item's first lines
-          const ItemTile tn = item_tile(a, item_next / RT);
-          ask_ahead((mat == 0 ? a.w0 : a.w1) + (uint64_t)tn.slot * a.slice_bytes, (item_next % RT) * kTileM + m);
+          const ItemTile tn = item_tile(a, item_next / RTU);
+          ask_ahead((mat == 0 ? a.w0 : a.w1) + (uint64_t)tn.slot * a.slice_bytes, item_rows0(item_next) + m);
         }
         if (!ok || it + kDecGroups >= KT) break;
         if (it + 2 * kDecGroups < KT) fetch(0, it + 2 * kDecGroups);
@@ -768,7 +908,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
           drain(t, r0, 0, kTileN, warp / 4, kDW / 4 + 1);
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_wide);
+          if (lane == 0) arrive_lead(acc_empty_wide_lead, acc_empty_wide);
         }
         use0++, use1++, wides++;
       } else {
@@ -779,8 +919,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
     // Epilogue warps: warp w reads TMEM lanes 32 (w % 4) .., its quarter of the weight rows.
     uint32_t li = 0;
     for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
-      const ItemTile t = item_tile(a, item / RT);
-      const uint32_t r0 = (item % RT) * kTileM;
+      const ItemTile t = item_tile(a, item / RTU);
+      const uint32_t r0 = item_rows0(item);
       if (is_wide(t.count)) {
         if (ok) ok = mbar_wait(acc_full(0), use0 & 1, abort, a.error);
         if (ok) ok = mbar_wait(acc_full(1), use1 & 1, abort, a.error);
@@ -789,7 +929,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         drain(t, r0, 0, kTileN, kDW / 4, kDW / 4 + 1);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty(0)), mbar_arrive(acc_empty(1));
+        if (lane == 0) arrive_lead(acc_empty_lead(0), acc_empty(0)), arrive_lead(acc_empty_lead(1), acc_empty(1));
         use0++, use1++, wides++;
       } else {
         const uint32_t b = next_buf;
@@ -799,7 +939,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         drain(t, r0, b * kTileN, b * kTileN + kTileN / 2, 0, 1);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty(b));
+        if (lane == 0) arrive_lead(acc_empty_lead(b), acc_empty(b));
         use_inc(b), next_buf ^= 1;
       }
     }
@@ -809,16 +949,26 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
     if (lane == 0) {
       uint32_t li = 0;
       for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
-        const ItemTile t = item_tile(a, item / RT);
-        const uint32_t nbox = (t.count + kTileBoxRows - 1) / kTileBoxRows;
+        const ItemTile t = item_tile(a, item / RTU);
+        // A CTA of a pair brings its half of the rows the instruction takes (the rows rounded up to 16): the first
+        // CTA the first half.
+        const uint32_t half = ((t.count + 15) & ~15u) / 2;
+        const uint32_t mine = PAIR ? half : t.count, row0 = t.start + (PAIR ? rank * half : 0);
+        const uint32_t nbox = (mine + kTileBoxRows - 1) / kTileBoxRows;
         for (uint32_t it = 0; it < KT && ok; it++) {
           const uint32_t g = li * KT + it, s = g % S, use_s = g / S;
           if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
           if (!ok) break;
           const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + NMAT * SM::kWBytes;
-          mbar_arrive_expect(full_bar(s), nbox * kTileBoxRows * kTileK * 2);
-          for (uint32_t i = 0; i < nbox; i++)
-            tma_load_rows(xt + i * kTileBoxRows * kTileK * 2, &act_map, it * kTileK, t.start + i * kTileBoxRows, full_bar(s));
+          if constexpr (PAIR) {
+            mbar_arrive_expect_cluster(full_lead(s), nbox * kTileBoxRows * kTileK * 2);
+            for (uint32_t i = 0; i < nbox; i++)
+              tma_load_rows_pair(xt + i * kTileBoxRows * kTileK * 2, &act_map, it * kTileK, row0 + i * kTileBoxRows, full_lead(s));
+          } else {
+            mbar_arrive_expect(full_bar(s), nbox * kTileBoxRows * kTileK * 2);
+            for (uint32_t i = 0; i < nbox; i++)
+              tma_load_rows(xt + i * kTileBoxRows * kTileK * 2, &act_map, it * kTileK, row0 + i * kTileBoxRows, full_bar(s));
+          }
         }
       }
       if (!ok) {
@@ -832,7 +982,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
       // as the decode warps have read the slot's last contents; it runs ahead of the stages by the ring's two slots.
       uint32_t li = 0;
       for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
-        const ItemTile t = item_tile(a, item / RT);
+        const ItemTile t = item_tile(a, item / RTU);
         for (uint32_t j = 0; j < KT / kDecGroups && ok; j++) {
           const uint32_t qn = li * (KT / kDecGroups) + j, qb = qn % SM::kQSlots, use_q = qn / SM::kQSlots;
           if (use_q > 0) ok = mbar_wait(q_empty(qb), (use_q - 1) & 1, abort, a.error);
@@ -840,7 +990,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
           const uint32_t dst = smem_u32(smem + SM::kQuants + qb * SM::kQSlotBytes);
           mbar_arrive_expect(q_full(qb), SM::kQSlotBytes);
           for (uint32_t mt = 0; mt < (uint32_t)NMAT; mt++)
-            tma_load_quants(dst + mt * SM::kQMatBytes, &a.qmap[mt], j * SM::kQRowBytes, (item % RT) * kTileM, t.slot, q_full(qb));
+            tma_load_quants(dst + mt * SM::kQMatBytes, &a.qmap[mt], j * SM::kQRowBytes, item_rows0(item), t.slot, q_full(qb));
         }
       }
       if (!ok) {
@@ -849,51 +999,71 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         }
       }
     }
-  } else if (lane == 0) {
-    // The MMA thread: per stage, four K steps of 16 for each matrix; the commit frees the stage when they are done.
+  } else if (lane == 0 && rank == 0) {
+    // The MMA thread (of a pair's first CTA): per stage, four K steps of 16 for each matrix; the commit frees the stage
+    // when they are done, in both CTAs of a pair.
+    auto wait_lead = [&](uint32_t bar, uint32_t parity) { return mbar_wait(bar, parity, abort, a.error); };
+    auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+      if constexpr (PAIR)
+        mma_f16_pair(d, da, db, idesc, acc);
+      else
+        mma_f16(d, da, db, idesc, acc);
+    };
+    auto commit = [&](uint32_t bar) {
+      if constexpr (PAIR)
+        mma_commit_pair(bar, 3);
+      else
+        mma_commit(bar);
+    };
     uint32_t li = 0;
     bool after_wide = false;
     for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
-      const ItemTile t = item_tile(a, item / RT);
-      const uint32_t idesc = instr_desc((t.count + 15) & ~15u);
+      const ItemTile t = item_tile(a, item / RTU);
+      const uint32_t idesc = instr_desc((t.count + 15) & ~15u, PAIR ? 2 * kTileM : kTileM);
       const bool wide = is_wide(t.count);
       const uint32_t b = next_buf, colg = wide ? 0 : b * kTileN, colu = wide ? kTileN : colg + kTileN / 2;
       // The buffers this item writes must have been read: by the epilogue warps, and after a two-buffer item by the
       // decode warps too.
-      if (after_wide) ok = mbar_wait(acc_empty_wide, (wides - 1) & 1, abort, a.error);
+      if (after_wide) ok = wait_lead(acc_empty_wide, (wides - 1) & 1);
       after_wide = false;
       for (uint32_t bb = 0; bb < 2 && ok; bb++)
-        if ((wide || bb == b) && use_of(bb) > 0) ok = mbar_wait(acc_empty(bb), (use_of(bb) - 1) & 1, abort, a.error);
+        if ((wide || bb == b) && use_of(bb) > 0) ok = wait_lead(acc_empty(bb), (use_of(bb) - 1) & 1);
       for (uint32_t it = 0; it < KT && ok; it++) {
         const uint32_t g = li * KT + it, s = g % S;
-        ok = mbar_wait(full_bar(s), (g / S) & 1, abort, a.error);
+        ok = wait_lead(full_bar(s), (g / S) & 1);
         if (!ok) break;
         tc_fence_after();
         const uint32_t stage = smem_u32(smem + s * SM::kStageBytes), xt = stage + NMAT * SM::kWBytes;
 #pragma unroll
         for (uint32_t k = 0; k < kTileK / 16; k++) {
           const uint64_t db = smem_desc_sw128(xt + 32 * k);
-          mma_f16(tmem_base + colg, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
-          if constexpr (NMAT == 2) mma_f16(tmem_base + colu, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
+          mma(tmem_base + colg, smem_desc(stage + 2 * k * kLbo), db, idesc, (it | k) != 0);
+          if constexpr (NMAT == 2) mma(tmem_base + colu, smem_desc(stage + SM::kWBytes + 2 * k * kLbo), db, idesc, (it | k) != 0);
         }
-        mma_commit(empty_bar(s));
+        commit(empty_bar(s));
       }
       if (!ok) break;
       if (wide) {
-        mma_commit(acc_full(0)), mma_commit(acc_full(1));
+        commit(acc_full(0)), commit(acc_full(1));
         use0++, use1++, wides++, after_wide = true;
       } else {
-        mma_commit(acc_full(b));
+        commit(acc_full(b));
         use_inc(b), next_buf ^= 1;
       }
     }
   }
   tc_fence_before();
   __syncthreads();
+  // Neither CTA of a pair may leave (or free tensor memory) while the other may still read its shared memory or write
+  // its tensor memory.
+  if constexpr (PAIR) cluster_sync();
   if (warp == kMmaWarp) {
     __syncwarp();
     tc_fence_after();
-    tmem_free(tmem_base, kCols);
+    if constexpr (PAIR)
+      tmem_free_pair(tmem_base, kCols);
+    else
+      tmem_free(tmem_base, kCols);
   }
 }
 

@@ -271,6 +271,70 @@ __device__ __forceinline__ float exact_logits4(const float *__restrict__ x, cons
   return tot;
 }
 
+// exact_logits4 with the operands brought through shared memory. A lane walking its own piece of a row from global
+// memory touches, with the other lanes, 32 different lines an instruction, and the tag stage of L1 then sets the pace
+// (measured: two thirds of its peak, the kernel's limit). Here the warp copies the row and the four experts' rows
+// chunk by chunk with 16-byte asynchronous copies, eight lanes to a piece's 128 contiguous bytes, the next chunk on
+// its way while this one is summed; the lanes read their pieces from shared memory, whose padding (a piece's chunk
+// every 144 bytes) spreads a quarter-warp's eight 16-byte reads over all banks. The sums are the same chains.
+constexpr uint32_t kExChunk = 32;                        // values of each piece a chunk holds
+constexpr uint32_t kExPiece = kExChunk * 4 + 16;         // bytes from one piece's chunk to the next in shared memory
+constexpr uint32_t kExRow = kRouterPieces * kExPiece;    // a row's chunk: 1,152 bytes
+constexpr uint32_t kExBuf = 5 * kExRow;                  // the row and four experts' rows
+constexpr uint32_t kExWarpBytes = 2 * kExBuf;            // two chunks: 11,520 bytes a warp
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ float exact_logits4_staged(const float *__restrict__ x, const float *__restrict__ W, const float *__restrict__ bias,
+                                                      uint32_t E, uint32_t e, uint32_t lane, uint8_t *buf) {
+  const uint32_t piece = E / kRouterPieces, nch = piece / kExChunk, s = lane % 8, g = lane / 8;
+  const uint32_t buf32 = (uint32_t)__cvta_generic_to_shared(buf);
+  // The four experts of the pass, known to every lane.
+  uint32_t ex[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) ex[j] = __shfl_sync(0xffffffffu, e, 8 * j);
+  auto issue = [&](uint32_t c, uint32_t b) {
+    // A row's chunk is 8 pieces x 128 bytes: 64 copies of 16 bytes, two a lane.
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+      const uint32_t idx = k * 32 + lane, pc = idx / 8, j = idx % 8;
+      const uint64_t off = (uint64_t)pc * piece + c * kExChunk + j * 4;
+      const uint32_t dst = buf32 + b * kExBuf + pc * kExPiece + j * 16;
+      cp_async16(dst, x + off);
+#pragma unroll
+      for (int r = 0; r < 4; r++) cp_async16(dst + (1 + r) * kExRow, W + (uint64_t)ex[r] * E + off);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float p = 0.0f;
+  issue(0, 0);
+  for (uint32_t c = 0; c < nch; c++) {
+    if (c + 1 < nch) {
+      issue(c + 1, (c + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncwarp();
+    const float4 *xs = (const float4 *)(buf + (c & 1) * kExBuf + s * kExPiece);
+    const float4 *ws = (const float4 *)(buf + (c & 1) * kExBuf + (1 + g) * kExRow + s * kExPiece);
+#pragma unroll
+    for (int j = 0; j < (int)kExChunk / 4; j++) {
+      const float4 xv = xs[j], wv = ws[j];
+      p = fmaf(xv.x, wv.x, p);
+      p = fmaf(xv.y, wv.y, p);
+      p = fmaf(xv.z, wv.z, p);
+      p = fmaf(xv.w, wv.w, p);
+    }
+    __syncwarp();  // every lane has read the chunk before its buffer is filled again
+  }
+  float tot = __shfl_sync(0xffffffffu, p, lane & ~7u);
+#pragma unroll
+  for (int j = 1; j < (int)kRouterPieces; j++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, p, (lane & ~7u) + j));
+  if (bias) tot = __fadd_rn(tot, bias[e]);
+  return tot;
+}
+
 // The block's part: its rows' ids, weights and gates written, the chunk's count of every expert left in hist (shared,
 // 512 words) and, when s_ids is not null, the chunk's ids there too (shared, kChunkTokens * K words).
 //
@@ -283,8 +347,14 @@ __device__ __forceinline__ float exact_logits4(const float *__restrict__ x, cons
 // has every logit recomputed exactly instead.
 __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, const RouterApprox ap, const float *__restrict__ bias,
                                                   uint32_t T, uint32_t NE, uint32_t K, int32_t *__restrict__ ids, float *__restrict__ w,
-                                                  float *__restrict__ gs, uint32_t *hist, int32_t *s_ids) {
+                                                  float *__restrict__ gs, uint32_t *hist, int32_t *s_ids, uint8_t *ex_smem = nullptr) {
   // hist null: the caller counts the chunks' experts itself (k_chunk_hist), and the block may be of any number of warps.
+  // ex_smem: kExWarpBytes of shared memory for every warp of the block, through which the exact sums then take their
+  // operands (E a multiple of 8 * kExChunk); null: straight from global memory.
+  uint8_t *ex_buf = ex_smem ? ex_smem + (threadIdx.x / 32) * kExWarpBytes : nullptr;
+  auto exact4 = [&](const float *xr, uint32_t e, uint32_t ln) {
+    return ex_buf ? exact_logits4_staged(xr, ap.W, bias, ap.E, e, ln, ex_buf) : exact_logits4(xr, ap.W, bias, ap.E, e, ln);
+  };
   if (hist) {
     for (uint32_t i = threadIdx.x; i < NE; i += blockDim.x) hist[i] = 0;
     __syncthreads();
@@ -332,7 +402,7 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
         // Every logit exactly, four experts a pass: for rows the approximate ones cannot serve.
         mx = -INFINITY;
         for (uint32_t e0 = 0; e0 < NE; e0 += 4) {
-          const float v = exact_logits4(ap.x + (uint64_t)t * ap.E, ap.W, bias, ap.E, e0 + lane / 8, lane);
+          const float v = exact4(ap.x + (uint64_t)t * ap.E, e0 + lane / 8, lane);
 #pragma unroll
           for (int q = 0; q < 4; q++) {
             const float vq = __shfl_sync(0xffffffffu, v, 8 * q);
@@ -360,20 +430,20 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
       float vK = 0.0f;
       bool overflow = false;
       ncand = 0;
+      // A lane keeps the best of its own keys (the lower expert among equals); a round is then two warp reductions,
+      // the largest key and among its holders the lowest expert, and only the winner's lane has a new best to find.
+      uint32_t lkey = 0, lj = 0;
+      auto rescan = [&]() {
+        lkey = 0, lj = 0;
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; j++)
+          if ((uint32_t)j < per && key[j] > lkey) lkey = key[j], lj = j;
+      };
+      rescan();
       for (uint32_t k = 0; k < 32; k++) {
-        unsigned long long best = 0;
-#pragma unroll
-        for (int j = 0; j < kMaxPerLane; j++) {
-          const unsigned long long c = ((unsigned long long)key[j] << 32) | (uint32_t)~(lane + 32 * j);
-          if ((uint32_t)j < per && c > best) best = c;
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-          const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, off);
-          if (o > best) best = o;
-        }
-        const uint32_t e = ~(uint32_t)best, bkey = (uint32_t)(best >> 32);
+        const uint32_t bkey = __reduce_max_sync(0xffffffffu, lkey);
         if (bkey == 0) break;  // nothing left (fewer than 32 experts in all)
+        const uint32_t e = __reduce_min_sync(0xffffffffu, lkey == bkey ? lane + 32 * lj : 0xFFFFFFFFu);
         const float v = key_value(bkey);
         if (k == K - 1) vK = v;
         if (k >= K && !(eps2 > 0.0f && v >= vK - eps2)) break;
@@ -381,6 +451,7 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
 #pragma unroll
           for (int j = 0; j < kMaxPerLane; j++)
             if ((uint32_t)j == e / 32) key[j] = 0;
+          rescan();
         }
         if (lane == k) my_id = e, my_v = v;
         ncand = k + 1;
@@ -403,7 +474,7 @@ __device__ __forceinline__ void router_topk_block(const float *__restrict__ rl, 
         }
         const uint32_t g8 = lane / 8, mine = g8 == 0 ? c[0] : g8 == 1 ? c[1] : g8 == 2 ? c[2] : c[3];
         const uint32_t e = __shfl_sync(0xffffffffu, my_id, mine == 0xFFFFFFFFu ? 0 : mine);
-        const float v = exact_logits4(ap.x + (uint64_t)t * ap.E, ap.W, bias, ap.E, e, lane);
+        const float v = exact4(ap.x + (uint64_t)t * ap.E, e, lane);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
           const float vq = __shfl_sync(0xffffffffu, v, 8 * q);
@@ -455,7 +526,8 @@ constexpr uint32_t kTopkRowsPerCta = 4;
 static __global__ void __launch_bounds__(32 * kTopkRowsPerCta) k_router_topk_rows(const RouterApprox ap, const float *__restrict__ bias, uint32_t T,
                                                                                  uint32_t NE, uint32_t K, int32_t *__restrict__ ids,
                                                                                  float *__restrict__ w, float *__restrict__ gs) {
-  router_topk_block(nullptr, ap, bias, T, NE, K, ids, w, gs, nullptr, nullptr);
+  __shared__ __align__(16) uint8_t ex_smem[kTopkRowsPerCta * kExWarpBytes];
+  router_topk_block(nullptr, ap, bias, T, NE, K, ids, w, gs, nullptr, nullptr, ap.E % (kRouterPieces * kExChunk) == 0 ? ex_smem : nullptr);
 }
 
 static __global__ void __launch_bounds__(32 * kChunkTokens) k_router_topk(const float *__restrict__ rl, const RouterApprox ap,

@@ -90,7 +90,8 @@ class MoELayer:
         sl = slice(expert_first, expert_first + count)
         ge, ue, de = own_experts if own_experts is not None else (layer["gate_exps"][sl], layer["up_exps"][sl], layer["down_exps"][sl])
         if len(ge) != count or len(ue) != count or len(de) != count:
-            raise ValueError("the experts' arrays must hold expert_count experts")
+            # Refused here as the library refuses a bad shape: it would read past the arrays' ends.
+            raise MoEError(_lib.MOE_BAD_ARGUMENT, "the experts' arrays must hold expert_count experts")
         keep = [np.ascontiguousarray(layer["router"], dtype=np.float32),
                 np.ascontiguousarray(layer["shexp_gate_inp"], dtype=np.float32) if has_shared else None,
                 np.ascontiguousarray(layer["router_bias"], dtype=np.float32) if layer.get("router_bias") is not None else None,
