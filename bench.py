@@ -208,7 +208,8 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
     T = T_total if world == 1 or scaling == "weak" else max(1, T_total // world)
     base = build_layer(w)
     flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
-    x_host = torch.from_numpy(synth.make_input(T, E, seed=1 + rank)).pin_memory()
+    x_np = synth.make_input(T, E, seed=1 + rank)
+    x_host = torch.from_numpy(x_np).pin_memory()  # a page-locked copy
     out_host = torch.empty_like(x_host).pin_memory()
 
     # The layers of a stack share their experts' bytes on the host (each layer still has its own copy in HBM, so the
@@ -271,6 +272,9 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
         """The same from pinned host rows to pinned host rows."""
         if world == 1 and nlayers == 1:
             layers[0].forward(x_host.numpy(), out_host.numpy())  # the C ABI's host-buffer call
+            return
+        if world > 1 and nlayers == 1:
+            moes[0].forward_host(x_host, out_host, chunks=4 if T >= 8192 else 1)  # the expert-parallel layer's host-buffer call
             return
         with torch.cuda.stream(stream):
             x_dev.copy_(x_host, non_blocking=True)
@@ -385,7 +389,8 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
     # The order things are dropped in: every tensor first (and the allocator's cached blocks with them, while the
     # streams they were used on still exist), then the layers with their streams.
     torch.cuda.synchronize()
-    del x_dev, out_dev, res, xn, flush, tt
+    # (The page-locked rows too: freeing them records an event on every stream their copies ran on.)
+    del x_dev, out_dev, res, xn, flush, tt, x_host, out_host
     moes.clear()
     torch.cuda.empty_cache()
     for st in stages:
@@ -414,7 +419,7 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
     roof.update(kernel=dom, kernel_ms=dom_ms, peak_source=peaks["source"], traffic=traffic_for(w["name"], T, dom) if world == 1 else None)
     cpu_line = None
     if world == 1 and cpu and not args.no_cpu and nlayers == 1:
-        cpu_line, _ = cpu_leg(base, x_host.numpy(), min(T, args.cpu_tokens))
+        cpu_line, _ = cpu_leg(base, x_np, min(T, args.cpu_tokens))
     if world == 1:
         par = "1 GPU"
     else:

@@ -100,7 +100,7 @@ struct ActSource {
 
 // One pack: `rows` assignments sorted by expert over `nexp` experts.
 struct PackBuffers {
-  DeviceBuffer<uint32_t> chunk_hist, chunk_off, cnt, base, counters, inv, row_src;
+  DeviceBuffer<uint32_t> chunk_hist, chunk_off, group_off, cnt, base, counters, inv, row_src;
   DeviceBuffer<MoeTile> tiles;
   DeviceBuffer<MoeGroup> groups;
   DeviceBuffer<BigTile> big;
@@ -108,7 +108,7 @@ struct PackBuffers {
   void alloc(uint64_t max_rows, uint32_t n, uint32_t chunk_len) {
     nexp = n;
     const uint64_t nchunks = (max_rows + chunk_len - 1) / chunk_len + 1;
-    chunk_hist.alloc(nchunks * n), chunk_off.alloc(nchunks * n);
+    chunk_hist.alloc(nchunks * n), chunk_off.alloc(nchunks * n), group_off.alloc((nchunks / kScanGroup + 1) * n);
     cnt.alloc(n), base.alloc(n), counters.alloc(8), inv.alloc(max_rows), row_src.alloc(max_rows);
     tiles.alloc(max_rows / kTileRows + n), big.alloc(max_rows / kTileN + n);
     // As long as any grid over it: the integer-dot kernel reads its entry before it knows the list's length.
@@ -118,6 +118,7 @@ struct PackBuffers {
 };
 
 enum Stage { ST_QUANT, ST_ROUTER, ST_PACK, ST_GATE_UP, ST_DOWN, ST_SHARED, ST_COMBINE, ST_COPIES };
+
 constexpr uint32_t kRouterExactRows = 64;  // steps of up to this many rows take the exact fp32 router product
 constexpr uint32_t kLocalChunk = 512;  // entries per chunk when packing rows that came from other GPUs
 
@@ -200,6 +201,27 @@ namespace {
 void launched(moe_layer *l, cudaError_t e, const char *what) {
   cuda_check(e, what, __FILE__, __LINE__);
   l->stats.kernels++;
+}
+
+// From the chunks' counts (pk.chunk_hist) to the pack: the scan over chunks and experts, then every chunk's rows handed
+// out. Steps of more than two groups of chunks take the scan in two levels.
+struct PackJob {
+  const int32_t *ids;
+  uint32_t entries, chunk_len, nchunks, first_expert, tensor_min, tensor_budget, group_max, src_div;
+};
+void launch_pack(moe_layer *l, PackBuffers &pk, const PackJob &j, cudaStream_t st) {
+  const uint32_t ngroups = (j.nchunks + kScanGroup - 1) / kScanGroup;
+  uint32_t *groups = ngroups > 2 ? pk.group_off.get() : nullptr;
+  if (groups) {
+    k_pack_scan_groups<<<ngroups, 512, 0, st>>>(pk.chunk_hist.get(), j.nchunks, pk.nexp, pk.chunk_off.get(), groups);
+    launched(l, cudaGetLastError(), "pack scan of the groups");
+  }
+  k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), j.nchunks, pk.nexp, j.first_expert, j.tensor_min, j.tensor_budget, j.group_max, pk.out(), groups,
+                                 ngroups);
+  launched(l, cudaGetLastError(), "pack scan");
+  k_pack_fill<<<j.nchunks, 512, j.chunk_len * sizeof(int32_t), st>>>(j.ids, j.entries, j.chunk_len, pk.nexp, pk.base.get(), pk.chunk_off.get(), j.src_div,
+                                                                 pk.inv.get(), pk.row_src.get(), j.first_expert, groups);
+  launched(l, cudaGetLastError(), "pack fill");
 }
 
 void mark(moe_layer *l, int stage, cudaStream_t st) {
@@ -513,11 +535,7 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
       launched(l, cudaGetLastError(), "router top-k");
     }
     mark(l, ST_PACK, st);
-    k_pack_scan<<<1, 512, 0, st>>>(l->pack.chunk_hist.get(), nchunks, NE, 0, tm, budget, group_cap(A, NE), l->pack.out());
-    launched(l, cudaGetLastError(), "pack scan");
-    k_pack_fill<<<nchunks, 512, chunk_len * sizeof(int32_t), st>>>(l->ids.get(), (uint32_t)A, chunk_len, NE, l->pack.base.get(),
-                                                               l->pack.chunk_off.get(), K, l->pack.inv.get(), l->pack.row_src.get());
-    launched(l, cudaGetLastError(), "pack fill");
+    launch_pack(l, l->pack, PackJob{l->ids.get(), (uint32_t)A, chunk_len, nchunks, 0, tm, budget, group_cap(A, NE), K}, st);
   }
   l->last_T = T, l->last_pack = &l->pack;
 }
@@ -631,6 +649,8 @@ void stage_combine(moe_layer *l, const Y *y, uint32_t T, float *out, cudaStream_
   mark(l, ST_COPIES, st);
 }
 
+constexpr uint64_t kSharedInlineRows = 65536;  // expert rows from which the shared expert runs after the routed ones, not beside them
+
 // The whole block on device buffers, queued on st: a GPU that holds every expert.
 void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {
   if (l->local != l->NE) throw BadArgument("this call needs every expert on the GPU; an expert-parallel layer goes stage by stage");
@@ -638,7 +658,10 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   stage_route(l, x, T, st);
   // The shared expert needs only the quantised rows: it runs on a second stream beside the routed experts and joins
   // before the combine. With per-stage timing on, it runs in line instead, so that its stage can be timed.
-  const bool beside = l->has_shared && !l->profile;
+  // In long steps it runs in line after all: the routed kernels then fill the GPU for many rounds of items dealt to
+  // their CTAs beforehand, and CTAs that start late because the shared expert's hold their SMs finish late (a step of
+  // 32,768 rows measured 6 % slower with the two side by side than one after the other; 3,521 rows 5 % faster).
+  const bool beside = l->has_shared && !l->profile && A < kSharedInlineRows;
   if (beside) {
     l->fork_ev->record(st);
     CUDA_OK(cudaStreamWaitEvent(l->aux->get(), l->fork_ev->get(), 0));
@@ -935,11 +958,7 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
     const uint32_t nchunks = (R + kLocalChunk - 1) / kLocalChunk;
     k_chunk_hist<<<nchunks, 256, 0, st>>>(ids_dev, R, kLocalChunk, nexp, l->cfg.expert_first, pk.chunk_hist.get());
     launched(l, cudaGetLastError(), "local counts");
-    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, tensor_budget_for(l, R), group_cap(R, nexp), pk.out());
-    launched(l, cudaGetLastError(), "local pack scan");
-    k_pack_fill<<<nchunks, 512, kLocalChunk * sizeof(int32_t), st>>>(ids_dev, R, kLocalChunk, nexp, pk.base.get(), pk.chunk_off.get(), 1,
-                                                                 pk.inv.get(), pk.row_src.get(), l->cfg.expert_first);
-    launched(l, cudaGetLastError(), "local pack fill");
+    launch_pack(l, pk, PackJob{ids_dev, R, kLocalChunk, nchunks, l->cfg.expert_first, tm, tensor_budget_for(l, R), group_cap(R, nexp), 1}, st);
     const uint8_t *wire = (const uint8_t *)rows_dev;
     const uint32_t dbytes = q8k ? E / 64 : E / 8;
     ActSource src{ActView{(const int8_t *)wire, (const float *)(wire + E), (const int16_t *)(wire + E + dbytes), wb, wb, wb}, nullptr,
@@ -1033,11 +1052,8 @@ MOE_API moe_status moe_layer_experts_partial_device(moe_layer *l, const void *ro
     const uint32_t nchunks = (uint32_t)((entries + kLocalChunk - 1) / kLocalChunk);
     k_chunk_hist<<<nchunks, 256, 0, st>>>(l->ids_local.get(), (uint32_t)entries, kLocalChunk, nexp, l->cfg.expert_first, pk.chunk_hist.get());
     launched(l, cudaGetLastError(), "local counts");
-    k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), nchunks, nexp, l->cfg.expert_first, tm, tensor_budget_for(l, A), group_cap(A, nexp), pk.out());
-    launched(l, cudaGetLastError(), "local pack scan");
-    k_pack_fill<<<nchunks, 512, kLocalChunk * sizeof(int32_t), st>>>(l->ids_local.get(), (uint32_t)entries, kLocalChunk, nexp, pk.base.get(),
-                                                                 pk.chunk_off.get(), K, pk.inv.get(), pk.row_src.get(), l->cfg.expert_first);
-    launched(l, cudaGetLastError(), "local pack fill");
+    launch_pack(l, pk, PackJob{l->ids_local.get(), (uint32_t)entries, kLocalChunk, nchunks, l->cfg.expert_first, tm, tensor_budget_for(l, A),
+                               group_cap(A, nexp), K}, st);
     const uint32_t dbytes = q8k ? E / 64 : E / 8;
     ActSource src{ActView{(const int8_t *)wire, (const float *)(wire + E), (const int16_t *)(wire + E + dbytes), wb2, wb2, wb2}, nullptr,
                   pk.row_src.get()};

@@ -294,6 +294,43 @@ class ExpertParallelMoE:
         self.sent_rows, self.received_rows, self.expert_rows = sum(send) - send[self.rank], R - recv[self.rank], R
         return out
 
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 4) -> torch.Tensor:
+        """From page-locked host rows to page-locked host rows, the step cut into `chunks` steps of about equal rows
+        (the same number on every rank, none with more chunks than rows: each is a step of the whole group) so that a chunk's copy in and the copy out
+        of the one before run beside a chunk's computation and exchanges, each on a stream of its own. What
+        sent_rows, received_rows and expert_rows say afterwards is the sum over the chunks."""
+        st = self.st
+        T = x_host.shape[0]
+        if chunks < 1 or chunks > T:
+            raise ValueError("every rank needs at least one row in each of the chunks (the ranks take them in step)")
+        if not hasattr(self, "_copy_in"):
+            self._copy_in, self._copy_out = torch.cuda.Stream(device=st.device), torch.cuda.Stream(device=st.device)
+        x_dev = st.empty(tuple(x_host.shape), x_host.dtype, "host_x")
+        o_dev = st.empty(tuple(x_host.shape), torch.float32, "host_out")
+        bounds = [(T * c // chunks, T * (c + 1) // chunks) for c in range(chunks)]
+        self._copy_in.wait_stream(st.stream)       # the buffers' last readers and writers, a call ago
+        self._copy_out.wait_stream(st.stream)
+        arrived = []
+        with torch.cuda.stream(self._copy_in):
+            for a, b in bounds:
+                x_dev[a:b].copy_(x_host[a:b], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._copy_in)
+                arrived.append(ev)
+        totals = [0, 0, 0]
+        for (a, b), ev in zip(bounds, arrived):
+            st.stream.wait_event(ev)
+            self.forward(x_dev[a:b], o_dev[a:b])
+            done = torch.cuda.Event()
+            done.record(st.stream)
+            self._copy_out.wait_event(done)
+            with torch.cuda.stream(self._copy_out):
+                out_host[a:b].copy_(o_dev[a:b], non_blocking=True)
+            totals = [t + v for t, v in zip(totals, (self.sent_rows, self.received_rows, self.expert_rows))]
+        self._copy_out.synchronize()
+        self.sent_rows, self.received_rows, self.expert_rows = totals
+        return out_host
+
     def forward_by_token(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """One row per (token, GPU) out, one weighted partial sum per (token, GPU) back. Failures are handled as in
         forward(): what every rank can know is checked on every rank before a row moves; a stage's own failure is held until

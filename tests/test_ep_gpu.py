@@ -56,6 +56,14 @@ def _worker(rank, world, port, q):
             st.sync()
             got = out.cpu().numpy()
             res.append((t, "by_token", True, float(np.abs(got - ref).max() / np.abs(ref).max()), moe.sent_rows))
+            # The host-buffer call, the step cut into three whose copies run beside their neighbours: the same bits
+            # (every expert on the tile kernels, whose results for a row do not depend on the rows beside it).
+            if min(T) >= 3:
+                xh, oh = torch.from_numpy(x).pin_memory(), torch.empty((T[rank], 512), dtype=torch.float32).pin_memory()
+                for _ in range(2):
+                    moe.forward_host(xh, oh, chunks=3)
+                res.append((t, "host", bool(np.array_equal(oh.numpy(), got)), float(np.abs(oh.numpy() - ref).max() / np.abs(ref).max()), moe.sent_rows))
+                del xh, oh
             st.close()
         q.put((rank, res))
     finally:
@@ -70,6 +78,6 @@ def test_two_gpus_match_one():
     for rank, res in run_ranks(_worker, 2, timeout=600):
         for t, f16, same_bits, rel, sent in res:
             assert rel <= 1e-2, (rank, t, f16, rel)
-            if f16 is True:
-                assert same_bits, (rank, t)
+            if f16 is True or f16 == "host":
+                assert same_bits, (rank, t, f16)
             assert sent > 0
