@@ -273,6 +273,121 @@ struct Unit<QT_IQ3_S> {
   }
 };
 
+// A codebook word's four bytes made negative where the nibble's bits say so. A byte is in 1 .. 127, so (v ^ 0xFF) + 1 =
+// 256 - v stays within the byte and the four take one exclusive-or and one 32-bit add; the nibble's bits reach the
+// bytes' low bits by one multiply: bit i times 2^(7 i) lands on bit 8 i, and no two products share a bit.
+__device__ __forceinline__ int signed_word(uint32_t g, uint32_t nib) {
+  const uint32_t lsb = (nib * 0x00204081u) & 0x01010101u;
+  return (int)((g ^ (lsb * 0xFFu)) + lsb);
+}
+// 8 activation words of a sub-block against 8 decoded words.
+__device__ __forceinline__ int dot8(const int *g, const int4 &a0, const int4 &a1) {
+  int s = __dp4a(g[0], a0.x, 0);
+  s = __dp4a(g[1], a0.y, s), s = __dp4a(g[2], a0.z, s), s = __dp4a(g[3], a0.w, s);
+  s = __dp4a(g[4], a1.x, s), s = __dp4a(g[5], a1.y, s), s = __dp4a(g[6], a1.z, s), s = __dp4a(g[7], a1.w, s);
+  return s;
+}
+
+// IQ3_XXS: y = d * (0.5 + s) / 2 * grid[index][i] * sign: 8-bit indices into a 256-entry codebook, one per 4 values;
+// a sub-block of 32 has one word: four 7-bit sign indices (the eighth sign of each 8 values is the index's parity)
+// and the 4-bit s (QUANT_FORMATS.md:147-173). A unit is 16 bytes of indices: two sub-blocks.
+template <>
+struct Unit<QT_IQ3_XXS> {
+  static constexpr int kValues = 64;
+  struct Raw {
+    uint4 qs;
+    uint2 gas;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.qs = ldg_stream16(s + (uint64_t)r * (K / 4) + 16u * u);
+    const uint32_t c = u % 4;
+    const uint64_t blk = (uint64_t)r * (K / 256) + u / 4;
+    x.gas = __ldg((const uint2 *)(s + 64 * nblk + 32 * blk + 8 * c));
+    x.d = 0.25f * __half2float(__ldg((const __half *)(s + 96 * nblk) + blk));  // (2 s + 1) / 4 = (0.5 + s) / 2
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc,
+                                             uint32_t n, const uint32_t *grid) {
+    const uint32_t b = u / 4, c = u % 4;
+    int g[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const uint32_t word = i < 4 ? x.qs.x : i < 8 ? x.qs.y : i < 12 ? x.qs.z : x.qs.w;
+      const uint32_t w32 = i < 8 ? x.gas.x : x.gas.y;
+      const uint32_t k7 = (w32 >> (7 * ((i & 7) >> 1))) & 127u, sbyte = k7 | ((__popc(k7) & 1u) << 7);
+      g[i] = signed_word(grid[(word >> (8 * (i & 3))) & 0xFF], (sbyte >> (4 * (i & 1))) & 0xF);
+    }
+    const int sc0 = 2 * (int)(x.gas.x >> 28) + 1, sc1 = 2 * (int)(x.gas.y >> 28) + 1;
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
+      const uint8_t *a = acts + t * stride;
+      const int4 *av = (const int4 *)(a + 256 * b + 64 * c);
+      const uint32_t sw = (u >> 1) & 3;  // act_slot's swizzle
+      const int s0 = dot8(g, av[0 ^ sw], av[1 ^ sw]), s1 = dot8(g + 8, av[2 ^ sw], av[3 ^ sw]);
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[b], (float)(sc0 * s0 + sc1 * s1), acc[t]);
+    }
+  }
+};
+
+// IQ2_S: y = d * (0.5 + s) / 4 * grid[index][i] * sign: 10-bit indices into a 1024-entry codebook of 8 values (8 bits in
+// qs, 2 in qh), a byte of signs a group, a 4-bit s per 16 values (QUANT_FORMATS.md:115-145). A unit is 8 bytes of qs:
+// two sub-blocks of 32. The codebook in shared memory is two words an entry.
+template <>
+struct Unit<QT_IQ2_S> {
+  static constexpr int kValues = 64;
+  struct Raw {
+    uint2 qs, sg;
+    uint32_t qh, sc;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.qs = __ldg((const uint2 *)(s + (uint64_t)r * (K / 8) + 8u * u));
+    const uint32_t c = u % 4;
+    const uint64_t blk = (uint64_t)r * (K / 256) + u / 4;
+    x.sg = __ldg((const uint2 *)(s + 32 * nblk + 32 * blk + 8 * c));
+    x.qh = __ldg((const uint16_t *)(s + 64 * nblk + 8 * blk + 2 * c));
+    x.sc = __ldg((const uint16_t *)(s + 72 * nblk + 8 * blk + 2 * c));
+    x.d = 0.125f * __half2float(__ldg((const __half *)(s + 80 * nblk) + blk));  // (2 s + 1) / 8 = (0.5 + s) / 4
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc,
+                                             uint32_t n, const uint32_t *grid) {
+    const uint32_t b = u / 4, c = u % 4;
+    const uint2 *grid2 = (const uint2 *)grid;
+    int g[16];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {  // group j: sub-block j / 4, its group j % 4
+      const uint32_t lo8 = ((j < 4 ? x.qs.x : x.qs.y) >> (8 * (j & 3))) & 0xFF;
+      const uint32_t hi2 = ((x.qh >> (8 * (j >> 2))) >> (2 * (j & 3))) & 3u;
+      const uint32_t sb = ((j < 4 ? x.sg.x : x.sg.y) >> (8 * (j & 3))) & 0xFF;
+      const uint2 e = grid2[lo8 | (hi2 << 8)];
+      g[2 * j] = signed_word(e.x, sb & 0xF), g[2 * j + 1] = signed_word(e.y, sb >> 4);
+    }
+    // 2 s + 1 of the four 16-value halves.
+    const int k0 = 2 * (int)(x.sc & 0xF) + 1, k1 = 2 * (int)((x.sc >> 4) & 0xF) + 1, k2 = 2 * (int)((x.sc >> 8) & 0xF) + 1,
+              k3 = 2 * (int)((x.sc >> 12) & 0xF) + 1;
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
+      const uint8_t *a = acts + t * stride;
+      const int4 *av = (const int4 *)(a + 256 * b + 64 * c);
+      const uint32_t sw = (u >> 1) & 3;  // act_slot's swizzle
+      const int4 a0 = av[0 ^ sw], a1 = av[1 ^ sw], a2 = av[2 ^ sw], a3 = av[3 ^ sw];
+      int p0 = __dp4a(g[0], a0.x, 0), p1 = __dp4a(g[4], a1.x, 0), p2 = __dp4a(g[8], a2.x, 0), p3 = __dp4a(g[12], a3.x, 0);
+      p0 = __dp4a(g[1], a0.y, p0), p1 = __dp4a(g[5], a1.y, p1), p2 = __dp4a(g[9], a2.y, p2), p3 = __dp4a(g[13], a3.y, p3);
+      p0 = __dp4a(g[2], a0.z, p0), p1 = __dp4a(g[6], a1.z, p1), p2 = __dp4a(g[10], a2.z, p2), p3 = __dp4a(g[14], a3.z, p3);
+      p0 = __dp4a(g[3], a0.w, p0), p1 = __dp4a(g[7], a1.w, p1), p2 = __dp4a(g[11], a2.w, p2), p3 = __dp4a(g[15], a3.w, p3);
+      acc[t] = fmaf(x.d * ((const float *)(a + K))[b], (float)(k0 * p0 + k1 * p1 + k2 * p2 + k3 * p3), acc[t]);
+    }
+  }
+};
+
 // The 16-entry table of IQ4_NL and IQ4_XS as four words of four signed bytes, entries 4 i .. 4 i + 3 in word i.
 __host__ __device__ constexpr uint32_t iq4_table_word(int i) {
   return (uint32_t)(uint8_t)kIq4nlValues[4 * i] | (uint32_t)(uint8_t)kIq4nlValues[4 * i + 1] << 8 | (uint32_t)(uint8_t)kIq4nlValues[4 * i + 2] << 16 |
@@ -361,18 +476,18 @@ struct Unit<QT_IQ4_XS> {
 template <int QT, int M>
 __device__ __forceinline__ void unit_dot(const typename Unit<QT>::Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride,
                                          float *acc, uint32_t n, const uint32_t *grid) {
-  if constexpr (QT == QT_IQ3_S)
+  if constexpr (grid_words(QT) > 0)
     Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n, grid);
   else
     Unit<QT>::template dot<M>(x, K, u, acts, stride, acc, n);
 }
 
-// Where the 16-byte piece i of an activation row's codes sits in shared memory. IQ3_S's units read four pieces 64 bytes
+// Where the 16-byte piece i of an activation row's codes sits in shared memory. The codebook types' units read four pieces 64 bytes
 // apart from lane to lane, which without a swizzle puts a quarter-warp on two groups of four banks (four wavefronts an
 // access instead of one): piece (i & 3) of unit i / 4 is stored at (i & 3) ^ ((unit >> 1) & 3).
 template <int QT>
 __device__ __forceinline__ uint32_t act_slot(uint32_t i) {
-  if constexpr (QT == QT_IQ3_S) return (i & ~3u) | ((i & 3u) ^ ((i >> 3) & 3u));
+  if constexpr (grid_words(QT) > 0) return (i & ~3u) | ((i & 3u) ^ ((i >> 3) & 3u));
   return i;
 }
 
@@ -420,7 +535,7 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, li = lane % G, sub = lane / G;
   constexpr uint32_t RPP = 32 / G;  // weight rows a warp takes per pass
   constexpr int NU = UPL > 0 ? UPL : 1;
-  constexpr int RB = rows_batch(NMAT, NU, M, QT == QT_IQ3_S);  // passes whose loads go out together
+  constexpr int RB = rows_batch(NMAT, NU, M, grid_words(QT) > 0);  // passes whose loads go out together
   using Raw = typename Unit<QT>::Raw;
   const uint32_t rows_per_warp = UPL > 0 ? RPP * RB : a.rows_per_cta / 8;
   // A CTA takes `slabs` slabs of 8 * rows_per_warp weight rows one after another, so that what it does once (being
@@ -448,8 +563,8 @@ __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, con
   if constexpr (UPL > 0) fetch_slab(r_begin);
 
   uint32_t *grid = (uint32_t *)(smem + M * stride);
-  if constexpr (QT == QT_IQ3_S)
-    for (uint32_t i = threadIdx.x; i < 512; i += 256) grid[i] = grid_global[i];
+  if constexpr (grid_words(QT) > 0)
+    for (uint32_t i = threadIdx.x; i < grid_words(QT); i += 256) grid[i] = grid_global[grid_offset(QT) + i];
   // The group's activation rows into shared memory; rows past n get zero scales, so they add nothing.
   for (uint32_t t = 0; t < (uint32_t)M; t++) {
     uint8_t *dst = smem + t * stride;

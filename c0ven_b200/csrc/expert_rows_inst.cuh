@@ -13,15 +13,15 @@ static cudaError_t launch_one(ExpertRowsArgs a, uint32_t max_groups, const uint3
   // With the row length known at compile time a CTA's eight warps take one batch of passes each; else the caller's count.
   constexpr uint32_t rpp = 32 / G;
   if (UPL > 0)
-    a.rows_per_cta = 8 * rpp * rows_batch(NMAT, UPL, M, QT == QT_IQ3_S);
+    a.rows_per_cta = 8 * rpp * rows_batch(NMAT, UPL, M, grid_words(QT) > 0);
   else if (a.rows_per_cta < 8 * rpp)
     a.rows_per_cta = 8 * rpp;
-  const size_t smem = (size_t)M * act_row_stride(q8k, a.K) + (QT == QT_IQ3_S ? 2048 : 0);
+  const size_t smem = (size_t)M * act_row_stride(q8k, a.K) + 4 * grid_words(QT);
   auto kernel = k_expert_rows<QT, NMAT, M, G, UPL>;
   if (smem > 48 * 1024) {
     // The most a group's rows take, whatever this launch's row length: set once per device.
     static std::atomic<uint32_t> attr_done{0};
-    const size_t most = (size_t)M * act_row_stride(q8k, kRowsMaxK) + 2048;
+    const size_t most = (size_t)M * act_row_stride(q8k, kRowsMaxK) + 4 * grid_words(QT);
     if (smem > most) return cudaErrorInvalidValue;
     const cudaError_t e = ensure_dynamic_smem(kernel, most, attr_done, ctx.device);
     if (e != cudaSuccess) return e;

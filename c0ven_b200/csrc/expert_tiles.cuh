@@ -464,6 +464,94 @@ struct Decoder<QT_IQ3_S> {
   }
 };
 
+// Four codebook bytes (a word of values below 128) times sc as f16 with the nibble's signs, into o[0], o[1].
+__device__ __forceinline__ void grid_word_to_f16(uint32_t g, uint32_t nib, __half2 sc, uint32_t *o) {
+  const __half2 off = as_h2(0x64006400u);
+  // The sign bit of each f16: values 0, 1 from the nibble's bits 0, 1; 2, 3 from bits 2, 3.
+  const uint32_t s01 = ((nib & 1u) << 15) | ((nib & 2u) << 30), s23 = ((nib & 4u) << 13) | ((nib & 8u) << 28);
+  o[0] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(g, 0x4140)), off), sc)) ^ s01;
+  o[1] = as_u32(__hmul2(__hsub2(as_h2(bias_h2(g, 0x4342)), off), sc)) ^ s23;
+}
+
+// IQ3_XXS: w = d * (0.5 + s) / 2 * grid[index][i] * sign. A half is one sub-block of 32: 8 bytes of indices and its
+// word of four 7-bit sign indices and the scale. The codebook is in shared memory.
+template <>
+struct Decoder<QT_IQ3_XXS> {
+  static constexpr uint32_t kStageBytes = 16;  // bytes of a row's main quants run a 64-value stage reads
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
+  struct Raw {
+    uint2 qs;
+    uint32_t w32;
+    __half d;
+  };
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + 64 * ((uint64_t)r * (K / 256) + k0 / 256) + 8 * ((k0 % 256) / 32 + h);
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    const uint32_t sb = (k0 % 256) / 32 + h;  // the sub-block within its block
+    const uint64_t blk = (uint64_t)r * (K / 256) + k0 / 256;
+    Raw x;
+    x.qs = __ldg((const uint2 *)(s + 64 * blk + 8 * sb));
+    x.w32 = __ldg((const uint32_t *)(s + 64 * nblk + 32 * blk + 4 * sb));
+    x.d = __ldg((const __half *)(s + 96 * nblk) + blk);
+    return x;
+  }
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *grid) {
+    // d * (2 s + 1) / 4, rounded to f16 once.
+    const __half2 sc = __float2half2_rn(__half2float(x.d) * (float)(2 * (x.w32 >> 28) + 1) * 0.25f);
+    uint32_t o[16];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      const uint32_t word = k < 4 ? x.qs.x : x.qs.y;
+      const uint32_t k7 = (x.w32 >> (7 * (k >> 1))) & 127u, sbyte = k7 | ((__popc(k7) & 1u) << 7);
+      grid_word_to_f16(grid[(word >> (8 * (k & 3))) & 0xFF], (sbyte >> (4 * (k & 1))) & 0xF, sc, o + 2 * k);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
+  }
+};
+
+// IQ2_S: w = d * (0.5 + s) / 4 * grid[index][i] * sign. A half is one sub-block of 32: four groups of 8 values, each a
+// 10-bit index (a byte of qs, two bits of the sub-block's qh byte) and a byte of signs; a scale nibble per two groups.
+template <>
+struct Decoder<QT_IQ2_S> {
+  static constexpr uint32_t kStageBytes = 8;  // bytes of a row's main quants run a 64-value stage reads
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
+  struct Raw {
+    uint32_t qs, sg, qh, sc;
+    __half d;
+  };
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + 32 * ((uint64_t)r * (K / 256) + k0 / 256) + 4 * ((k0 % 256) / 32 + h);
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    const uint32_t sb = (k0 % 256) / 32 + h;
+    const uint64_t blk = (uint64_t)r * (K / 256) + k0 / 256;
+    Raw x;
+    x.qs = __ldg((const uint32_t *)(s + 32 * blk + 4 * sb));
+    x.sg = __ldg((const uint32_t *)(s + 32 * nblk + 32 * blk + 4 * sb));
+    x.qh = __ldg(s + 64 * nblk + 8 * blk + sb);
+    x.sc = __ldg(s + 72 * nblk + 8 * blk + sb);
+    x.d = __ldg((const __half *)(s + 80 * nblk) + blk);
+    return x;
+  }
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *grid) {
+    const float d8 = __half2float(x.d) * 0.125f;  // d * (2 s + 1) / 8
+    const __half2 sc_lo = __float2half2_rn(d8 * (float)(2 * (x.sc & 0xF) + 1)), sc_hi = __float2half2_rn(d8 * (float)(2 * (x.sc >> 4) + 1));
+    const uint2 *grid2 = (const uint2 *)grid;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      const uint2 e = grid2[((x.qs >> (8 * g)) & 0xFF) | (((x.qh >> (2 * g)) & 3u) << 8)];
+      const uint32_t sb = (x.sg >> (8 * g)) & 0xFF;
+      uint32_t o[4];
+      grid_word_to_f16(e.x, sb & 0xF, g < 2 ? sc_lo : sc_hi, o), grid_word_to_f16(e.y, sb >> 4, g < 2 ? sc_lo : sc_hi, o + 2);
+      store_chunk(tile, m, 4 * h + g, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  }
+};
+
 // Sixteen table values (four words of signed bytes) times d2 as f16, into o[0 .. 7].
 __device__ __forceinline__ void int8x16_to_f16(const uint32_t (&w)[4], __half2 d2, uint32_t *o) {
   const __half2 off = as_h2(0x64806480u);  // 1152 = 1024 + 128
@@ -548,7 +636,7 @@ struct Decoder<QT_IQ4_XS> {
 __host__ __device__ constexpr bool quants_by_copy(uint32_t qt) { return qt == QT_Q4_K; }
 
 // Shared memory of a CTA: the stages (NMAT weight tiles of 16 KB and a row tile of 32 KB each), then (for types whose
-// quants come by copy) a ring of two quant slots, then the barriers, then IQ3_S's codebook.
+// quants come by copy) a ring of two quant slots, then the barriers, then a codebook type's codebook.
 // A quant slot holds, for every weight row of the item, the quants of one stage per decode group: 32 bytes a stage for
 // Q4_K, so 64 bytes a row with two groups (64-byte swizzle) and 128 with four (128-byte swizzle).
 template <int QT, int NMAT, bool PAIR = false>
@@ -565,8 +653,8 @@ struct TileSmem {
   static constexpr uint32_t kBarriers = kQuants + (quants_by_copy(QT) ? kQSlots * kQSlotBytes : 0);
   // full[kStages], empty[kStages], accumulators full[2], empty[2], empty after a two-buffer item, quant slots full[2],
   // empty[2]; tmem address; abort
-  static constexpr uint32_t kGrid = kBarriers + 256;                                  // IQ3_S's codebook, 2 KB
-  static constexpr uint32_t kBytes = kGrid + (QT == QT_IQ3_S ? 2048 : 0) + 1024;      // and room to align the base to 1024
+  static constexpr uint32_t kGrid = kBarriers + 256;                                  // the codebook: 1, 2 or 8 KB
+  static constexpr uint32_t kBytes = kGrid + 4 * grid_words(QT) + 1024;               // and room to align the base to 1024
   static_assert(kBytes <= 227 * 1024, "a CTA's shared memory");
 };
 
@@ -663,8 +751,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
     *abort = 0;
     fence_barrier_init();
   }
-  if constexpr (QT == QT_IQ3_S)
-    for (uint32_t i = tid; i < 512; i += blockDim.x) grid[i] = grid_global[i];
+  if constexpr (grid_words(QT) > 0)
+    for (uint32_t i = tid; i < grid_words(QT); i += blockDim.x) grid[i] = grid_global[grid_offset(QT) + i];
   if (warp == kMmaWarp) {
     if constexpr (PAIR)
       tmem_alloc_pair(smem_u32(tmem_slot), kCols);  // the same warp of both CTAs, the same place for the address

@@ -42,6 +42,8 @@ static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, i
     ROWS_CASE(QT_IQ3_S)
     ROWS_CASE(QT_IQ4_NL)
     ROWS_CASE(QT_IQ4_XS)
+    ROWS_CASE(QT_IQ3_XXS)
+    ROWS_CASE(QT_IQ2_S)
     default: return cudaErrorInvalidValue;
   }
 #undef ROWS_CASE
@@ -59,6 +61,8 @@ static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a,
     TILES_CASE(QT_IQ3_S)
     TILES_CASE(QT_IQ4_NL)
     TILES_CASE(QT_IQ4_XS)
+    TILES_CASE(QT_IQ3_XXS)
+    TILES_CASE(QT_IQ2_S)
     default: return cudaErrorInvalidValue;
   }
 #undef TILES_CASE
@@ -243,7 +247,7 @@ void check_config(const moe_layer_config &c, const moe_layer_weights &w) {
   if (c.n_ff == 0 || c.n_ff % 256 || c.n_ff > kRowsMaxK) bad("n_ff must be a multiple of 256, at most 16384");
   if (c.n_experts == 0 || c.n_experts % 32 || c.n_experts > 512) bad("n_experts must be a multiple of 32, at most 512");
   if (c.n_used == 0 || c.n_used > 16 || c.n_used > c.n_experts) bad("n_used must be 1 .. 16 and at most n_experts");
-  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K, IQ3_S, IQ4_NL or IQ4_XS");
+  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K, IQ3_S, IQ4_NL, IQ4_XS, IQ3_XXS or IQ2_S");
   if (c.shexp_gate_type && (!type_known(c.shexp_gate_type) || !type_known(c.shexp_down_type)))
     bad("the shared expert's types must be Q8_0, Q4_K, Q6_K or IQ3_S");
   if (c.expert_first + (c.expert_count ? c.expert_count : c.n_experts - c.expert_first) > c.n_experts)
@@ -304,8 +308,13 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
     l->bias.alloc(NE);
     CUDA_OK(cudaMemcpyAsync(l->bias.get(), w.router_bias, NE * sizeof(float), cudaMemcpyHostToDevice, st));
   }
-  l->grid.alloc(512);
-  CUDA_OK(cudaMemcpyAsync(l->grid.get(), kIq3sGrid, sizeof(kIq3sGrid), cudaMemcpyHostToDevice, st));
+  // The codebooks, one after another (formats.h: grid_offset).
+  l->grid.alloc(kGridWordsAll);
+  static_assert(sizeof(kIq3sGrid) == 4 * grid_words(QT_IQ3_S) && sizeof(kIq3xxsGrid) == 4 * grid_words(QT_IQ3_XXS) && sizeof(kIq2sGrid) == 4 * grid_words(QT_IQ2_S),
+                "the generated tables' sizes");
+  CUDA_OK(cudaMemcpyAsync(l->grid.get() + grid_offset(QT_IQ3_S), kIq3sGrid, sizeof(kIq3sGrid), cudaMemcpyHostToDevice, st));
+  CUDA_OK(cudaMemcpyAsync(l->grid.get() + grid_offset(QT_IQ3_XXS), kIq3xxsGrid, sizeof(kIq3xxsGrid), cudaMemcpyHostToDevice, st));
+  CUDA_OK(cudaMemcpyAsync(l->grid.get() + grid_offset(QT_IQ2_S), kIq2sGrid, sizeof(kIq2sGrid), cudaMemcpyHostToDevice, st));
   CUDA_OK(cudaStreamSynchronize(st));
 
   const uint64_t gblk = (uint64_t)F * (E / block_values(c.gate_type)), dblk = (uint64_t)E * (F / block_values(c.down_type));

@@ -50,7 +50,7 @@ void orc_set_threads(int n) {
 uint32_t orc_block_values(uint32_t t) {
   switch (t) {
     case ORC_Q8_0: case ORC_IQ4_NL: return 32;
-    case ORC_Q4_K: case ORC_Q6_K: case ORC_Q8_K: case ORC_IQ3_S: case ORC_IQ4_XS: return 256;
+    case ORC_Q4_K: case ORC_Q6_K: case ORC_Q8_K: case ORC_IQ3_S: case ORC_IQ4_XS: case ORC_IQ3_XXS: case ORC_IQ2_S: return 256;
     default: return 0;
   }
 }
@@ -63,6 +63,8 @@ uint32_t orc_block_bytes(uint32_t t) {
     case ORC_IQ3_S: return 110;
     case ORC_IQ4_NL: return 18;
     case ORC_IQ4_XS: return 136;
+    case ORC_IQ3_XXS: return 98;
+    case ORC_IQ2_S: return 82;
     default: return 0;
   }
 }
@@ -80,6 +82,9 @@ static uint32_t fields(uint32_t t, uint32_t off[5], uint32_t sz[5]) {
       return 5;
     case ORC_IQ4_NL: off[0] = 2, sz[0] = 16, off[1] = 0, sz[1] = 2; return 2;
     case ORC_IQ4_XS: off[0] = 8, sz[0] = 128, off[1] = 4, sz[1] = 4, off[2] = 2, sz[2] = 2, off[3] = 0, sz[3] = 2; return 4;
+    /* grid indices, scale-and-sign words, d; and grid index low bits, signs, qh, scales, d (QUANT_FORMATS.md:602-603) */
+    case ORC_IQ3_XXS: off[0] = 2, sz[0] = 64, off[1] = 66, sz[1] = 32, off[2] = 0, sz[2] = 2; return 3;
+    case ORC_IQ2_S: off[0] = 2, sz[0] = 32, off[1] = 34, sz[1] = 32, off[2] = 66, sz[2] = 8, off[3] = 74, sz[3] = 8, off[4] = 0, sz[4] = 2; return 5;
     default: return 0;
   }
 }
@@ -101,6 +106,14 @@ void orc_from_runs(uint32_t t, const uint8_t *src, uint64_t n, uint8_t *dst) {
     for (uint64_t k = 0; k < n; k++) memcpy(dst + k * bb + off[f], src + run + k * sz[f], sz[f]);
     run += (uint64_t)sz[f] * n;
   }
+}
+
+/* ksigns_iq2xs[k]: k with bit 7 set when k has an odd number of set bits, so that every sign byte has even parity
+ * (QUANT_FORMATS.md:167-168; the table's sha256, :548, is checked against this rule in the tests). */
+static inline uint8_t ksigns(uint32_t k) {
+  uint32_t p = k ^ (k >> 4);
+  p ^= p >> 2, p ^= p >> 1;
+  return (uint8_t)(k | ((p & 1u) << 7));
 }
 
 /* Q4_K's packed 6-bit scale and minimum of sub-block j (QUANT_FORMATS.md:386-392). */
@@ -190,6 +203,40 @@ void orc_dequantize_row(uint32_t t, const void *vb, float *y, int64_t n) {
         for (int j = 0; j < 16; j++) {
           y[i * QK_K + 32 * ib + j] = dl * (float)kIq4nlValues[qs[16 * ib + j] & 0xF];
           y[i * QK_K + 32 * ib + 16 + j] = dl * (float)kIq4nlValues[qs[16 * ib + j] >> 4];
+        }
+      }
+    } else if (t == ORC_IQ3_XXS) {
+      /* y = d * (0.5 + s) / 2 * grid byte * sign; sub-block sb's word holds four 7-bit sign indices, each completed to
+       * 8 signs by parity, and the scale s in bits 28-31 (QUANT_FORMATS.md:147-168). */
+      const float d = h2f(rd16(b));
+      const uint8_t *qs = b + 2, *gas = b + 66;
+      for (int sb = 0; sb < 8; sb++) {
+        uint32_t w32;
+        memcpy(&w32, gas + 4 * sb, 4);
+        const float db = d * (0.5f + (float)(w32 >> 28)) * 0.5f;
+        for (int l = 0; l < 4; l++) {
+          const uint8_t signs = ksigns((w32 >> (7 * l)) & 127);
+          for (int k = 0; k < 2; k++) {
+            const uint32_t g = kIq3xxsGrid[qs[8 * sb + 2 * l + k]];
+            for (int v = 0; v < 4; v++)
+              y[i * QK_K + 32 * sb + 8 * l + 4 * k + v] = db * (float)((g >> (8 * v)) & 0xFF) * (((signs >> (4 * k + v)) & 1) ? -1.0f : 1.0f);
+          }
+        }
+      }
+    } else if (t == ORC_IQ2_S) {
+      /* y = d * (0.5 + s) / 4 * grid byte * sign: groups of 8 values from a 10-bit index (qs and two bits of qh), a
+       * byte of signs a group, a scale nibble per 16 values (QUANT_FORMATS.md:115-137). */
+      const float d = h2f(rd16(b));
+      const uint8_t *qs = b + 2, *sg = b + 34, *qh = b + 66, *sc = b + 74;
+      for (int sb = 0; sb < 8; sb++) {
+        for (int g = 0; g < 4; g++) {
+          const float db = d * (0.5f + (float)((sc[sb] >> (4 * (g / 2))) & 0xF)) * 0.25f;
+          const uint32_t idx = qs[4 * sb + g] | ((((uint32_t)qh[sb] >> (2 * g)) & 3u) << 8);
+          const uint8_t signs = sg[4 * sb + g];
+          for (int v = 0; v < 8; v++) {
+            const uint32_t word = kIq2sGrid[2 * idx + v / 4];
+            y[i * QK_K + 32 * sb + 8 * g + v] = db * (float)((word >> (8 * (v % 4))) & 0xFF) * (((signs >> v) & 1) ? -1.0f : 1.0f);
+          }
         }
       }
     }
@@ -346,6 +393,66 @@ static float dot_iq3_s(int64_t n, const uint8_t *w, const uint8_t *a) {
   return (r0 + r2) + (r1 + r3);
 }
 
+/* core/cpu/multirow.cpp:128-177 in scalar form, the same lanes and order as dot_iq3_s: lane L takes values 4L .. 4L+3 of
+ * every sub-block of 32 times the sub-block's 2 s + 1; the quarter comes last. */
+static float dot_iq3_xxs(int64_t n, const uint8_t *w, const uint8_t *a) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int64_t i = 0; i < n / QK_K; i++, w += 98, a += 292) {
+    const uint8_t *qs = w + 2, *gas = w + 66;
+    const int8_t *p = (const int8_t *)(a + 4);
+    int32_t lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int sb = 0; sb < 8; sb++) {
+      uint32_t w32;
+      memcpy(&w32, gas + 4 * sb, 4);
+      const int sc = 2 * (int)(w32 >> 28) + 1;
+      for (int k = 0; k < 8; k++) {
+        const uint32_t g = kIq3xxsGrid[qs[8 * sb + k]];
+        const uint8_t sg = ksigns((w32 >> (7 * (k / 2))) & 127) >> (4 * (k % 2));
+        int s = 0;
+        for (int v = 0; v < 4; v++) {
+          const int q = p[32 * sb + 4 * k + v];
+          s += (int)((g >> (8 * v)) & 0xFF) * (((sg >> v) & 1) ? -q : q);
+        }
+        lane[k] += sc * s;
+      }
+    }
+    const float d = h2f(rd16(w)) * rdf(a);
+    for (int L = 0; L < 8; L++) acc[L] = fmaf(d, (float)lane[L], acc[L]);
+  }
+  const float r0 = acc[4] + acc[0], r1 = acc[5] + acc[1], r2 = acc[6] + acc[2], r3 = acc[7] + acc[3];
+  return 0.25f * ((r0 + r2) + (r1 + r3));
+}
+
+/* core/cpu/multirow.cpp:65-125 in scalar form: lane L takes values 4L .. 4L+3 of every sub-block times 2 s + 1 of the
+ * half (values 0-15 or 16-31) they are in; the eighth comes last. */
+static float dot_iq2_s(int64_t n, const uint8_t *w, const uint8_t *a) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int64_t i = 0; i < n / QK_K; i++, w += 82, a += 292) {
+    const uint8_t *qs = w + 2, *sg = w + 34, *qh = w + 66, *scl = w + 74;
+    const int8_t *p = (const int8_t *)(a + 4);
+    int32_t lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int sb = 0; sb < 8; sb++) {
+      for (int k = 0; k < 8; k++) { /* values 4k .. 4k+3: half k % 2 of group k / 2 */
+        const int g = k / 2;
+        const int sc = 2 * (int)((scl[sb] >> (4 * (g / 2))) & 0xF) + 1;
+        const uint32_t idx = qs[4 * sb + g] | ((((uint32_t)qh[sb] >> (2 * g)) & 3u) << 8);
+        const uint32_t word = kIq2sGrid[2 * idx + k % 2];
+        const uint8_t bits = sg[4 * sb + g] >> (4 * (k % 2));
+        int s = 0;
+        for (int v = 0; v < 4; v++) {
+          const int q = p[32 * sb + 4 * k + v];
+          s += (int)((word >> (8 * v)) & 0xFF) * (((bits >> v) & 1) ? -q : q);
+        }
+        lane[k] += sc * s;
+      }
+    }
+    const float d = h2f(rd16(w)) * rdf(a);
+    for (int L = 0; L < 8; L++) acc[L] = fmaf(d, (float)lane[L], acc[L]);
+  }
+  const float r0 = acc[4] + acc[0], r1 = acc[5] + acc[1], r2 = acc[6] + acc[2], r3 = acc[7] + acc[3];
+  return 0.125f * ((r0 + r2) + (r1 + r3));
+}
+
 /* IQ4_NL against q8_0: per block the integer sum of table values times codes, times d_w * d_a (QUANT_FORMATS.md:246-247). */
 static float dot_iq4_nl(int64_t n, const uint8_t *w, const uint8_t *a) {
   float sumf = 0.0f;
@@ -386,6 +493,8 @@ float orc_vec_dot(uint32_t t, int64_t n, const void *w, const void *a) {
     case ORC_IQ3_S: return dot_iq3_s(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_IQ4_NL: return dot_iq4_nl(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_IQ4_XS: return dot_iq4_xs(n, (const uint8_t *)w, (const uint8_t *)a);
+    case ORC_IQ3_XXS: return dot_iq3_xxs(n, (const uint8_t *)w, (const uint8_t *)a);
+    case ORC_IQ2_S: return dot_iq2_s(n, (const uint8_t *)w, (const uint8_t *)a);
     default: return NAN;
   }
 }

@@ -30,7 +30,9 @@ extern "C" {
 #define ORC_Q6_K 14
 #define ORC_Q8_K 15
 #define ORC_IQ4_NL 20
+#define ORC_IQ3_XXS 18
 #define ORC_IQ3_S 21
+#define ORC_IQ2_S 22
 #define ORC_IQ4_XS 23
 
 uint32_t orc_block_values(uint32_t type);

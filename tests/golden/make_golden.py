@@ -16,7 +16,7 @@ from c0ven_b200 import synth  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CLASSES = {synth.Q8_0: quants.Q8_0, synth.Q4_K: quants.Q4_K, synth.Q6_K: quants.Q6_K, synth.IQ3_S: quants.IQ3_S,
-           synth.IQ4_NL: quants.IQ4_NL, synth.IQ4_XS: quants.IQ4_XS}
+           synth.IQ4_NL: quants.IQ4_NL, synth.IQ4_XS: quants.IQ4_XS, synth.IQ3_XXS: quants.IQ3_XXS, synth.IQ2_S: quants.IQ2_S}
 
 
 def main():
@@ -36,6 +36,8 @@ def main():
         else:
             blocks[:2, 0:2] = keep[:, 0:2]
         out[f"blocks_{t}"] = blocks
+        if hasattr(cls, "init_grid"):
+            cls.init_grid()
         out[f"values_{t}"] = cls.dequantize_blocks(blocks).astype(np.float32).reshape(-1)
     x = (rng.standard_normal(32 * 40) * np.repeat(rng.uniform(0.01, 30, 40), 32)).astype(np.float32)
     x[:32] = 0.0  # a block of zeros: d = 0

@@ -7,7 +7,7 @@ import pytest
 from c0ven_b200 import synth
 from oracle import oracle as O
 
-TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS]
+TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S]
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -86,7 +86,7 @@ def test_runs_layout_is_a_permutation(t):
     assert np.array_equal(O.from_runs(t, runs).reshape(blocks.shape), blocks)
     # The first run holds every block's quants, block k's at k * size (shared/quant.h:172-176).
     qoff, qsz = {synth.Q8_0: (2, 32), synth.Q4_K: (16, 128), synth.Q6_K: (0, 128), synth.IQ3_S: (2, 64),
-                 synth.IQ4_NL: (2, 16), synth.IQ4_XS: (8, 128)}[t]
+                 synth.IQ4_NL: (2, 16), synth.IQ4_XS: (8, 128), synth.IQ3_XXS: (2, 64), synth.IQ2_S: (2, 32)}[t]
     assert np.array_equal(runs.reshape(-1)[:n * qsz].reshape(n, qsz), blocks[:, qoff:qoff + qsz])
 
 
