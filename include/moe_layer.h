@@ -38,8 +38,10 @@ typedef enum {
 #define MOE_TYPE_Q8_0 8
 #define MOE_TYPE_Q4_K 12
 #define MOE_TYPE_Q6_K 14
+#define MOE_TYPE_IQ3_XXS 18
 #define MOE_TYPE_IQ4_NL 20
 #define MOE_TYPE_IQ3_S 21
+#define MOE_TYPE_IQ2_S 22
 #define MOE_TYPE_IQ4_XS 23
 
 typedef struct moe_layer moe_layer;
