@@ -406,6 +406,49 @@ __device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t &lo, uint32_t &
   lo = __byte_perm(r0, r1, 0x6420u), hi = __byte_perm(r0, r1, 0x7531u);
 }
 
+// Sixteen 2-bit codes (a word's low or high half: 4 bytes of 4 codes) as 16 signed bytes q - 1 in four words. A byte's
+// four codes are spread to the digits of a permute selector, whose table is the bytes -1, 0, 1, 2.
+__device__ __forceinline__ uint32_t q2_bytes(uint32_t c) {  // c: one byte, four codes
+  const uint32_t sel = (c & 0x3u) | ((c & 0xCu) << 2) | ((c & 0x30u) << 4) | ((c & 0xC0u) << 6);
+  return __byte_perm(0x020100FFu, 0u, sel);
+}
+
+// Q2_0: y = (q - 1) * d, 64 values in 16 bytes with an f16 scale, value j in bits 2 (j mod 4) of byte j / 4
+// (QUANT_FORMATS.md:251-270). A unit is one block; it meets two q8_0 blocks of activations, each with its own scale.
+template <>
+struct Unit<QT_Q2_0> {
+  static constexpr int kValues = 64;
+  struct Raw {
+    uint4 q;
+    float d;
+  };
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t u, const uint32_t *) {
+    Raw x;
+    x.q = ldg_stream16(s + (uint64_t)r * (K / 4) + 16u * u);
+    x.d = __half2float(__ldg((const __half *)(s + 16 * nblk) + (uint64_t)r * (K / 64) + u));
+    return x;
+  }
+  template <int M>
+  __device__ static __forceinline__ void dot(const Raw &x, uint32_t K, uint32_t u, const uint8_t *acts, uint32_t stride, float *acc, uint32_t n) {
+    int g[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const uint32_t word = i < 4 ? x.q.x : i < 8 ? x.q.y : i < 12 ? x.q.z : x.q.w;
+      g[i] = (int)q2_bytes((word >> (8 * (i & 3))) & 0xFF);
+    }
+#pragma unroll
+    for (int t = 0; t < M; t++) {
+      if ((uint32_t)t >= n) break;  // the group's rows: the same for the whole CTA
+      const uint8_t *a = acts + t * stride;
+      const int4 *av = (const int4 *)(a + 64u * u);
+      const int s0 = dot8(g, av[0], av[1]), s1 = dot8(g + 8, av[2], av[3]);
+      const float *da = (const float *)(a + K) + 2 * u;
+      acc[t] = fmaf(x.d * da[0], (float)s0, acc[t]);
+      acc[t] = fmaf(x.d * da[1], (float)s1, acc[t]);
+    }
+  }
+};
+
 // IQ4_NL: y = d * table[q], blocks of 32 with an f16 scale; a block's 16 bytes hold values 0 .. 15 in their low nibbles
 // and 16 .. 31 in their high ones (QUANT_FORMATS.md:236-247). A unit is one block. Activations are q8_0.
 template <>

@@ -572,6 +572,36 @@ __device__ __forceinline__ void iq4_store32(const uint4 &q, __half2 d2, uint8_t 
   for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
 }
 
+// Q2_0: w = (q - 1) * d. A stage is one block of 64; a half is 8 of its 16 bytes.
+template <>
+struct Decoder<QT_Q2_0> {
+  static constexpr uint32_t kStageBytes = 16;  // bytes of a row's main quants run a 64-value stage reads
+  struct Hdr {};
+  __device__ static __forceinline__ Hdr fetch_hdr(const uint8_t *, uint64_t, uint32_t, uint32_t, uint32_t) { return Hdr{}; }
+  struct Raw {
+    uint2 q;
+    __half d;
+  };
+  __device__ static __forceinline__ const uint8_t *quants_at(const uint8_t *s, uint64_t, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    return s + (uint64_t)r * (K / 4) + k0 / 4 + 8 * h;
+  }
+  __device__ static __forceinline__ Raw fetch(const uint8_t *s, uint64_t nblk, uint32_t K, uint32_t r, uint32_t k0, uint32_t h) {
+    Raw x;
+    x.q = __ldg((const uint2 *)quants_at(s, nblk, K, r, k0, h));
+    x.d = __ldg((const __half *)(s + 16 * nblk) + (uint64_t)r * (K / 64) + k0 / 64);
+    return x;
+  }
+  __device__ static __forceinline__ void store(const Hdr &, const Raw &x, uint8_t *tile, uint32_t m, uint32_t h, uint32_t, const uint32_t *) {
+    uint32_t w[8], o[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = q2_bytes(((i < 4 ? x.q.x : x.q.y) >> (8 * (i & 3))) & 0xFF);
+    const __half2 d2 = __half2half2(x.d);
+    int8x16_to_f16(*(const uint32_t(*)[4])&w[0], d2, o), int8x16_to_f16(*(const uint32_t(*)[4])&w[4], d2, o + 8);
+#pragma unroll
+    for (int c = 0; c < 4; c++) store_chunk(tile, m, 4 * h + c, make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]));
+  }
+};
+
 // IQ4_NL: w = d * table[q]. A half is one block of 32.
 template <>
 struct Decoder<QT_IQ4_NL> {

@@ -44,6 +44,7 @@ static cudaError_t launch_rows(uint32_t qt, int nmat, const ExpertRowsArgs &a, i
     ROWS_CASE(QT_IQ4_XS)
     ROWS_CASE(QT_IQ3_XXS)
     ROWS_CASE(QT_IQ2_S)
+    ROWS_CASE(QT_Q2_0)
     default: return cudaErrorInvalidValue;
   }
 #undef ROWS_CASE
@@ -63,6 +64,7 @@ static cudaError_t launch_tiles(uint32_t qt, int nmat, const ExpertTilesArgs &a,
     TILES_CASE(QT_IQ4_XS)
     TILES_CASE(QT_IQ3_XXS)
     TILES_CASE(QT_IQ2_S)
+    TILES_CASE(QT_Q2_0)
     default: return cudaErrorInvalidValue;
   }
 #undef TILES_CASE
@@ -247,7 +249,7 @@ void check_config(const moe_layer_config &c, const moe_layer_weights &w) {
   if (c.n_ff == 0 || c.n_ff % 256 || c.n_ff > kRowsMaxK) bad("n_ff must be a multiple of 256, at most 16384");
   if (c.n_experts == 0 || c.n_experts % 32 || c.n_experts > 512) bad("n_experts must be a multiple of 32, at most 512");
   if (c.n_used == 0 || c.n_used > 16 || c.n_used > c.n_experts) bad("n_used must be 1 .. 16 and at most n_experts");
-  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K, IQ3_S, IQ4_NL, IQ4_XS, IQ3_XXS or IQ2_S");
+  if (!type_known(c.gate_type) || !type_known(c.down_type)) bad("the experts' types must be Q8_0, Q4_K, Q6_K, IQ3_S, IQ4_NL, IQ4_XS, IQ3_XXS, IQ2_S or Q2_0");
   if (c.shexp_gate_type && (!type_known(c.shexp_gate_type) || !type_known(c.shexp_down_type)))
     bad("the shared expert's types must be Q8_0, Q4_K, Q6_K or IQ3_S");
   if (c.expert_first + (c.expert_count ? c.expert_count : c.n_experts - c.expert_first) > c.n_experts)

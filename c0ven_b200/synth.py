@@ -10,10 +10,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_K, Q6_K, IQ3_XXS, IQ4_NL, IQ3_S, IQ2_S, IQ4_XS = 8, 12, 14, 18, 20, 21, 22, 23
-BLOCK_VALUES = {Q8_0: 32, Q4_K: 256, Q6_K: 256, IQ3_S: 256, IQ4_NL: 32, IQ4_XS: 256, IQ3_XXS: 256, IQ2_S: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210, IQ3_S: 110, IQ4_NL: 18, IQ4_XS: 136, IQ3_XXS: 98, IQ2_S: 82}
-TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ3_S: "IQ3_S", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS", IQ3_XXS: "IQ3_XXS", IQ2_S: "IQ2_S"}
+Q8_0, Q4_K, Q6_K, IQ3_XXS, IQ4_NL, IQ3_S, IQ2_S, IQ4_XS, Q2_0 = 8, 12, 14, 18, 20, 21, 22, 23, 42
+BLOCK_VALUES = {Q8_0: 32, Q4_K: 256, Q6_K: 256, IQ3_S: 256, IQ4_NL: 32, IQ4_XS: 256, IQ3_XXS: 256, IQ2_S: 256, Q2_0: 64}
+BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210, IQ3_S: 110, IQ4_NL: 18, IQ4_XS: 136, IQ3_XXS: 98, IQ2_S: 82, Q2_0: 18}
+TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ3_S: "IQ3_S", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS", IQ3_XXS: "IQ3_XXS", IQ2_S: "IQ2_S", Q2_0: "Q2_0"}
 TYPE_IDS = {v: k for k, v in TYPE_NAMES.items()}
 
 
@@ -43,6 +43,8 @@ def random_blocks(t: int, nblocks: int, rng: np.random.Generator) -> np.ndarray:
         b[:, 0:2] = _f16_bytes(rng, nblocks, 1e-4, 1e-3)
     elif t == IQ2_S:    # codebook bytes 8, 25, 43 times (0.5 + s) / 4
         b[:, 0:2] = _f16_bytes(rng, nblocks, 2.5e-4, 2.5e-3)
+    elif t == Q2_0:     # codes -1 .. 2 times d
+        b[:, 0:2] = _f16_bytes(rng, nblocks, 5e-3, 2e-2)
     elif t == IQ4_NL:   # the table's values reach 127: scales as Q8_0's
         b[:, 0:2] = _f16_bytes(rng, nblocks, 1e-4, 3e-4)
     elif t == IQ4_XS:   # times a 6-bit scale minus 32: d chosen so that the weights are about the size of the others'

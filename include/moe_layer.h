@@ -43,6 +43,7 @@ typedef enum {
 #define MOE_TYPE_IQ3_S 21
 #define MOE_TYPE_IQ2_S 22
 #define MOE_TYPE_IQ4_XS 23
+#define MOE_TYPE_Q2_0 42 /* the reference's fork of ggml (shared/quant.h:33) */
 
 typedef struct moe_layer moe_layer;
 

@@ -50,6 +50,7 @@ void orc_set_threads(int n) {
 uint32_t orc_block_values(uint32_t t) {
   switch (t) {
     case ORC_Q8_0: case ORC_IQ4_NL: return 32;
+    case ORC_Q2_0: return 64;
     case ORC_Q4_K: case ORC_Q6_K: case ORC_Q8_K: case ORC_IQ3_S: case ORC_IQ4_XS: case ORC_IQ3_XXS: case ORC_IQ2_S: return 256;
     default: return 0;
   }
@@ -65,10 +66,11 @@ uint32_t orc_block_bytes(uint32_t t) {
     case ORC_IQ4_XS: return 136;
     case ORC_IQ3_XXS: return 98;
     case ORC_IQ2_S: return 82;
+    case ORC_Q2_0: return 18;
     default: return 0;
   }
 }
-uint32_t orc_vec_dot_type(uint32_t t) { return t == ORC_Q8_0 || t == ORC_IQ4_NL ? ORC_Q8_0 : ORC_Q8_K; }
+uint32_t orc_vec_dot_type(uint32_t t) { return t == ORC_Q8_0 || t == ORC_IQ4_NL || t == ORC_Q2_0 ? ORC_Q8_0 : ORC_Q8_K; }
 uint64_t orc_row_bytes(uint32_t t, uint64_t n) { return n / orc_block_values(t) * orc_block_bytes(t); }
 
 /* The fields of a block in run order, (offset, size): shared/quant.h:78-169. */
@@ -80,7 +82,7 @@ static uint32_t fields(uint32_t t, uint32_t off[5], uint32_t sz[5]) {
     case ORC_IQ3_S:
       off[0] = 2, sz[0] = 64, off[1] = 74, sz[1] = 32, off[2] = 66, sz[2] = 8, off[3] = 106, sz[3] = 4, off[4] = 0, sz[4] = 2;
       return 5;
-    case ORC_IQ4_NL: off[0] = 2, sz[0] = 16, off[1] = 0, sz[1] = 2; return 2;
+    case ORC_IQ4_NL: case ORC_Q2_0: off[0] = 2, sz[0] = 16, off[1] = 0, sz[1] = 2; return 2;
     case ORC_IQ4_XS: off[0] = 8, sz[0] = 128, off[1] = 4, sz[1] = 4, off[2] = 2, sz[2] = 2, off[3] = 0, sz[3] = 2; return 4;
     /* grid indices, scale-and-sign words, d; and grid index low bits, signs, qh, scales, d (QUANT_FORMATS.md:602-603) */
     case ORC_IQ3_XXS: off[0] = 2, sz[0] = 64, off[1] = 66, sz[1] = 32, off[2] = 0, sz[2] = 2; return 3;
@@ -205,6 +207,10 @@ void orc_dequantize_row(uint32_t t, const void *vb, float *y, int64_t n) {
           y[i * QK_K + 32 * ib + 16 + j] = dl * (float)kIq4nlValues[qs[16 * ib + j] >> 4];
         }
       }
+    } else if (t == ORC_Q2_0) {
+      /* y = (q - 1) * d, q the 2-bit code: value j is bits 2 (j mod 4) .. of byte j / 4 (QUANT_FORMATS.md:251-263). */
+      const float d = h2f(rd16(b));
+      for (int j = 0; j < 64; j++) y[i * 64 + j] = (float)((int)((b[2 + j / 4] >> (2 * (j % 4))) & 3) - 1) * d;
     } else if (t == ORC_IQ3_XXS) {
       /* y = d * (0.5 + s) / 2 * grid byte * sign; sub-block sb's word holds four 7-bit sign indices, each completed to
        * 8 signs by parity, and the scale s in bits 28-31 (QUANT_FORMATS.md:147-168). */
@@ -453,6 +459,24 @@ static float dot_iq2_s(int64_t n, const uint8_t *w, const uint8_t *a) {
   return 0.125f * ((r0 + r2) + (r1 + r3));
 }
 
+/* Q2_0 against q8_0: a block of 64 meets two activation blocks of 32; each half's integer sum of (q - 1) * code times
+ * d_w * d_a of its half, as the single-token GPU kernel states it (QUANT_FORMATS.md:265-270). The type is the
+ * reference's fork's; neither gguf-py nor the reference's own CPU kernels (core/cpu/multirow.cpp) have it, so the order
+ * in which ggml's CPU dot adds the halves is not pinned here. */
+static float dot_q2_0(int64_t n, const uint8_t *w, const uint8_t *a) {
+  float sumf = 0.0f;
+  for (int64_t i = 0; i < n / 64; i++, w += 18, a += 68) {
+    const float d = h2f(rd16(w));
+    for (int h = 0; h < 2; h++) {
+      const int8_t *p = (const int8_t *)(a + 34 * h + 2);
+      int sumi = 0;
+      for (int j = 0; j < 32; j++) sumi += ((int)((w[2 + 8 * h + j / 4] >> (2 * (j % 4))) & 3) - 1) * p[j];
+      sumf += (float)sumi * (d * h2f(rd16(a + 34 * h)));
+    }
+  }
+  return sumf;
+}
+
 /* IQ4_NL against q8_0: per block the integer sum of table values times codes, times d_w * d_a (QUANT_FORMATS.md:246-247). */
 static float dot_iq4_nl(int64_t n, const uint8_t *w, const uint8_t *a) {
   float sumf = 0.0f;
@@ -495,6 +519,7 @@ float orc_vec_dot(uint32_t t, int64_t n, const void *w, const void *a) {
     case ORC_IQ4_XS: return dot_iq4_xs(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_IQ3_XXS: return dot_iq3_xxs(n, (const uint8_t *)w, (const uint8_t *)a);
     case ORC_IQ2_S: return dot_iq2_s(n, (const uint8_t *)w, (const uint8_t *)a);
+    case ORC_Q2_0: return dot_q2_0(n, (const uint8_t *)w, (const uint8_t *)a);
     default: return NAN;
   }
 }

@@ -34,6 +34,7 @@ extern "C" {
 #define ORC_IQ3_S 21
 #define ORC_IQ2_S 22
 #define ORC_IQ4_XS 23
+#define ORC_Q2_0 42 /* the reference's fork of ggml: shared/quant.h:33 */
 
 uint32_t orc_block_values(uint32_t type);
 uint32_t orc_block_bytes(uint32_t type);

@@ -14,7 +14,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libmoe_oracle.so")
 
-Q8_0, Q4_K, Q6_K, Q8_K, IQ3_XXS, IQ4_NL, IQ3_S, IQ2_S, IQ4_XS = 8, 12, 14, 15, 18, 20, 21, 22, 23
+Q8_0, Q4_K, Q6_K, Q8_K, IQ3_XXS, IQ4_NL, IQ3_S, IQ2_S, IQ4_XS, Q2_0 = 8, 12, 14, 15, 18, 20, 21, 22, 23, 42
 
 
 def build() -> str:

@@ -9,7 +9,7 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S]
+TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S, synth.Q2_0]
 MAX_REL, MIN_COS = 1e-2, 0.9999   # the bar the layer is held to
 # Routing weights: 1e-5 where the logits are the exactly ordered fp32 sums (steps of up to 64 rows). Longer steps take
 # their logits from the tensor-core product, a few 1e-6 from those sums; the weights follow, while the expert ids, which
@@ -279,9 +279,9 @@ def test_full_shape_sweep_q4k_q6k_q8_0():
     gpu.close()
 
 
-@pytest.mark.parametrize("t", [synth.Q8_0, synth.Q6_K, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S])
+@pytest.mark.parametrize("t", [synth.Q8_0, synth.Q6_K, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S, synth.Q2_0])
 def test_tile_kernels_full_shape_other_types(t):
-    """The tile kernels' Q8_0, Q6_K, IQ4_NL, IQ4_XS, IQ3_XXS and IQ2_S decoders at the full shape (rows of 2048 and of 512 values), every expert on them."""
+    """The tile kernels' Q8_0, Q6_K, IQ4_NL, IQ4_XS, IQ3_XXS, IQ2_S and Q2_0 decoders at the full shape (rows of 2048 and of 512 values), every expert on them."""
     layer = synth.make_layer(gate_type=t, zipf_s=1.1, seed=300 + t)
     gpu = MoELayer(layer, max_tokens=700, tensor_min_rows=1)
     x = synth.make_input(700, 2048, seed=11)

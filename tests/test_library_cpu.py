@@ -40,7 +40,7 @@ def test_struct_layouts_match_the_library():
     assert ctypes.sizeof(_lib.Config) == 68 and ctypes.sizeof(_lib.Weights) == 72 and ctypes.sizeof(_lib.Stats) == 72
 
 
-@pytest.mark.parametrize("t", [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S])
+@pytest.mark.parametrize("t", [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S, synth.Q2_0])
 def test_host_repack_is_a_permutation_in_run_order(t):
     rng = np.random.default_rng(t)
     n = 256

@@ -8,13 +8,27 @@ from c0ven_b200 import synth
 from oracle import oracle as O
 
 TYPES = [synth.Q8_0, synth.Q4_K, synth.Q6_K, synth.IQ3_S, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_XXS, synth.IQ2_S]
+# Q2_0 is a type of the reference's fork of ggml: gguf-py has no decoder for it, so it is held to its stated rule.
+ALL_TYPES = TYPES + [synth.Q2_0]
 
 
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", ALL_TYPES)
 def test_tables_match_shared_quant_h(t):
     assert O.block_values(t) == synth.BLOCK_VALUES[t]
     assert O.block_bytes(t) == synth.BLOCK_BYTES[t]
-    assert O.vec_dot_type(t) == (O.Q8_0 if t in (synth.Q8_0, synth.IQ4_NL) else O.Q8_K)
+    assert O.vec_dot_type(t) == (O.Q8_0 if t in (synth.Q8_0, synth.IQ4_NL, synth.Q2_0) else O.Q8_K)
+
+
+def test_q2_0_decodes_by_its_rule():
+    """y = (q - 1) * d, four 2-bit codes a byte, value j in bits 2 (j mod 4) of byte j / 4 (docs/spec/QUANT_FORMATS.md:251-263)."""
+    rng = np.random.default_rng(42)
+    blocks = synth.random_blocks(synth.Q2_0, 50, rng)
+    blocks[0, 2:] = 0
+    blocks[1, 2:] = 255
+    d = blocks[:, :2].copy().view(np.float16).astype(np.float32)
+    codes = (blocks[:, 2:, None] >> np.array([0, 2, 4, 6], dtype=np.uint8)) & 3
+    want = ((codes.reshape(50, 64).astype(np.float32) - 1) * d).reshape(-1)
+    assert np.array_equal(O.dequantize(synth.Q2_0, blocks, want.size), want)
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -57,7 +71,7 @@ def test_q8_K_quantiser_rule():
     assert d[2] > 0 and d[0] * x[np.argmax(np.abs(xb[0]))] < 0
 
 
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", ALL_TYPES)
 @pytest.mark.parametrize("n", [256, 512, 2048])
 def test_dot_against_own_dequantisation(t, n):
     rng = np.random.default_rng(100 + t + n)
@@ -76,7 +90,7 @@ def test_dot_against_own_dequantisation(t, n):
         assert abs(got - want) <= 1e-4 * np.abs(dw * da).sum()  # quant_test.cpp:120's bound; in practice ~1e-8
 
 
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", ALL_TYPES)
 def test_runs_layout_is_a_permutation(t):
     rng = np.random.default_rng(7)
     n = 40
@@ -86,7 +100,7 @@ def test_runs_layout_is_a_permutation(t):
     assert np.array_equal(O.from_runs(t, runs).reshape(blocks.shape), blocks)
     # The first run holds every block's quants, block k's at k * size (shared/quant.h:172-176).
     qoff, qsz = {synth.Q8_0: (2, 32), synth.Q4_K: (16, 128), synth.Q6_K: (0, 128), synth.IQ3_S: (2, 64),
-                 synth.IQ4_NL: (2, 16), synth.IQ4_XS: (8, 128), synth.IQ3_XXS: (2, 64), synth.IQ2_S: (2, 32)}[t]
+                 synth.IQ4_NL: (2, 16), synth.IQ4_XS: (8, 128), synth.IQ3_XXS: (2, 64), synth.IQ2_S: (2, 32), synth.Q2_0: (2, 16)}[t]
     assert np.array_equal(runs.reshape(-1)[:n * qsz].reshape(n, qsz), blocks[:, qoff:qoff + qsz])
 
 
