@@ -422,8 +422,8 @@ void setup_router_tensor(moe_layer *l, const float *router, const float *bias, c
   CUDA_OK(cudaMemsetAsync(l->rx_hi.get(), 0, xrows * E * sizeof(__half), st));
   CUDA_OK(cudaMemsetAsync(l->rx_lo.get(), 0, xrows * E * sizeof(__half), st));
   l->approx.alloc((size_t)T * NE), l->norm2_parts.alloc((size_t)T * (E / 256));
-  l->rw_hi_map = make_rows_map(l->rw_hi.get(), wrows, E, kRouterTileExperts);
-  l->rw_lo_map = make_rows_map(l->rw_lo.get(), wrows, E, kRouterTileExperts);
+  l->rw_hi_map = make_rows_map(l->rw_hi.get(), wrows, E, 128);  // 128 experts a box: an item takes one or two
+  l->rw_lo_map = make_rows_map(l->rw_lo.get(), wrows, E, 128);
   l->rx_hi_map = make_rows_map(l->rx_hi.get(), xrows, E, kRouterTileRows);
   l->rx_lo_map = make_rows_map(l->rx_lo.get(), xrows, E, kRouterTileRows);
   CUDA_OK(cudaStreamSynchronize(st));
@@ -514,8 +514,11 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
       CUDA_OK(cudaFuncSetAttribute(k_router_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRouterSmemBytes));
       l->router_attr_set = true;
     }
-    const RouterMmaArgs ra{T, E, NE, l->rw_unscale.get(), l->approx.get(), l->error.get()};
-    const uint32_t items = ((T + kRouterTileRows - 1) / kRouterTileRows) * ((NE + kRouterTileExperts - 1) / kRouterTileExperts);
+    // Items of 256 experts halve what is read of x again; items of 128 give a short step twice the CTAs.
+    const uint32_t row_tiles = (T + kRouterTileRows - 1) / kRouterTileRows;
+    const uint32_t ne_tile = row_tiles * ((NE + kRouterTileExperts - 1) / kRouterTileExperts) >= l->sms ? kRouterTileExperts : 128;
+    const RouterMmaArgs ra{T, E, NE, ne_tile, l->rw_unscale.get(), l->approx.get(), l->error.get()};
+    const uint32_t items = row_tiles * ((NE + ne_tile - 1) / ne_tile);
     k_router_mma<<<std::min(items, l->sms), kRouterThreads, kRouterSmemBytes, st>>>(ra, l->rx_hi_map, l->rx_lo_map, l->rw_hi_map, l->rw_lo_map);
   }
   launched(l, cudaGetLastError(), "router logits");

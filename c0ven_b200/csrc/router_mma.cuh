@@ -7,7 +7,7 @@
 // as three f16 MMAs into one f32 accumulator. The router's rows are scaled by a power of two per expert so that their
 // lo parts are normal f16 numbers; the scale is taken out again, exactly, when the accumulators are read.
 //
-// A work item is 128 rows of x by 256 experts; persistent CTAs of six warps take items in turn: one thread issues the
+// A work item is 128 rows of x by 256 experts (128 in steps too short to give every SM an item of 256); persistent CTAs of six warps take items in turn: one thread issues the
 // bulk-tensor copies (x hi and lo: 64 values x 128 rows; the router's hi and lo: 64 values x 256 experts, all in the
 // 128-byte-swizzled K-major layout), one issues the MMAs (M 128, N 256, K 16; twelve a stage), four warps read the
 // accumulators back and store the logits. Tensor memory holds two accumulators of 256 columns, so the MMAs of item
@@ -27,6 +27,7 @@ constexpr uint32_t kRouterSmemBytes = kRouterStages * kRouterStageBytes + 256 + 
 
 struct RouterMmaArgs {
   uint32_t T, E, NE;
+  uint32_t ne_tile;        // experts an item takes: 256, or 128 when items of 256 would leave SMs without one
   const float *w_unscale;  // [NE]: what an accumulator is multiplied by (the inverse of the expert's power-of-two scale)
   float *logits;           // [T][NE]
   uint32_t *error;         // set non-zero when a wait ran out
@@ -40,7 +41,7 @@ static __global__ void __launch_bounds__(kRouterThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const uint32_t KT = a.E / kRouterTileK, col_tiles = (a.NE + kRouterTileExperts - 1) / kRouterTileExperts;
+  const uint32_t KT = a.E / kRouterTileK, ne_tile = a.ne_tile, col_tiles = (a.NE + ne_tile - 1) / ne_tile;
   const uint32_t nitems = ((a.T + kRouterTileRows - 1) / kRouterTileRows) * col_tiles;
   if (blockIdx.x >= nitems) return;
   uint64_t *bars = (uint64_t *)(smem + S * kRouterStageBytes);
@@ -69,17 +70,20 @@ static __global__ void __launch_bounds__(kRouterThreads, 1)
     if (lane == 0) {
       uint32_t li = 0;
       for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
-        const uint32_t row0 = (item / col_tiles) * kRouterTileRows, e0 = (item % col_tiles) * kRouterTileExperts;
+        const uint32_t row0 = (item / col_tiles) * kRouterTileRows, e0 = (item % col_tiles) * ne_tile;
         for (uint32_t it = 0; it < KT && ok; it++) {
           const uint32_t g = li * KT + it, s = g % S, use_s = g / S;
           if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
           if (!ok) break;
           const uint32_t st = smem_u32(smem + s * kRouterStageBytes), k0 = it * kRouterTileK;
-          mbar_arrive_expect(full_bar(s), kRouterStageBytes);
+          // The router's maps copy 128 experts' rows a box: one or two boxes for each half.
+          mbar_arrive_expect(full_bar(s), 2 * kRouterABytes + 2 * ne_tile * kRouterTileK * 2);
           tma_load_rows(st, &x_hi, k0, row0, full_bar(s));
           tma_load_rows(st + kRouterABytes, &x_lo, k0, row0, full_bar(s));
-          tma_load_rows(st + 2 * kRouterABytes, &w_hi, k0, e0, full_bar(s));
-          tma_load_rows(st + 2 * kRouterABytes + kRouterBBytes, &w_lo, k0, e0, full_bar(s));
+          for (uint32_t e = 0; e < ne_tile; e += 128) {
+            tma_load_rows(st + 2 * kRouterABytes + e * kRouterTileK * 2, &w_hi, k0, e0 + e, full_bar(s));
+            tma_load_rows(st + 2 * kRouterABytes + kRouterBBytes + e * kRouterTileK * 2, &w_lo, k0, e0 + e, full_bar(s));
+          }
         }
       }
       if (!ok) {
@@ -91,7 +95,7 @@ static __global__ void __launch_bounds__(kRouterThreads, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | ((kRouterTileExperts >> 3) << 17) | ((kRouterTileRows >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | ((ne_tile >> 3) << 17) | ((kRouterTileRows >> 4) << 24);
       uint32_t li = 0;
       for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
         const uint32_t b = li & 1, use_b = li / 2;
@@ -122,14 +126,14 @@ static __global__ void __launch_bounds__(kRouterThreads, 1)
     const uint32_t q = warp % 4;
     uint32_t li = 0;
     for (uint32_t item = blockIdx.x; item < nitems && ok; item += gridDim.x, li++) {
-      const uint32_t row0 = (item / col_tiles) * kRouterTileRows, e0 = (item % col_tiles) * kRouterTileExperts;
+      const uint32_t row0 = (item / col_tiles) * kRouterTileRows, e0 = (item % col_tiles) * ne_tile;
       const uint32_t b = li & 1, use_b = li / 2;
       ok = mbar_wait(acc_full(b), use_b & 1, abort, a.error);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t = row0 + 32 * q + lane;
       float *out = a.logits + (uint64_t)t * a.NE + e0;
-      for (uint32_t c = 0; c < kRouterTileExperts / 16; c++) {
+      for (uint32_t c = 0; c < ne_tile / 16; c++) {
         if (e0 + 16 * c >= a.NE) break;
         uint32_t v[16];
         tmem_ld16(tmem_base + ((32 * q) << 16) + b * kRouterTileExperts + 16 * c, v);
