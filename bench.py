@@ -341,9 +341,8 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
 
     for m in layers:
         m.set_profiling(True)
-    for ex in moes:
-        if ex is not None:
-            ex.st.shared_beside = False  # in line, so that its stage can be timed
+    for st_ in stages:
+        st_.shared_beside = False  # in line, so that its stage can be timed
     step()
     sync()
     nprof = max(3, min(steps, 10))
@@ -377,6 +376,20 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
         if total >= MIN_TIMED_S or len(e2e_times) >= MAX_TIMED_STEPS:
             break
     e2e_s = agree(statistics.median(e2e_times), MAX)
+
+    # Expert parallel: where a step's device time goes on this rank, phase by phase (a few steps with the phases timed).
+    ep_phases = None
+    if world > 1 and nlayers == 1 and not args.per_assignment:
+        moes[0].time_phases = True
+        acc = {}
+        for i in range(5):
+            step()
+            sync()
+            if i >= 2:
+                for k, v in moes[0].phase_ms.items():
+                    acc[k] = acc.get(k, 0.0) + v / 3
+        moes[0].time_phases = False
+        ep_phases = {k: round(v, 4) for k, v in acc.items()}
 
     # Expert parallel: the rows each rank's experts ran in the last step (routing skew shows here: the busiest rank
     # bounds the step).
@@ -440,6 +453,7 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
                 vs_baseline=None, dtype="f16" if tensor_rows > 0 else "i8", data="synthetic",
                 config=static_config(w, args, world),
                 run=dict(experts_hit=hit, tiles=sum(s["last_tiles"] for s in stats), parallelism=par, expert_rows_per_gpu=ep_rows,
+                         ep_phase_ms=ep_phases,
                          timing=f"median of {len(times)} steps, each between its own events ({steps} asked for; more until {MIN_TIMED_S} s is timed)"),
                 roofline=roof, stage_ms=stage, layer_bytes=alg["bytes_layer"], layer_flops=alg["flops_layer"],
                 cpu_baseline=cpu_line, clocks=clocks.summary(),

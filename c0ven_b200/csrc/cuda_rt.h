@@ -36,7 +36,30 @@ inline void cuda_check(cudaError_t e, const char *what, const char *file, int li
 struct LaunchCtx {
   int device = 0;
   uint32_t sms = 148;
+  bool pdl = false;  // launch-bound steps: kernels are launched as programmatic dependents of the one before (launch_kernel)
 };
+
+#if defined(__CUDACC__)
+// For kernels that may be launched as programmatic dependents: the first lets the kernel after this one be scheduled
+// (it then waits where this one waits), the second waits until the kernels before have completed and their writes are
+// visible. Both do nothing in a kernel launched the ordinary way. They stand at a kernel's top, before it reads or
+// writes anything another kernel touches.
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_predecessors() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// kernel<<<grid, block, smem, st>>>(args...), as a programmatic dependent of the stream's last kernel when pdl is set:
+// it may be scheduled while that kernel still runs, which takes the launch's latency out of a chain of short kernels.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_kernel(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute at{};
+  at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = pdl ? &at : nullptr, cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 // A kernel's opt-in to more than 48 KB of dynamic shared memory holds per device: `done` has a bit per device ordinal
 // (one static word per kernel instantiation), so the attribute is set on a kernel's first launch on a device and not

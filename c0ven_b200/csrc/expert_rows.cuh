@@ -11,6 +11,7 @@
 
 #include <cstdint>
 
+#include "cuda_rt.h"
 #include "formats.h"
 #include "iq4nl_values.h"
 
@@ -556,6 +557,7 @@ __host__ __device__ constexpr int rows_batch(int nmat, int nu, int m, bool heavy
 template <int QT, int NMAT, int M, int G, int UPL>
 __global__ void __launch_bounds__(256) k_expert_rows(const ExpertRowsArgs a, const uint32_t *__restrict__ grid_global) {
   extern __shared__ __align__(16) uint8_t smem[];
+  dependents_may_launch(), wait_for_predecessors();
   constexpr bool q8k = act_is_q8k(QT);
   uint32_t slot, start, n;
   if (a.groups) {

@@ -36,8 +36,7 @@ static cudaError_t launch_one(ExpertRowsArgs a, uint32_t max_groups, const uint3
   }
   a.slabs = slabs;
   const dim3 grid((a.R + a.rows_per_cta * slabs - 1) / (a.rows_per_cta * slabs), max_groups);
-  kernel<<<grid, 256, smem, st>>>(a, grid_global);
-  return cudaGetLastError();
+  return launch_kernel(ctx.pdl, kernel, grid, dim3(256), smem, st, a, grid_global);
 }
 
 template <int QT, int NMAT, int M>

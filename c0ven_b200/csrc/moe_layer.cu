@@ -5,6 +5,7 @@
 // (core/cpu/experts.cpp:152-284).
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <initializer_list>
 #include <memory>
@@ -185,6 +186,7 @@ struct moe_layer {
   uint32_t dest_world = 0;
   ActBuffers xq_routed, xq_shared, hq_routed, hq_shared;
   bool shared_x_same = true, rows_attr_set = false, shared_on_tensor = false;
+  bool pdl_ok = true;  // off when C0VEN_NO_PDL is set in the environment at create
   uint32_t last_T = 0, last_tensor_min = 0;
   const float *residual = nullptr;  // of the call being queued: rows the combine adds last (moe_layer_forward_residual_device)
   PackBuffers *last_pack = nullptr;
@@ -283,6 +285,7 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   l->stream = std::make_unique<Stream>();
   l->aux = std::make_unique<Stream>();
   l->fork_ev = std::make_unique<Event>(), l->join_ev = std::make_unique<Event>();
+  l->pdl_ok = std::getenv("C0VEN_NO_PDL") == nullptr;
   cudaStream_t st = l->stream->get();
   const uint32_t E = l->E, F = l->F, NE = l->NE, K = l->K, T = l->Tmax;
   const uint64_t A = (uint64_t)T * K;
@@ -437,10 +440,13 @@ void quantize_rows(moe_layer *l, const float *src, uint64_t rows, uint32_t Kv, c
   const ActView v = dst.view();
   const unsigned grid = (unsigned)((nblk + 7) / 8);
   if (dst.q8k)
-    k_quant_q8_K<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get(), gate, Kv / 256, gate_parts, rs);
+    launched(l, launch_kernel(l->ctx.pdl, k_quant_q8_K, dim3(grid), dim3(256), 0, st, src, nblk, (int8_t *)v.q, (float *)v.d, (int16_t *)v.bs, dst.h.get(),
+                              gate, Kv / 256, gate_parts, rs),
+             "quantize");
   else
-    k_quant_q8_0<<<grid, 256, 0, st>>>(src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get(), gate, Kv / 256, gate_parts, rs);
-  launched(l, cudaGetLastError(), "quantize");
+    launched(l, launch_kernel(l->ctx.pdl, k_quant_q8_0, dim3(grid), dim3(256), 0, st, src, nblk, (int8_t *)v.q, (float *)v.d, dst.h.get(), gate, Kv / 256,
+                              gate_parts, rs),
+             "quantize");
 }
 
 // Whether a call of R expert rows keeps its experts' results in f16: when every expert takes the tile kernels, whose
@@ -529,10 +535,10 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   const uint32_t chunk_len = kChunkTokens * K;
   if (nchunks == 1 && NE <= 512) {
     // One chunk: top-k, scan and fill in one CTA (the pack stage then has no kernel of its own).
-    k_router_topk_pack<<<1, 32 * kChunkTokens, chunk_len * sizeof(int32_t), st>>>(l->rl.get(), l->bias.get(), T, NE, K, l->ids.get(), l->w.get(),
-                                                                                  l->gs.get(), tm, budget, group_cap(A, NE), l->pack.out(),
-                                                                                  l->pack.inv.get(), l->pack.row_src.get());
-    launched(l, cudaGetLastError(), "router top-k and pack");
+    launched(l, launch_kernel(l->ctx.pdl, k_router_topk_pack, dim3(1), dim3(32 * kChunkTokens), chunk_len * sizeof(int32_t), st, l->rl.get(), l->bias.get(),
+                              T, NE, K, l->ids.get(), l->w.get(), l->gs.get(), tm, budget, group_cap(A, NE), l->pack.out(), l->pack.inv.get(),
+                              l->pack.row_src.get()),
+             "router top-k and pack");
     mark(l, ST_PACK, st);
   } else {
     if (approx) {
@@ -657,25 +663,35 @@ void stage_shared(moe_layer *l, uint32_t T, cudaStream_t st) {
 template <class Y>
 void stage_combine(moe_layer *l, const Y *y, uint32_t T, float *out, cudaStream_t st) {
   mark(l, ST_COMBINE, st);
-  k_combine<Y><<<T, 256, 0, st>>>(y, l->pack.inv.get(), l->w.get(), l->gs.get(), l->has_shared ? l->s.get() : nullptr, l->K, l->E, out,
-                                  l->residual);
-  launched(l, cudaGetLastError(), "combine");
+  launched(l, launch_kernel(l->ctx.pdl, k_combine<Y>, dim3(T), dim3(256), 0, st, y, (const uint32_t *)l->pack.inv.get(), (const float *)l->w.get(),
+                            (const float *)l->gs.get(), (const float *)(l->has_shared ? l->s.get() : nullptr), l->K, l->E, out, l->residual),
+           "combine");
   mark(l, ST_COPIES, st);
 }
 
+constexpr uint32_t kGraphMaxRows = 64;
 constexpr uint64_t kSharedInlineRows = 65536;  // expert rows from which the shared expert runs after the routed ones, not beside them
 
 // The whole block on device buffers, queued on st: a GPU that holds every expert.
 void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {
   if (l->local != l->NE) throw BadArgument("this call needs every expert on the GPU; an expert-parallel layer goes stage by stage");
   const uint64_t A = (uint64_t)T * l->K;
-  stage_route(l, x, T, st);
+  // Launch-bound steps (the ones that are also replayed from a graph): each kernel a programmatic dependent of the one
+  // before it in its stream.
+  l->ctx.pdl = T <= kGraphMaxRows && !l->profile && l->pdl_ok;
+  struct PdlOff {
+    LaunchCtx &c;
+    ~PdlOff() { c.pdl = false; }
+  } pdl_off{l->ctx};
   // The shared expert needs only the quantised rows: it runs on a second stream beside the routed experts and joins
   // before the combine. With per-stage timing on, it runs in line instead, so that its stage can be timed.
   // In long steps it runs in line after all: the routed kernels then fill the GPU for many rounds of items dealt to
   // their CTAs beforehand, and CTAs that start late because the shared expert's hold their SMs finish late (a step of
   // 32,768 rows measured 6 % slower with the two side by side than one after the other; 3,521 rows 5 % faster).
   const bool beside = l->has_shared && !l->profile && A < kSharedInlineRows;
+  // (The quantiser of a short step, whose exact router reads x itself, was tried on the second stream as well, ahead of
+  // the shared expert: 5 us slower at one row, 2 % faster on a stack of 48 layers of 32 rows; not kept.)
+  stage_route(l, x, T, st);
   if (beside) {
     l->fork_ev->record(st);
     CUDA_OK(cudaStreamWaitEvent(l->aux->get(), l->fork_ev->get(), 0));
@@ -696,7 +712,6 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   l->stats.calls++, l->stats.rows += T, l->stats.assignments += A;
 }
 
-constexpr uint32_t kGraphMaxRows = 64;
 
 // forward_device, replayed from a graph when the step is small and has been seen before with the same buffers.
 void forward_step(moe_layer *l, const float *x, uint32_t T, float *out, cudaStream_t st) {

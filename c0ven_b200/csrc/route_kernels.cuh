@@ -68,6 +68,7 @@ __device__ __forceinline__ void router_split(const float4 &a, const float4 &b, u
 static __global__ void __launch_bounds__(256) k_quant_q8_0(const float *__restrict__ x, uint64_t nblk256, int8_t *__restrict__ q,
                                                    float *__restrict__ d, __half *__restrict__ deq, const float *__restrict__ gate,
                                                    uint32_t per_row, float *__restrict__ gate_parts, RouterSplit rs) {
+  dependents_may_launch(), wait_for_predecessors();
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
@@ -103,6 +104,7 @@ static __global__ void __launch_bounds__(256) k_quant_q8_K(const float *__restri
                                                    float *__restrict__ d, int16_t *__restrict__ bs, __half *__restrict__ deq,
                                                    const float *__restrict__ gate, uint32_t per_row, float *__restrict__ gate_parts,
                                                    RouterSplit rs) {
+  dependents_may_launch(), wait_for_predecessors();
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32;
@@ -777,6 +779,7 @@ static __global__ void __launch_bounds__(32 * kChunkTokens, 1) k_router_topk_pac
                                                                        uint32_t *__restrict__ row_src) {
   __shared__ uint32_t hist[512];
   extern __shared__ int32_t s_chunk_ids[];
+  dependents_may_launch(), wait_for_predecessors();
   router_topk_block(rl, RouterApprox{}, bias, T, NE, K, ids, w, gs, hist, s_chunk_ids);
   const uint32_t e = threadIdx.x;
   const uint32_t run = e < NE ? hist[e] : 0;
@@ -807,6 +810,7 @@ static __global__ void __launch_bounds__(256) k_combine(const Y *__restrict__ y,
                                                        const float *__restrict__ w, const float *__restrict__ gs,
                                                        const float *__restrict__ s, uint32_t K, uint32_t E, float *__restrict__ out,
                                                        const float *__restrict__ res) {
+  dependents_may_launch(), wait_for_predecessors();
   const uint32_t t = blockIdx.x;
   __shared__ uint32_t rows[16];
   __shared__ float wk[16];

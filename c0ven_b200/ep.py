@@ -236,6 +236,9 @@ class ExpertParallelMoE:
         self.st, self.group, self.by_token = stages, group, by_token and hasattr(stages, "plan")
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.sent_rows = self.received_rows = self.expert_rows = 0  # of the last step: rows sent to and received from other ranks; rows its experts ran
+        # With time_phases set, forward_by_token brackets its phases with CUDA events on the stages' stream and leaves
+        # their device times in phase_ms after a wait for the step's end (a measuring aid: the wait costs the step).
+        self.time_phases, self.phase_ms = False, {}
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """A stage that fails on one rank (a bad argument, a timeout, a launch error) must not leave the others waiting
@@ -334,52 +337,102 @@ class ExpertParallelMoE:
     def forward_by_token(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """One row per (token, GPU) out, one weighted partial sum per (token, GPU) back. Failures are handled as in
         forward(): what every rank can know is checked on every rank before a row moves; a stage's own failure is held until
-        the step's collectives have been entered."""
+        the step's collectives have been entered. The step is the five phases below one after another."""
+        s = self.by_token_begin(x, out)
+        self.by_token_counts(s)
+        self.by_token_rows_out(s)
+        self.by_token_experts(s)
+        return self.by_token_finish(s)
+
+    def _on_stream(self):
+        return torch.cuda.stream(self.st.stream) if hasattr(self.st, "stream") else _null()
+
+    def _mark(self, s, name):
+        if self.time_phases and hasattr(self.st, "stream"):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(self.st.stream)
+            s["marks"].append((name, ev))
+
+    def by_token_begin(self, x, out=None) -> dict:
+        """Route, start the shared expert, plan the dispatch, gather every rank's totals (on the device: nothing waits yet)."""
         st, W = self.st, self.world
-        held = None
-        with torch.cuda.stream(st.stream) if hasattr(st, "stream") else _null():
+        s = dict(x=x, out=out, held=None, marks=[])
+        with self._on_stream():
+            self._mark(s, "route")
             st.route(x)
             if hasattr(st, "shared_start"):
                 st.shared_start()
+            self._mark(s, "plan")
             tot = st.plan()                                          # [16]: rows to each GPU, then assignments to each
-            tot_all = st.empty((W * 16,), tot.dtype, "tot_all")
-            dist.all_gather_into_tensor(tot_all, tot, group=self.group)
-            m = tot_all.cpu().numpy().reshape(W, 2, 8)               # the step's one wait on the host
-            send, recv = [int(v) for v in m[self.rank, 0, :W]], [int(v) for v in m[:, 0, self.rank]]
-            asg_in = int(m[:, 1, self.rank].sum())
-            most = getattr(st, "max_expert_rows", 0)
-            if most:
-                entries = m[:, 0, :W].sum(0) * st.n_used             # what every rank would receive, the same on every rank
-                if int(entries.max()) > most:
-                    raise RuntimeError(f"rank {int(entries.argmax())} would receive {int(entries.max())} row entries, more than "
-                                       f"max_expert_rows {most}: every rank stops here, before the exchange")
-            R = sum(recv)
+            s["tot_all"] = st.empty((W * 16,), tot.dtype, "tot_all")
+            dist.all_gather_into_tensor(s["tot_all"], tot, group=self.group)
+        return s
+
+    def by_token_counts(self, s: dict) -> None:
+        """The step's one wait on the host: the split sizes; what every rank can refuse is refused here, on every rank."""
+        st, W = self.st, self.world
+        with self._on_stream():
+            m = s["tot_all"].cpu().numpy().reshape(W, 2, 8)
+        s["send"], s["recv"] = [int(v) for v in m[self.rank, 0, :W]], [int(v) for v in m[:, 0, self.rank]]
+        s["asg_in"] = int(m[:, 1, self.rank].sum())
+        most = getattr(st, "max_expert_rows", 0)
+        if most:
+            entries = m[:, 0, :W].sum(0) * st.n_used                 # what every rank would receive, the same on every rank
+            if int(entries.max()) > most:
+                raise RuntimeError(f"rank {int(entries.argmax())} would receive {int(entries.max())} row entries, more than "
+                                   f"max_expert_rows {most}: every rank stops here, before the exchange")
+
+    def by_token_rows_out(self, s: dict) -> None:
+        st = self.st
+        send, recv = s["send"], s["recv"]
+        with self._on_stream():
+            self._mark(s, "dispatch")
             try:
                 rows = st.dispatch(sum(send))
             except Exception as e:  # noqa: BLE001
-                held, rows = e, st.empty((sum(send), st.dispatch_bytes), torch.uint8, "drows")
-            rows_in = st.empty((R, rows.shape[1]), rows.dtype, "drows_in")
-            dist.all_to_all_single(rows_in, rows, recv, send, group=self.group)
+                s["held"], rows = e, st.empty((sum(send), st.dispatch_bytes), torch.uint8, "drows")
+            s["rows_in"] = st.empty((sum(recv), rows.shape[1]), rows.dtype, "drows_in")
+            self._mark(s, "rows out")
+            dist.all_to_all_single(s["rows_in"], rows, recv, send, group=self.group)
+
+    def by_token_experts(self, s: dict) -> None:
+        st = self.st
+        send, recv, R = s["send"], s["recv"], sum(s["recv"])
+        with self._on_stream():
+            self._mark(s, "experts")
             y_in = None
-            if held is None:
+            if s["held"] is None:
                 try:
-                    y_in = st.experts_partial(rows_in, asg_in)       # [R][E] f16, in arrival order
+                    y_in = st.experts_partial(s["rows_in"], s["asg_in"])   # [R][E] f16, in arrival order
                 except Exception as e:  # noqa: BLE001
-                    held = e
+                    s["held"] = e
             if y_in is None:
-                y_in = st.empty((R, x.shape[1]), getattr(st, "partial_dtype", torch.float16), "y_part")   # the type every rank sends
-            back = st.empty((sum(send), y_in.shape[1]), y_in.dtype, "y_back")
-            dist.all_to_all_single(back, y_in, send, recv, group=self.group)
-            if held is not None:
-                raise held
+                y_in = st.empty((R, s["x"].shape[1]), getattr(st, "partial_dtype", torch.float16), "y_part")   # the type every rank sends
+            s["back"] = st.empty((sum(send), y_in.shape[1]), y_in.dtype, "y_back")
+            self._mark(s, "sums back")
+            dist.all_to_all_single(s["back"], y_in, send, recv, group=self.group)
+
+    def by_token_finish(self, s: dict) -> torch.Tensor:
+        st = self.st
+        if s["held"] is not None:
+            raise s["held"]
+        with self._on_stream():
+            self._mark(s, "combine")
             if hasattr(st, "shared_finish"):
                 st.shared_finish()
             else:
                 st.shared()
+            out = s["out"]
             if out is None:
-                out = st.empty(tuple(x.shape), torch.float32)
-            st.combine_partials(back, out)
-        self.sent_rows, self.received_rows, self.expert_rows = sum(send) - send[self.rank], R - recv[self.rank], asg_in
+                out = st.empty(tuple(s["x"].shape), torch.float32)
+            st.combine_partials(s["back"], out)
+            self._mark(s, "end")
+        marks = s["marks"]
+        if marks:
+            marks[-1][1].synchronize()
+            self.phase_ms = {a[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks, marks[1:])}
+        send, recv = s["send"], s["recv"]
+        self.sent_rows, self.received_rows, self.expert_rows = sum(send) - send[self.rank], sum(recv) - recv[self.rank], s["asg_in"]
         return out
 
 

@@ -4,7 +4,7 @@ offsets and sizes, as a C compiler lays them out on x86-64. The header is read w
 offsetof and sizeof for each, and the result is the table the reference's own engine_abi_layout returns
 (include/engine_api.h:414-421: one row per field, "struct.field", then one row per struct).
 
-    python tests/golden/make_engine_abi_golden.py /root/reference
+    python tests/golden/make_engine_abi_golden.py <the reference's checkout>
 """
 import json
 import os
@@ -51,4 +51,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_engine_abi_golden.py <the reference's checkout>")
+    main(sys.argv[1])
