@@ -520,9 +520,10 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
       CUDA_OK(cudaFuncSetAttribute(k_router_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRouterSmemBytes));
       l->router_attr_set = true;
     }
-    // Items of 256 experts halve what is read of x again; items of 128 give a short step twice the CTAs.
+    // Items of 256 experts halve what is read of x again; items of 128 give a short step twice the CTAs, as long as
+    // they still all run at once (8,192 rows: 128 items of 256 experts took 50 us, 256 items of 128 took 62).
     const uint32_t row_tiles = (T + kRouterTileRows - 1) / kRouterTileRows;
-    const uint32_t ne_tile = row_tiles * ((NE + kRouterTileExperts - 1) / kRouterTileExperts) >= l->sms ? kRouterTileExperts : 128;
+    const uint32_t ne_tile = 2 * row_tiles * ((NE + kRouterTileExperts - 1) / kRouterTileExperts) <= l->sms ? 128 : kRouterTileExperts;
     const RouterMmaArgs ra{T, E, NE, ne_tile, l->rw_unscale.get(), l->approx.get(), l->error.get()};
     const uint32_t items = row_tiles * ((NE + ne_tile - 1) / ne_tile);
     k_router_mma<<<std::min(items, l->sms), kRouterThreads, kRouterSmemBytes, st>>>(ra, l->rx_hi_map, l->rx_lo_map, l->rw_hi_map, l->rw_lo_map);
