@@ -220,7 +220,8 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
         lw = base if i == 0 else dict(base, router=(np.random.default_rng(100 + i).standard_normal((NE, E)) * 0.02).astype(np.float32))
         if world == 1:
             m = MoELayer(lw, max_tokens=T, device=local, profile=False, tensor_min_rows=args.tensor_min,
-                         host_chunk_rows=args.host_chunk if args.host_chunk >= 0 else (8192 if T >= 16384 else 0))
+                         host_chunk_rows=args.host_chunk if args.host_chunk >= 0 else (8192 if T >= 16384 else 0),
+                         gather_in_kernel=args.gather_in_kernel)
             layers.append(m), moes.append(None)
             main_sp = main_sp or m.stream
         else:
@@ -508,6 +509,8 @@ def main():
     ap.add_argument("--host-chunk", type=int, default=-1,
                     help="rows of a chunk of the host-buffer call, whose copies overlap its neighbours' computation (0: never cut; default: 8192 for batches of 16384 rows and more)")
     ap.add_argument("--per-assignment", action="store_true", help="expert parallel: one row per assignment on the wire (one GPU's bits) instead of one per (token, GPU)")
+    ap.add_argument("--gather-in-kernel", action="store_true",
+                    help="long steps: the gate/up tile kernel gathers its rows by index itself (MOE_FLAG_GATHER_IN_KERNEL)")
     ap.add_argument("--contiguous", action="store_true", help="expert parallel: GPU g holds experts [g * per, (g + 1) * per) of the layer as given")
     ap.add_argument("--tensor-min", type=int, default=0, help="rows from which an expert takes the tensor-core kernels (0: the library's default)")
     args = ap.parse_args()

@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libc0ven_moe.so")
 
 MOE_OK, MOE_ERROR, MOE_BAD_ARGUMENT, MOE_BUSY, MOE_TIMEOUT = range(5)
-FLAG_PROFILE, FLAG_NO_TENSOR = 1, 2
+FLAG_PROFILE, FLAG_NO_TENSOR, FLAG_GATHER_IN_KERNEL = 1, 2, 4
 STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine", "copies")
 
 SYMBOLS = ("moe_layer_create", "moe_layer_destroy", "moe_layer_forward", "moe_layer_forward_device", "moe_layer_sync",

@@ -46,6 +46,8 @@ struct ExpertTilesArgs {
   const BigTile *tiles;     // null: dense_rows rows of slot 0 in tiles of kTileN
   const uint32_t *ntiles;
   uint32_t dense_rows;
+  const uint32_t *gather_rows;  // not null: row r of the tiles' order is row gather_rows[r] of the map's tensor, whose box is
+                                // one row (the copies gather four rows each); null: the same row, boxes of 64 rows
   void *out;                // out[expert-order row][r]: f32, or f16 when out_f16 is set
   uint32_t out_stride;
   uint32_t out_f16;
@@ -115,6 +117,23 @@ __device__ __forceinline__ void tma_load_rows(uint32_t dst_smem, const CUtensorM
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar)
                : "memory");
+}
+// Four rows y0 .. y3 of the map's tensor (its box one row of 64 values), values x .. x + 63 of each, into four
+// consecutive 128-byte rows of shared memory at dst (512-byte aligned inside a 1024-byte aligned tile), swizzled as the
+// tile's other rows are. The rows need not be neighbours: this is how a tile's rows are gathered by index.
+__device__ __forceinline__ void tma_gather4_rows(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y0, uint32_t y1, uint32_t y2,
+                                                 uint32_t y3, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+               ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar)
+               : "memory");
+}
+// The same by a CTA of a pair, the bytes counted on a barrier that may be the other CTA's.
+__device__ __forceinline__ void tma_gather4_rows_pair(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y0, uint32_t y1,
+                                                      uint32_t y2, uint32_t y3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar)
+      : "memory");
 }
 // Box (x .. of the row's bytes, rows y .., expert slot z) of a weight matrix's quants run into shared memory at dst.
 // x is a multiple of 16 bytes.
@@ -1062,9 +1081,60 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
       }
     }
   } else if (warp == kCopyWarp) {
-    // The copy thread: per stage, the 64 values of the tile's rows, 64 rows a copy, in the swizzled layout. A copy may
-    // run past the tile's rows into the next expert's, or past the tensor (zeros): those columns of the result are dropped.
-    if (lane == 0) {
+    if (a.gather_rows) {
+      // The copy warp, gathering: the tile's rows are scattered over the activations (row r of the expert order is row
+      // gather_rows[r] of the map's tensor) and a copy brings four of them: up to 32 copies a stage for a pair's CTA (one
+      // a lane), 64 for a single CTA (two a lane). A lane keeps its row indices for the whole item. Rows past the
+      // tile's count repeat its last row; their columns of the result are dropped.
+      constexpr uint32_t kPerLane = PAIR ? 1 : 2;
+      uint32_t li = 0;
+      for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
+        const ItemTile t = item_tile(a, item / RTU);
+        const uint32_t half = ((t.count + 15) & ~15u) / 2;
+        const uint32_t mine = PAIR ? half : t.count, first_row = PAIR ? rank * half : 0;
+        const uint32_t ncopies = (mine + 3) / 4;
+        uint32_t idx[4 * kPerLane];
+#pragma unroll
+        for (uint32_t j = 0; j < 4 * kPerLane; j++) {
+          const uint32_t r = first_row + 4 * (lane + 32 * (j / 4)) + j % 4;
+          idx[j] = a.gather_rows[t.start + min(r, t.count - 1)];
+        }
+        for (uint32_t it = 0; it < KT && ok; it++) {
+          const uint32_t g = li * KT + it, s = g % S, use_s = g / S;
+          const uint32_t bar = PAIR ? full_lead(s) : full_bar(s);
+          if (lane == 0) {
+            if (use_s > 0) ok = mbar_wait(empty_bar(s), (use_s - 1) & 1, abort, a.error);
+            if (ok) {
+              if constexpr (PAIR)
+                mbar_arrive_expect_cluster(bar, ncopies * 4 * kTileK * 2);
+              else
+                mbar_arrive_expect(bar, ncopies * 4 * kTileK * 2);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          const uint32_t xt = smem_u32(smem + s * SM::kStageBytes) + NMAT * SM::kWBytes;
+#pragma unroll
+          for (uint32_t c = 0; c < kPerLane; c++) {
+            const uint32_t copy = lane + 32 * c;
+            if (copy < ncopies) {
+              if constexpr (PAIR)
+                tma_gather4_rows_pair(xt + copy * 4 * kTileK * 2, &act_map, it * kTileK, idx[4 * c], idx[4 * c + 1], idx[4 * c + 2], idx[4 * c + 3], bar);
+              else
+                tma_gather4_rows(xt + copy * 4 * kTileK * 2, &act_map, it * kTileK, idx[4 * c], idx[4 * c + 1], idx[4 * c + 2], idx[4 * c + 3], bar);
+            }
+          }
+        }
+      }
+      if (!ok && lane == 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000) {
+        }
+      }
+      __syncwarp();
+    } else if (lane == 0) {
+      // The copy thread: per stage, the 64 values of the tile's rows, 64 rows a copy, in the swizzled layout. A copy may
+      // run past the tile's rows into the next expert's, or past the tensor (zeros): those columns of the result are dropped.
       uint32_t li = 0;
       for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
         const ItemTile t = item_tile(a, item / RTU);
@@ -1095,26 +1165,27 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         while (clock64() - t0 < 400000) {
         }
       }
-    } else if (quants_by_copy(QT) && lane == 1) {
-      // The quants' copy thread: a quant slot, one stage per decode group for every weight row of the item, as soon
-      // as the decode warps have read the slot's last contents; it runs ahead of the stages by the ring's two slots.
-      uint32_t li = 0;
-      for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
-        const ItemTile t = item_tile(a, item / RTU);
-        for (uint32_t j = 0; j < KT / kDecGroups && ok; j++) {
-          const uint32_t qn = li * (KT / kDecGroups) + j, qb = qn % SM::kQSlots, use_q = qn / SM::kQSlots;
-          if (use_q > 0) ok = mbar_wait(q_empty(qb), (use_q - 1) & 1, abort, a.error);
-          if (!ok) break;
-          const uint32_t dst = smem_u32(smem + SM::kQuants + qb * SM::kQSlotBytes);
-          mbar_arrive_expect(q_full(qb), SM::kQSlotBytes);
-          for (uint32_t mt = 0; mt < (uint32_t)NMAT; mt++)
-            tma_load_quants(dst + mt * SM::kQMatBytes, &a.qmap[mt], j * SM::kQRowBytes, item_rows0(item), t.slot, q_full(qb));
-        }
+    }
+  } else if (quants_by_copy(QT) && lane == 1) {
+    // (A lane of the warp that owns tensor memory.)
+    // The quants' copy thread: a quant slot, one stage per decode group for every weight row of the item, as soon
+    // as the decode warps have read the slot's last contents; it runs ahead of the stages by the ring's two slots.
+    uint32_t li = 0;
+    for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
+      const ItemTile t = item_tile(a, item / RTU);
+      for (uint32_t j = 0; j < KT / kDecGroups && ok; j++) {
+        const uint32_t qn = li * (KT / kDecGroups) + j, qb = qn % SM::kQSlots, use_q = qn / SM::kQSlots;
+        if (use_q > 0) ok = mbar_wait(q_empty(qb), (use_q - 1) & 1, abort, a.error);
+        if (!ok) break;
+        const uint32_t dst = smem_u32(smem + SM::kQuants + qb * SM::kQSlotBytes);
+        mbar_arrive_expect(q_full(qb), SM::kQSlotBytes);
+        for (uint32_t mt = 0; mt < (uint32_t)NMAT; mt++)
+          tma_load_quants(dst + mt * SM::kQMatBytes, &a.qmap[mt], j * SM::kQRowBytes, item_rows0(item), t.slot, q_full(qb));
       }
-      if (!ok) {
-        const long long t0 = clock64();
-        while (clock64() - t0 < 400000) {
-        }
+    }
+    if (!ok) {
+      const long long t0 = clock64();
+      while (clock64() - t0 < 400000) {
       }
     }
   } else if (lane == 0 && rank == 0) {

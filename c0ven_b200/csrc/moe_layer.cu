@@ -78,6 +78,7 @@ struct ActBuffers {
   DeviceBuffer<int16_t> bs;
   DeviceBuffer<__half> h;  // the codes dequantised, f16: the tensor-core kernels' operand
   CUtensorMap h_map{};     // over h, for the tile kernels' copies
+  CUtensorMap h_row_map{}; // over h with a box of one row: for copies that gather rows by index
   bool q8k = false;
   uint32_t K = 0;
   void alloc(uint64_t rows, uint32_t Kv, bool k, bool with_f16) {
@@ -89,6 +90,7 @@ struct ActBuffers {
       const uint64_t hr = std::max<uint64_t>(rows, kMapBoxRows);  // a map's tensor is at least one box high
       h.alloc(hr * K);
       h_map = make_rows_map(h.get(), hr, K);
+      h_row_map = make_rows_map(h.get(), hr, K, 1);
     }
   }
   ActView view(uint64_t row0 = 0) const {
@@ -179,6 +181,7 @@ struct moe_layer {
   DeviceBuffer<__half> wire_h;  // rows from other GPUs, dequantised for the tensor-core kernels
   DeviceBuffer<__half> xg;      // the routed experts' activation rows in expert order, f16: what their tile kernel copies from
   CUtensorMap xg_map{};
+
   PackBuffers pack, pack_local;  // the step's own rows over every expert; the rows received, over this GPU's experts
   // Expert parallel with one row per (token, GPU): where each token's row goes, and the received rows' lists.
   DeviceBuffer<uint32_t> dest_pos, dest_chunk_cnt, dest_chunk_asg, dest_totals;
@@ -561,6 +564,8 @@ void stage_route(moe_layer *l, const float *x, uint32_t T, cudaStream_t st) {
   l->last_T = T, l->last_pack = &l->pack;
 }
 
+constexpr uint64_t kGatherInKernelRows = 163840;  // expert rows from which the gate/up tile kernel gathers its rows itself
+
 // The routed experts on the R rows a pack lists: gate/up and SwiGLU into h, h quantised, down into y (expert order).
 // most: the most rows one expert can have (a step's tokens; in an expert-parallel call, not known below R).
 // y16: the results in f16 (only with every expert on the tile kernels: the integer-dot kernels write f32).
@@ -577,13 +582,22 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   // The pack may have lowered the threshold to 1 (tensor_budget_for): the tile launches are sized for that.
   const uint32_t tm_low = tm && tensor_budget_for(l, R) ? 1 : tm;
   const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
+  // With MOE_FLAG_GATHER_IN_KERNEL, long steps of a GPU's own rows: the gate/up tile kernel gathers the rows by index
+  // itself (cp.async.bulk.tensor's tile::gather4 form, 32 copies of four rows a stage for a pair's CTA instead of two
+  // boxes of 64). The copies then set that kernel's pace (1.46 -> 1.84 ms at 32,768 rows) but the 0.48 ms gather kernel
+  // and its 1.3 GB each way go: the step 4.54 -> 4.41 ms on one box. At 3,521 rows it is no gain (0.682 -> 0.687 ms).
+  // Not the default: three parts in a hundred of a step for a dominant kernel that no longer runs at the tensor
+  // cores' pace.
+  const bool gather_in_kernel = (l->cfg.flags & MOE_FLAG_GATHER_IN_KERNEL) && max_big && R >= kGatherInKernelRows &&
+                                src.h == l->xq_routed.h.get() && src.act_row != nullptr;
   if (max_big) {
     // The rows in expert order first (the reference's p_moe_scatter, kernels/models/qwen4exp/prompt.cl:744-754): a tile's
     // rows are then one box after another for the kernel's copies. Part of the pack stage: the gate/up stage times the
-    // product's own kernels. (Copies that gather four rows by index, cp.async.bulk.tensor's tile::gather4 form, were
-    // measured in its place: 64 copies a stage instead of 4 held the tile kernel to half its rate.)
-    k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
-    launched(l, cudaGetLastError(), "rows to expert order");
+    // product's own kernels.
+    if (!gather_in_kernel) {
+      k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
+      launched(l, cudaGetLastError(), "rows to expert order");
+    }
   }
   mark(l, ST_GATE_UP, st);
   if (max_big) {
@@ -592,7 +606,12 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     a.qmap[0] = l->wg_q, a.qmap[1] = l->wu_q;
     a.tiles = pk.big.get(), a.ntiles = pk.counters.get() + 4;
     a.out = l->h.get(), a.out_stride = F, a.limit = c.swiglu_limit, a.error = l->error.get();
-    launched(l, launch_tiles(c.gate_type, 2, a, l->xg_map, max_big, l->grid.get(), l->ctx, st), "experts gate/up tiles");
+    if (gather_in_kernel) {
+      a.gather_rows = src.act_row;
+      launched(l, launch_tiles(c.gate_type, 2, a, l->xq_routed.h_row_map, max_big, l->grid.get(), l->ctx, st), "experts gate/up tiles");
+    } else {
+      launched(l, launch_tiles(c.gate_type, 2, a, l->xg_map, max_big, l->grid.get(), l->ctx, st), "experts gate/up tiles");
+    }
   }
   if (max_groups) {
     ExpertRowsArgs a{};

@@ -73,7 +73,7 @@ class MoELayer:
 
     def __init__(self, layer: dict, max_tokens: int = 4352, device: int = 0, profile: bool = False,
                  expert_first: int = 0, expert_count: int = 0, no_tensor: bool = False, tensor_min_rows: int = 0,
-                 max_expert_rows: int = 0, host_chunk_rows: int = 0, own_experts=None):
+                 max_expert_rows: int = 0, host_chunk_rows: int = 0, own_experts=None, gather_in_kernel: bool = False):
         """own_experts: this GPU's experts' (gate, up, down) arrays, [expert_count][rows][row bytes] each, when they are
         not the slice [expert_first, expert_first + expert_count) of the layer's own arrays."""
         self._h = None
@@ -86,7 +86,8 @@ class MoELayer:
         cfg = _lib.Config(self.n_embd, self.n_ff, self.n_experts, self.n_used, layer["gate_type"], layer["down_type"],
                           layer["shexp_gate_type"] if has_shared else 0, layer["shexp_down_type"] if has_shared else 0,
                           expert_first, count, max_tokens, device, float(layer.get("swiglu_limit", 0.0)),
-                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0), tensor_min_rows, max_expert_rows, host_chunk_rows)
+                          (_lib.FLAG_PROFILE if profile else 0) | (_lib.FLAG_NO_TENSOR if no_tensor else 0)
+                          | (_lib.FLAG_GATHER_IN_KERNEL if gather_in_kernel else 0), tensor_min_rows, max_expert_rows, host_chunk_rows)
         sl = slice(expert_first, expert_first + count)
         ge, ue, de = own_experts if own_experts is not None else (layer["gate_exps"][sl], layer["up_exps"][sl], layer["down_exps"][sl])
         if len(ge) != count or len(ue) != count or len(de) != count:

@@ -264,6 +264,23 @@ def test_full_size_prefill32768_q4_k():
     gpu.close()
 
 
+def test_gate_up_kernel_gathering_its_rows_itself():
+    """MOE_FLAG_GATHER_IN_KERNEL at a size it applies to (16,384 rows, 163,840 expert rows): the tile kernel fetches its
+    rows by index with four-row gather copies. The products do not depend on how the rows came in, so the outputs are
+    the bits of the layer that gathers first; routing against the oracle, outputs of sampled rows too."""
+    layer = synth.make_layer(gate_type=synth.Q4_K, zipf_s=0.0, seed=77)
+    T = 16384
+    x = synth.make_input(T, 2048, seed=78)
+    a = MoELayer(layer, max_tokens=T)
+    want = a.forward(x).copy()
+    a.close()
+    b = MoELayer(layer, max_tokens=T, gather_in_kernel=True)
+    _route_and_sample(layer, b, x, np.linspace(0, T - 1, 24).astype(np.int64))
+    got = b.forward(x)
+    assert np.array_equal(got, want)
+    b.close()
+
+
 def test_full_shape_sweep_q4k_q6k_q8_0():
     """Configuration 5 at the real shape (hidden 2048, FFN 512, 512 experts, top 10): Q4_K gate and up, Q6_K down, Q8_0
     shared expert, Zipf routing, at every point of its sweep. Short steps whole against the oracle; the long ones by
