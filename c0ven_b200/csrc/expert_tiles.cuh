@@ -35,7 +35,7 @@ constexpr uint32_t kTileN = 256;   // activation rows at most
 constexpr uint32_t kTileK = 64;    // values of the contraction a stage holds
 constexpr uint32_t kTileDecoders = 512;  // threads that decode weights: 16 warps, enough of them to hide their loads' latency
 constexpr uint32_t kTileEpilogue = 128;  // threads that turn accumulators into results: a warp per quarter of the weight rows
-constexpr uint32_t kTileThreads = kTileDecoders + kTileEpilogue + 64;  // and the warp whose first lane issues the copies, and the MMA warp
+constexpr uint32_t kTileThreads = kTileDecoders + kTileEpilogue + 96;  // and the rows' copy warp, the MMA warp, the quants' copy warp
 constexpr uint32_t kTileBoxRows = 64;    // rows one bulk-tensor copy brings (the tensor map's box: 64 values x 64 rows)
 
 struct ExpertTilesArgs {
@@ -732,11 +732,13 @@ __device__ __forceinline__ ItemTile item_tile(const ExpertTilesArgs &a, uint32_t
 }
 
 // NMAT 2: out = swiglu(gate x, up x); NMAT 1: out = down h. Persistent: the grid is one CTA per SM (fewer when there is
-// less work), and CTA b takes the work items b, b + gridDim.x, ...; item i is weight-row tile i % (R / 128) of big tile
-// i / (R / 128), so neighbouring CTAs share a tile's activations in L2. Four roles: 16 decode warps (quants to f16
-// weights in shared memory), 4 epilogue warps (accumulators to the result), a warp whose first lane issues the
-// bulk-tensor copies of the rows' activations, and the warp that owns tensor memory and whose first lane issues the
-// MMAs. A warp arrives on a barrier once, by one lane.
+// less work), single or in pairs (PAIR, below); a unit (a CTA or a pair) takes the work items dealt to it round by
+// round; item i is weight-row tile (or pair of tiles) i % RTU of big tile i / RTU, so neighbouring units share a tile's
+// activations in L2. Five roles: 16 decode warps (quants to f16 weights in shared memory), 4 epilogue warps
+// (accumulators to the result), a warp whose first lane issues the bulk-tensor copies of the rows' activations (the
+// whole warp when the rows are gathered by index), the warp that owns tensor memory and whose first lane issues the
+// MMAs, and a warp whose first lane issues the copies of the quants for types that take them through the ring. A warp
+// arrives on a barrier once, by one lane.
 //
 // Tensor memory is two buffers of 256 columns. An item of at most 128 rows (any item, for NMAT 1) takes one buffer,
 // alternately, so the epilogue warps drain item i while the MMAs of item i + 1 run and the decode warps never stop. A
@@ -752,7 +754,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
   using Dec = Decoder<QT>;
   using Raw = typename Dec::Raw;
   constexpr uint32_t S = SM::kStages, kCols = 512;
-  constexpr uint32_t kDW = kTileDecoders / 32, kEW = kTileEpilogue / 32, kCopyWarp = kDW + kEW, kMmaWarp = kCopyWarp + 1;
+  constexpr uint32_t kDW = kTileDecoders / 32, kEW = kTileEpilogue / 32, kCopyWarp = kDW + kEW, kMmaWarp = kCopyWarp + 1, kQuantWarp = kMmaWarp + 1;
   // A decode thread takes a whole row of a stage, 64 values as two halves of 32, so that what a stage costs a thread
   // beside the arithmetic (the barrier round trip, the addresses, the block's scales) is paid once per 64 values. A
   // stage's NMAT * 128 rows are one group of threads; the 512 decode threads form 2 groups (two matrices) or 4 (one),
@@ -1166,9 +1168,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
         }
       }
     }
-  } else if (quants_by_copy(QT) && lane == 1) {
-    // (A lane of the warp that owns tensor memory.)
-    // The quants' copy thread: a quant slot, one stage per decode group for every weight row of the item, as soon
+  } else if (warp == kQuantWarp) {
+    if (quants_by_copy(QT) && lane == 0) {
+    // The quants' copy thread (a warp of its own: sharing a warp with the MMA thread cost the tile kernels 8 %): a quant slot, one stage per decode group for every weight row of the item, as soon
     // as the decode warps have read the slot's last contents; it runs ahead of the stages by the ring's two slots.
     uint32_t li = 0;
     for (uint32_t rnd = 0, item; (item = item_at(rnd)) != kNoItem && ok; rnd++, li++) {
@@ -1187,6 +1189,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
       const long long t0 = clock64();
       while (clock64() - t0 < 400000) {
       }
+    }
     }
   } else if (lane == 0 && rank == 0) {
     // The MMA thread (of a pair's first CTA): per stage, four K steps of 16 for each matrix; the commit frees the stage
