@@ -584,10 +584,10 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
   // With MOE_FLAG_GATHER_IN_KERNEL, long steps of a GPU's own rows: the gate/up tile kernel gathers the rows by index
   // itself (cp.async.bulk.tensor's tile::gather4 form, 32 copies of four rows a stage for a pair's CTA instead of two
-  // boxes of 64). The copies then set that kernel's pace (1.46 -> 1.84 ms at 32,768 rows) but the 0.48 ms gather kernel
-  // and its 1.3 GB each way go: the step 4.54 -> 4.41 ms on one box. At 3,521 rows it is no gain (0.682 -> 0.687 ms).
-  // Not the default: three parts in a hundred of a step for a dominant kernel that no longer runs at the tensor
-  // cores' pace.
+  // boxes of 64). The copies then set that kernel's pace (1.39 -> 1.85 ms at 32,768 rows) but the 0.48 ms gather kernel
+  // and its 1.3 GB each way go: the step 4.39 -> 4.35 ms on one box; no gain at 3,521 rows. Not the default: one part in
+  // a hundred of a step for a dominant kernel that no longer runs at the tensor cores' pace. (The same gather by the
+  // copy warp's own 16-byte asynchronous copies, cp.async, was slower still: 2.26 ms.)
   const bool gather_in_kernel = (l->cfg.flags & MOE_FLAG_GATHER_IN_KERNEL) && max_big && R >= kGatherInKernelRows &&
                                 src.h == l->xq_routed.h.get() && src.act_row != nullptr;
   if (max_big) {
