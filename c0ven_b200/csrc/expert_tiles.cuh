@@ -831,9 +831,9 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_expert_tiles(const __grid_c
   // The weight rows of an item that this CTA decodes and drains.
   auto item_rows0 = [&](uint32_t item) { return ((item % RTU) * (PAIR ? 2u : 1u) + rank) * kTileM; };
 
-  // CTA b's item of round r: the items come sorted by size (full tiles first, then the others by falling row count), and
-  // the rounds deal them boustrophedon (b, then G - 1 - b, ...), so that every CTA gets a like share of long and short
-  // items. kNoItem past the end; a CTA's last round may have no item for it while others still have one.
+  // CTA b's item of round r: the items come expert by expert for the experts with full tiles, then the short tiles of
+  // the others by falling row count, and the rounds deal them boustrophedon (b, then G - 1 - b, ...), so that every CTA
+  // gets a like share of long and short items. kNoItem past the end; a CTA's last round may have no item for it while others still have one.
   constexpr uint32_t kNoItem = 0xFFFFFFFFu;
   auto item_at = [&](uint32_t rnd) {
     const uint32_t base = rnd * nunits;

@@ -52,7 +52,7 @@ def test_two_ranks_give_the_single_process_bits(T):
     assert res[0][2] == res[1][3] and res[1][2] == res[0][3]
 
 
-@pytest.mark.parametrize("world,T", [(2, (37, 5)), (4, (9, 1, 30, 2))])
+@pytest.mark.parametrize("world,T", [(2, (37, 5)), (4, (9, 1, 30, 2)), (8, (5, 1, 12, 3, 8, 2, 7, 4))])
 def test_one_row_per_token_and_gpu(world, T):
     """One row per (token, GPU) out and one partial sum back: the outputs agree with the single process's to f32
     rounding (the sum over a token's experts is taken GPU by GPU), and fewer rows cross than there are assignments."""

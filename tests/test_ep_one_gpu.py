@@ -78,7 +78,8 @@ def test_two_ranges_on_one_gpu_match_the_whole_layer(wtype, rows):
             st.close()
 
 
-@pytest.mark.parametrize("wtype,rows,world", [("Q4_K", (300, 41), 2), ("IQ3_S", (7, 1, 30, 12), 4), ("Q8_0", (64, 33), 2)])
+@pytest.mark.parametrize("wtype,rows,world", [("Q4_K", (300, 41), 2), ("IQ3_S", (7, 1, 30, 12), 4), ("Q8_0", (64, 33), 2),
+                                              ("Q4_K", (40, 3, 17, 1, 64, 9, 25, 12), 8)])
 def test_one_row_per_token_and_gpu_on_one_gpu(wtype, rows, world):
     """The same on one GPU for the other form of the exchange: one row per (token, GPU) out, one weighted partial sum
     back. Each rank's outputs are held to the oracle (and so to the whole layer's) within the layer's bar; the rows
