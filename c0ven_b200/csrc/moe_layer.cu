@@ -569,8 +569,10 @@ constexpr uint64_t kGatherInKernelRows = 163840;  // expert rows from which the 
 // The routed experts on the R rows a pack lists: gate/up and SwiGLU into h, h quantised, down into y (expert order).
 // most: the most rows one expert can have (a step's tokens; in an expert-parallel call, not known below R).
 // y16: the results in f16 (only with every expert on the tile kernels: the integer-dot kernels write f32).
+// rows_in: when not 0, src holds that many rows and every one of them has R / rows_in places in expert order, pk.inv[row *
+// (R / rows_in) + k] (a GPU's own step); 0: a row's places are not laid out so (rows that came from other GPUs).
 void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint64_t most, uint32_t tm, void *y, bool y16,
-                   cudaStream_t st) {
+                   cudaStream_t st, uint32_t rows_in = 0) {
   const uint32_t E = l->E, F = l->F, nexp = pk.nexp;
   const moe_layer_config &c = l->cfg;
   // The most groups and big tiles the rows can make: an expert below tm rows has (tm - 2) / 8 + 1 groups at most, and one
@@ -584,17 +586,20 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
   const uint32_t max_big = tm_low && R >= tm_low ? (uint32_t)(R / kTileN + std::min<uint64_t>(nexp, R / tm_low)) : 0;
   // With MOE_FLAG_GATHER_IN_KERNEL, long steps of a GPU's own rows: the gate/up tile kernel gathers the rows by index
   // itself (cp.async.bulk.tensor's tile::gather4 form, 32 copies of four rows a stage for a pair's CTA instead of two
-  // boxes of 64). The copies then set that kernel's pace (1.39 -> 1.85 ms at 32,768 rows) but the 0.48 ms gather kernel
-  // and its 1.3 GB each way go: the step 4.39 -> 4.35 ms on one box; no gain at 3,521 rows. Not the default: one part in
-  // a hundred of a step for a dominant kernel that no longer runs at the tensor cores' pace. (The same gather by the
-  // copy warp's own 16-byte asynchronous copies, cp.async, was slower still: 2.26 ms.)
+  // boxes of 64) and no copy to expert order runs. The copies then set that kernel's pace (1.39 -> 1.85 ms at 32,768
+  // rows): even with the 0.48 ms the copy took as a gather, 0.2 ms behind the 0.24 ms it takes as a scatter. Off by default.
+  // (The same gather by the copy warp's own 16-byte asynchronous copies, cp.async, was slower still: 2.26 ms.)
   const bool gather_in_kernel = (l->cfg.flags & MOE_FLAG_GATHER_IN_KERNEL) && max_big && R >= kGatherInKernelRows &&
                                 src.h == l->xq_routed.h.get() && src.act_row != nullptr;
   if (max_big) {
     // The rows in expert order first (the reference's p_moe_scatter, kernels/models/qwen4exp/prompt.cl:744-754): a tile's
     // rows are then one box after another for the kernel's copies. Part of the pack stage: the gate/up stage times the
     // product's own kernels.
-    if (!gather_in_kernel) {
+    if (gather_in_kernel) {
+    } else if (rows_in) {
+      k_scatter_f16<<<rows_in, 256, 0, st>>>(src.h, pk.inv.get(), (uint32_t)(R / rows_in), E, l->xg.get());
+      launched(l, cudaGetLastError(), "rows to expert order");
+    } else {
       k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
       launched(l, cudaGetLastError(), "rows to expert order");
     }
@@ -720,7 +725,7 @@ void forward_device(moe_layer *l, const float *x, uint32_t T, float *out, cudaSt
   }
   const ActSource src{l->xq_routed.view(), l->xq_routed.h.get(), l->pack.row_src.get()};
   const bool y16 = results_f16(l, l->last_tensor_min);
-  stage_experts(l, src, l->pack, A, T, l->last_tensor_min, l->y.get(), y16, st);
+  stage_experts(l, src, l->pack, A, T, l->last_tensor_min, l->y.get(), y16, st, T);
   if (beside)
     CUDA_OK(cudaStreamWaitEvent(st, l->join_ev->get(), 0));
   else

@@ -76,8 +76,8 @@ typedef struct {
 #define MOE_FLAG_PROFILE 1u     /* time every stage of a call with events (moe_layer_stage_ms) */
 #define MOE_FLAG_NO_TENSOR 2u   /* every expert product by the integer-dot kernels, whatever its rows */
 #define MOE_FLAG_GATHER_IN_KERNEL 4u /* long steps (163,840 expert rows and more): the gate/up tile kernel gathers its rows by
-                                      * index itself instead of reading a copy made in expert order; the step's gather kernel and
-                                      * that copy's traffic go, the tile kernel runs at the pace of its copies */
+                                      * index itself instead of reading a copy made in expert order; that copy and its traffic
+                                      * go, the tile kernel runs at the pace of its own copies (slower in all: off by default) */
 
 /* Host pointers, read during moe_layer_create and not kept. Experts are the file's tensors
  * blk.N.ffn_{gate,up,down}_exps.weight cut to this GPU's experts: expert e's slice at e * its bytes, rows of whole
