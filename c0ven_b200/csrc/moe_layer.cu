@@ -178,7 +178,6 @@ struct moe_layer {
   float router_eps_rel = 0.0f, router_eps_abs = 0.0f;
   DeviceBuffer<int32_t> ids, ids_local;
   DeviceBuffer<uint32_t> error;
-  DeviceBuffer<__half> wire_h;  // rows from other GPUs, dequantised for the tensor-core kernels
   DeviceBuffer<__half> xg;      // the routed experts' activation rows in expert order, f16: what their tile kernel copies from
   CUtensorMap xg_map{};
 
@@ -358,7 +357,6 @@ void create(moe_layer *l, const moe_layer_config &c, const moe_layer_weights &w)
   if (ep) {
     l->pack_local.alloc(R, l->local, kLocalChunk);
     l->ids_local.alloc(R);
-    if (l->can_tensor) l->wire_h.alloc(R * E);
   }
   l->h.alloc((R + T) * F), l->y.alloc(R * E);
   if (l->can_tensor) {
@@ -571,8 +569,9 @@ constexpr uint64_t kGatherInKernelRows = 163840;  // expert rows from which the 
 // y16: the results in f16 (only with every expert on the tile kernels: the integer-dot kernels write f32).
 // rows_in: when not 0, src holds that many rows and every one of them has R / rows_in places in expert order, pk.inv[row *
 // (R / rows_in) + k] (a GPU's own step); 0: a row's places are not laid out so (rows that came from other GPUs).
+// in_order: the caller has put the rows' f16 form in expert order already (l->xg).
 void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, uint64_t R, uint64_t most, uint32_t tm, void *y, bool y16,
-                   cudaStream_t st, uint32_t rows_in = 0) {
+                   cudaStream_t st, uint32_t rows_in = 0, bool in_order = false) {
   const uint32_t E = l->E, F = l->F, nexp = pk.nexp;
   const moe_layer_config &c = l->cfg;
   // The most groups and big tiles the rows can make: an expert below tm rows has (tm - 2) / 8 + 1 groups at most, and one
@@ -595,12 +594,9 @@ void stage_experts(moe_layer *l, const ActSource &src, const PackBuffers &pk, ui
     // The rows in expert order first (the reference's p_moe_scatter, kernels/models/qwen4exp/prompt.cl:744-754): a tile's
     // rows are then one box after another for the kernel's copies. Part of the pack stage: the gate/up stage times the
     // product's own kernels.
-    if (gather_in_kernel) {
-    } else if (rows_in) {
+    if (!gather_in_kernel && !in_order) {
+      if (!rows_in) throw std::logic_error("rows neither in expert order nor with their places laid out");
       k_scatter_f16<<<rows_in, 256, 0, st>>>(src.h, pk.inv.get(), (uint32_t)(R / rows_in), E, l->xg.get());
-      launched(l, cudaGetLastError(), "rows to expert order");
-    } else {
-      k_gather_f16<<<(unsigned)((R * (E / 8) + 255) / 256), 256, 0, st>>>(src.h, src.act_row, R, E, l->xg.get());
       launched(l, cudaGetLastError(), "rows to expert order");
     }
   }
@@ -1018,15 +1014,15 @@ MOE_API moe_status moe_layer_experts_device(moe_layer *l, const void *rows_dev, 
     ActSource src{ActView{(const int8_t *)wire, (const float *)(wire + E), (const int16_t *)(wire + E + dbytes), wb, wb, wb}, nullptr,
                   pk.row_src.get()};
     if (tm) {
+      // The rows' f16 form straight to their places in expert order (one place a row here).
       const uint64_t nblk = (uint64_t)R * (E / 256);
-      k_wire_to_f16<<<(unsigned)((nblk + 7) / 8), 256, 0, st>>>(wire, E, q8k, nblk, l->wire_h.get());
-      launched(l, cudaGetLastError(), "wire rows to f16");
-      src.h = l->wire_h.get();
+      k_wire_to_f16<<<(unsigned)((nblk + 7) / 8), 256, 0, st>>>(wire, E, q8k, nblk, l->xg.get(), 0, ids_dev, pk.inv.get(), 1, l->Rmax);
+      launched(l, cudaGetLastError(), "wire rows to f16, in expert order");
     }
     l->last_pack = &pk;
     // The results stay f16 in between only when they also leave as f16 (f32 results are the bit-exact mode).
     const bool y16 = y_f16 && results_f16(l, tm);
-    stage_experts(l, src, pk, R, R, tm, l->y.get(), y16, st);
+    stage_experts(l, src, pk, R, R, tm, l->y.get(), y16, st, 0, true);
     if (y16)
       k_unpermute<__half, __half><<<R, 256, 0, st>>>((const __half *)l->y.get(), pk.inv.get(), E, (__half *)y_dev);
     else if (y_f16)
@@ -1112,14 +1108,15 @@ MOE_API moe_status moe_layer_experts_partial_device(moe_layer *l, const void *ro
     ActSource src{ActView{(const int8_t *)wire, (const float *)(wire + E), (const int16_t *)(wire + E + dbytes), wb2, wb2, wb2}, nullptr,
                   pk.row_src.get()};
     if (tm) {
+      // The rows' f16 form straight to their places in expert order: a row is read once, as it came, and no copy of the
+      // rows in their own order is made on the way.
       const uint64_t nblk = (uint64_t)R * (E / 256);
-      k_wire_to_f16<<<(unsigned)((nblk + 7) / 8), 256, 0, st>>>(wire, E, q8k, nblk, l->wire_h.get(), wb2);
-      launched(l, cudaGetLastError(), "wire rows to f16");
-      src.h = l->wire_h.get();
+      k_wire_to_f16<<<(unsigned)((nblk + 7) / 8), 256, 0, st>>>(wire, E, q8k, nblk, l->xg.get(), wb2, l->ids_local.get(), pk.inv.get(), K, l->Rmax);
+      launched(l, cudaGetLastError(), "wire rows to f16, in expert order");
     }
     l->last_pack = &pk;
     const bool y16 = results_f16(l, tm);
-    stage_experts(l, src, pk, A, A, tm, l->y.get(), y16, st);
+    stage_experts(l, src, pk, A, A, tm, l->y.get(), y16, st, 0, true);
     if (y16)
       k_combine_partial<__half><<<R, 256, 0, st>>>((const __half *)l->y.get(), pk.inv.get(), l->ids_local.get(), l->w_local.get(), K, E, (__half *)y_dev);
     else

@@ -577,20 +577,12 @@ static __global__ void __launch_bounds__(128) k_received_ids(const uint32_t *__r
   for (uint32_t i = threadIdx.x; i < n; i += 128) ids[start + i] = (int32_t)(first + b % per);
 }
 
-// dst[r] = src[row_src[r]] for r < R: the rows' f16 activations put in expert order, 16 bytes a thread, so that the
-// tile kernels' bulk-tensor copies find a tile's rows one after another.
-static __global__ void __launch_bounds__(256) k_gather_f16(const __half *__restrict__ src, const uint32_t *__restrict__ row_src, uint64_t R,
-                                                   uint32_t K, __half *__restrict__ dst) {
-  const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x, per = K / 8, r = i / per;
-  if (r >= R) return;
-  const uint32_t c = (uint32_t)(i % per);
-  ((uint4 *)(dst + r * K))[c] = __ldg((const uint4 *)(src + (uint64_t)row_src[r] * K) + c);
-}
-
-// The same copy from the rows' side, for a step whose every row has `per_row` places in expert order, place_of[t * per_row
-// + k]: dst[place_of[t * per_row + k]] = src[t]. A CTA a row; a thread reads 16 bytes of it once and writes them per_row
-// times. The gather reads a row once per place, in expert order, long after its last use left the L2: at 32,768 rows of
-// 2,048 values and ten places a row it read 1.0 GB from DRAM for the 134 MB of rows there are.
+// The rows' f16 activations put in expert order, so that the tile kernels' bulk-tensor copies find a tile's rows one
+// after another (the reference's p_moe_scatter, kernels/models/qwen4exp/prompt.cl:744-754), for a step whose every row has
+// `per_row` places in expert order, place_of[t * per_row + k]: dst[place_of[t * per_row + k]] = src[t]. A CTA a row; a
+// thread reads 16 bytes of it once and writes them per_row times. (The same copy taken from the places' side, dst[r] =
+// src[row_src[r]], reads a row once per place, in expert order, long after its last use left the L2: at 32,768 rows
+// of 2,048 values and ten places a row it read 1.0 GB from DRAM for the 134 MB of rows there are, and took twice as long.)
 static __global__ void __launch_bounds__(256) k_scatter_f16(const __half *__restrict__ src, const uint32_t *__restrict__ place_of, uint32_t per_row,
                                                     uint32_t K, __half *__restrict__ dst) {
   const uint64_t t = blockIdx.x;
@@ -884,8 +876,13 @@ static __global__ void __launch_bounds__(256) k_gather_wire(const ActView act, u
 
 // The f16 operand of the tensor-core kernels from wire rows: code * scale, as the quantisers write it. One warp per
 // 256 values. row_stride: bytes from a row to the next when they carry more than the row itself (0: none).
+// With place_of, a row goes straight to its places in expert order instead of to its own index: row r has up to
+// `places` entries, entry k with an expert when ids[r * places + k] >= 0 and then at row place_of[r * places + k] of
+// out's out_rows rows.
 static __global__ void __launch_bounds__(256) k_wire_to_f16(const uint8_t *__restrict__ wire, uint32_t K, bool q8k, uint64_t nblk256,
-                                                           __half *__restrict__ out, uint32_t row_stride = 0) {
+                                                           __half *__restrict__ out, uint32_t row_stride = 0,
+                                                           const int32_t *__restrict__ ids = nullptr, const uint32_t *__restrict__ place_of = nullptr,
+                                                           uint32_t places = 0, uint64_t out_rows = 0) {
   const uint64_t blk = (uint64_t)blockIdx.x * 8 + threadIdx.x / 32;
   if (blk >= nblk256) return;
   const uint32_t lane = threadIdx.x % 32, per_row = K / 256, wb = row_stride ? row_stride : wire_row_bytes(q8k, K);
@@ -898,7 +895,17 @@ static __global__ void __launch_bounds__(256) k_wire_to_f16(const uint8_t *__res
   const __half2 h2 = __floats2half2_rn(d * (float)hi.x, d * (float)hi.y), h3 = __floats2half2_rn(d * (float)hi.z, d * (float)hi.w);
   uint4 o;
   o.x = *(const uint32_t *)&h0, o.y = *(const uint32_t *)&h1, o.z = *(const uint32_t *)&h2, o.w = *(const uint32_t *)&h3;
-  ((uint4 *)(out + row * K + 256 * b))[lane] = o;
+  if (!place_of) {
+    ((uint4 *)(out + row * K + 256 * b))[lane] = o;
+    return;
+  }
+  // A place past out's rows can only come from an id that is not one of this GPU's experts (the pack leaves such an
+  // entry's place unset): it is skipped, not written.
+  for (uint32_t k = 0; k < places; k++) {
+    if (__ldg(ids + row * places + k) < 0) continue;
+    const uint64_t place = __ldg(place_of + row * places + k);
+    if (place < out_rows) ((uint4 *)(out + place * K + 256 * b))[lane] = o;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
