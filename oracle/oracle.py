@@ -25,6 +25,15 @@ def build() -> str:
     return _SO
 
 
+def build_ref(reference_root: str) -> str | None:
+    """Compiles the reference's shared layout headers, where they lie under reference_root, into oracle/_ref/
+    (ref_layout.cpp); None when that tree is not there."""
+    if not os.path.exists(os.path.join(reference_root, "shared", "quant.h")):
+        return None
+    subprocess.run(["make", "-C", _HERE, "REFERENCE=" + os.path.abspath(reference_root), "ref"], check=True, capture_output=True)
+    return os.path.join(_HERE, "_ref", "libref_layout.so")
+
+
 class Tile(C.Structure):
     _fields_ = [("expert", C.c_uint32), ("slot", C.c_uint32), ("start", C.c_uint32), ("count", C.c_uint32)]
 
