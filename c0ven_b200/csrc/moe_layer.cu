@@ -229,7 +229,8 @@ void launch_pack(moe_layer *l, PackBuffers &pk, const PackJob &j, cudaStream_t s
   k_pack_scan<<<1, 512, 0, st>>>(pk.chunk_hist.get(), j.nchunks, pk.nexp, j.first_expert, j.tensor_min, j.tensor_budget, j.group_max, pk.out(), groups,
                                  ngroups);
   launched(l, cudaGetLastError(), "pack scan");
-  k_pack_fill<<<j.nchunks, 512, j.chunk_len * sizeof(int32_t), st>>>(j.ids, j.entries, j.chunk_len, pk.nexp, pk.base.get(), pk.chunk_off.get(), j.src_div,
+  if (j.chunk_len > 512 || pk.nexp > 512) throw std::logic_error("pack fill: a chunk of at most 512 entries, at most 512 experts");
+  k_pack_fill<<<j.nchunks, 512, 16 * pk.nexp * sizeof(uint32_t), st>>>(j.ids, j.entries, j.chunk_len, pk.nexp, pk.base.get(), pk.chunk_off.get(), j.src_div,
                                                                  pk.inv.get(), pk.row_src.get(), j.first_expert, groups);
   launched(l, cudaGetLastError(), "pack fill");
 }
