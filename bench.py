@@ -119,8 +119,8 @@ _STAGES = ("quantize", "router", "pack", "gate_up", "down", "shared", "combine",
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), by
 # (workload, rows, stage), per launch (one layer); the summaries under profiles/ say which capture. None: not captured.
-TRAFFIC = {("prefill32768_q4_k", 32768, "gate_up"): 3132.9e6, ("prefill32768_q4_k", 32768, "down"): 2008.6e6,
-           ("ragged3521_q4_k_zipf", 3521, "gate_up"): 417.9e6, ("ragged3521_q4_k_zipf", 3521, "down"): 259.1e6,
+TRAFFIC = {("prefill32768_q4_k", 32768, "gate_up"): 2747.6e6, ("prefill32768_q4_k", 32768, "down"): 1932.4e6,
+           ("ragged3521_q4_k_zipf", 3521, "gate_up"): 417.9e6, ("ragged3521_q4_k_zipf", 3521, "down"): 258.9e6,
            ("decode1_q8_0", 32, "gate_up"): 554.2e6, ("decode1_q8_0", 32, "down"): 280.5e6, ("stack48_verify32_iq3_s", 32, "gate_up"): 220.6e6}
 
 
