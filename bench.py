@@ -124,6 +124,13 @@ TRAFFIC = {("prefill32768_q4_k", 32768, "gate_up"): 2747.6e6, ("prefill32768_q4_
            ("decode1_q8_0", 32, "gate_up"): 554.2e6, ("decode1_q8_0", 32, "down"): 280.5e6, ("stack48_verify32_iq3_s", 32, "gate_up"): 220.6e6}
 
 
+def host_chunk_for(T: int) -> int:
+    """Rows a chunk of a host-buffer call takes (the layer's host_chunk_rows; 0: the call whole). Long batches go in
+    chunks of 8,192 rows; batches of a few thousand in two halves (3,521 rows: 1.71 -> 1.56 ms end to end; in three or
+    four parts 1.79 and 1.85); shorter ones whole."""
+    return 8192 if T >= 16384 else T // 2 if T >= 2048 else 0
+
+
 def traffic_for(name: str, T: int, stage: str):
     """The captured DRAM bytes per launch of a workload's dominant kernel, or None when there is no capture."""
     return TRAFFIC.get((name, T, stage))
@@ -220,7 +227,7 @@ def measure(args, w, steps, world, rank, local, dist, cpu=True):
         lw = base if i == 0 else dict(base, router=(np.random.default_rng(100 + i).standard_normal((NE, E)) * 0.02).astype(np.float32))
         if world == 1:
             m = MoELayer(lw, max_tokens=T, device=local, profile=False, tensor_min_rows=args.tensor_min,
-                         host_chunk_rows=args.host_chunk if args.host_chunk >= 0 else (8192 if T >= 16384 else 0),
+                         host_chunk_rows=args.host_chunk if args.host_chunk >= 0 else host_chunk_for(T),
                          gather_in_kernel=args.gather_in_kernel)
             layers.append(m), moes.append(None)
             main_sp = main_sp or m.stream
@@ -507,7 +514,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="layers instead of the workload's")
     ap.add_argument("--tokens", type=int, default=0, help="rows instead of the workload's (the sweep's points)")
     ap.add_argument("--host-chunk", type=int, default=-1,
-                    help="rows of a chunk of the host-buffer call, whose copies overlap its neighbours' computation (0: never cut; default: 8192 for batches of 16384 rows and more)")
+                    help="rows of a chunk of the host-buffer call, whose copies overlap its neighbours' computation (0: never cut; default: 8192 for batches of 16384 rows and more, two halves from 2048 rows)")
     ap.add_argument("--per-assignment", action="store_true", help="expert parallel: one row per assignment on the wire (one GPU's bits) instead of one per (token, GPU)")
     ap.add_argument("--gather-in-kernel", action="store_true",
                     help="long steps: the gate/up tile kernel gathers its rows by index itself (MOE_FLAG_GATHER_IN_KERNEL)")
